@@ -1,0 +1,234 @@
+/*
+ * sso_b200 -- C ABI of the B200 (sm_100a) K-FAC curvature kernels.
+ *
+ * The reference library (PyTorch-SSO) has no C ABI of its own: its native work is done by
+ * torch ATen, CuPy/cuSOLVER and ChainerMN calls made from Python.  Each entry point below
+ * names the reference call site(s) (path within the reference project : lines) whose work
+ * it replaces.  The Python package `torchsso` in this repository binds these symbols with
+ * ctypes; nothing here takes or returns a torch type.
+ *
+ * Conventions
+ *   - every pointer named *_dev / x / out / ... is a DEVICE pointer unless the comment says
+ *     host; matrices are row-major fp32 unless a dtype argument says otherwise;
+ *   - `stream` is a cudaStream_t passed as void*; calls enqueue work and return without
+ *     synchronising (plan creation is the exception: it uploads its tables synchronously);
+ *   - return value 0 = success, negative = error (sso_last_error() gives the text);
+ *   - no entry point allocates device memory unless its comment says so: callers size
+ *     scratch with the *_bytes query and pass it in;
+ *   - numerical failure (non-positive pivot) is reported asynchronously through an int
+ *     `info` array on the device, LAPACK style (0 = ok, k > 0 = first bad pivot, 1-based).
+ */
+#ifndef SSO_B200_H_
+#define SSO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SSO_VERSION 100
+
+enum { SSO_F32 = 0, SSO_BF16 = 1, SSO_F16 = 2 };
+/* factor kernel implementations: AUTO picks tcgen05 when the shape is supported */
+enum { SSO_IMPL_AUTO = 0, SSO_IMPL_SIMT = 1, SSO_IMPL_TCGEN05 = 2 };
+
+int sso_version(void);
+const char* sso_last_error(void);
+
+/* ---------------------------------------------------------------------------------------
+ * Kronecker factor construction (symmetric rank-k update with the im2col gather fused in).
+ *
+ *   out <- alpha * sum_r w[n(r)] * u_r u_r^T  +  beta * out,        out is d x d, ld = ldo
+ *
+ * u_r is row r = (n, ho, wo) of the im2col matrix of x (logical NCHW dims n,c,h,w with
+ * element strides sn,sc,sh,sw -- channels_last and plain 2-D matrices are stride choices),
+ * columns ordered (c, kh, kw); append_ones adds a trailing column of ones (bias).  w is an
+ * optional per-sample weight (length n, fp32), NULL = 1.  Both triangles of out are written.
+ * A plain matrix X[rows, cols] is the case n=rows, c=cols, h=w=kh=kw=1.
+ *
+ * Replaces: torchsso/curv/cov/linear.py:50-67 (einsum 'ki,kj->ij' + cat of ones),
+ *           torchsso/curv/cov/conv.py:47-74 (F.unfold, transpose/reshape copy, cat, einsum),
+ *           torchsso/curv/fisher/linear.py:44-53, torchsso/curv/fisher/conv.py:56-66
+ *           (prob-weighted variants), the in-place rescale at torchsso/curv/curvature.py:299-300
+ *           and the accumulation at torchsso/utils/accumulator.py:23-38 (through alpha/beta).
+ * ------------------------------------------------------------------------------------- */
+size_t sso_factor_workspace_bytes(int64_t rows, int64_t d, int impl);
+
+int sso_factor_syrk_im2col(const void* x, int dtype,
+                           int64_t n, int64_t c, int64_t h, int64_t w,
+                           int64_t sn, int64_t sc, int64_t sh, int64_t sw,
+                           int kh, int kw, int stride_h, int stride_w,
+                           int pad_h, int pad_w, int dil_h, int dil_w,
+                           int append_ones, const float* sample_weight,
+                           float alpha, float beta, float* out, int64_t ldo,
+                           void* workspace, size_t workspace_bytes, int impl, void* stream);
+
+int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols,
+                    int64_t row_stride, int64_t col_stride,
+                    int append_ones, const float* row_weight,
+                    float alpha, float beta, float* out, int64_t ldo,
+                    void* workspace, size_t workspace_bytes, int impl, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * BatchNorm diagonal curvature in two streaming stages, so that nothing activation-sized
+ * is kept between forward and backward (in-place ReLU / residual adds may overwrite the
+ * layer output afterwards):
+ *   forward :  sx[n,c] = sum_hw ((y - shift[c]) / scale[c])^2       (y = layer output)
+ *   backward:  sg[n,c] = sum_hw g^2                                  (g = grad of the output)
+ *   finish  :  w_out[c] <- alpha/n * sum_n sx * p_n * sg + beta * w_out[c]
+ *              b_out[c] <- alpha/n * sum_n      p_n * sg + beta * b_out[c]     (b_out nullable)
+ * y / g are logical [n, c, hw] with element strides (s*n, s*c, s*p); either may be NULL to
+ * run only the other half; scale/shift NULL mean 1/0; p = sample_weight or 1.
+ * Replaces: torchsso/curv/curvature.py:123-134 (restore normalised input),
+ *           torchsso/curv/cov/batchnorm.py:10-49, torchsso/curv/fisher/batchnorm.py:11-32.
+ * ------------------------------------------------------------------------------------- */
+int sso_bn_plane_sums(const void* y, const void* g, int dtype, int64_t n, int64_t c, int64_t hw,
+                      int64_t syn, int64_t syc, int64_t syp, int64_t sgn, int64_t sgc, int64_t sgp,
+                      const float* scale, const float* shift, float* sx, float* sg, void* stream);
+int sso_bn_diag_finish(const float* sx, const float* sg, const float* sample_weight,
+                       int64_t n, int64_t c, float alpha, float beta,
+                       float* w_out, float* b_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Streaming kernels over flat fp32 buffers.  The Python side keeps every factor of every
+ * layer in one contiguous pool per role (data / ema / inverse), so one launch covers a model.
+ * ------------------------------------------------------------------------------------- */
+/* ema <- first ? data : beta*data + (1-beta)*ema      (beta weights the NEW data)
+ * Replaces: torchsso/curv/curvature.py:174-191. */
+int sso_ema_update(const float* data, float* ema, int64_t count, float beta, int first, void* stream);
+/* dst <- a*src + b*dst (dst is not read when b == 0).  Replaces the scale/accumulate copies of
+ * torchsso/utils/accumulator.py:23-53 and torchsso/optim/secondorder.py:174-182,213-223. */
+int sso_axpby(const float* src, float* dst, int64_t count, float a, float b, void* stream);
+/* Diagonal curvature:  inv <- 1/(ema [sqrt] + damping) if update_inv;  grad <- grad*inv if grad.
+ * Replaces: torchsso/curv/curvature.py:226-238. */
+int sso_diag_inv_precondition(const float* ema, float* inv, float* grad, int64_t count,
+                              float damping, int use_sqrt, int update_inv, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Triangular packing for the factor exchange: packed[n*y - y*(y+1)/2 + x] = scale*m[y][x],
+ * x >= y (row-major upper triangle); unpack writes both triangles.  One record = a run of
+ * rows of one matrix, one CTA per record; the table lives in device memory.
+ * Replaces: torchsso/utils/chainer_communicators/_utility.py:19-33 (unpack kernel),
+ *           :59-86 (cuBLAS trttp pack) and the mean kernel at
+ *           torchsso/utils/chainer_communicators/pure_nccl_communicator.py:184-199,430-435
+ *           (through scale).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  float* m;          /* matrix base (row-major, leading dimension ld) */
+  float* packed;     /* base of this matrix's packed triangle */
+  int32_t n, ld;
+  int32_t row0, nrows;
+} sso_tri_rec;
+int sso_tri_pack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream);
+int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Tile-task engine.  All dense algebra after factor construction (pi-damped SPD inverse,
+ * Cholesky factor of the inverse, G^-1 dW A^-1, posterior sampling) is expressed as phases
+ * of independent tile tasks   C[m x n] <- alpha * op(A)[m x k] * op(B)[k x n] + beta * C
+ * plus a small dense diagonal-block factorisation; one kernel launch runs a whole phase for
+ * every matrix of every layer.  A plan is built once for a fixed set of device buffers.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  const float* A;
+  const float* B;
+  float* C;
+  float* C2;          /* optional transposed copy of the tile (mirror), NULL if unused */
+  int32_t lda, ldb, ldc, ldc2;
+  int32_t m, n, k;
+  uint32_t flags;     /* bit0: A transposed, bit1: B transposed */
+  float alpha, beta;
+} sso_tile_task;
+
+/* diagonal-block record: factor block (<= 64 x 64) in place, also write the inverse of its factor */
+typedef struct {
+  float* L;           /* block (j,j) of the working matrix; lower triangle valid on entry */
+  float* Linv;        /* receives the inverse of the block's Cholesky factor */
+  int32_t ld_l, ld_inv;
+  int32_t size;       /* valid rows/cols of this block */
+  int32_t mat;        /* matrix index (for info) */
+  int32_t row0;       /* first global row of the block (for info) */
+  int32_t info_slot;  /* 0 inverse pass, 1 Cholesky-of-inverse pass */
+} sso_diag_rec;
+
+/* copy record: a run of whole rows of one d x d matrix */
+typedef struct {
+  const float* src;
+  float* dst;
+  int32_t d;
+  int32_t row0, nrows;
+  int32_t mat;        /* index into the diagonal-shift table, or -1 */
+  int32_t mode;       /* 0 dst = src (+ shift on the diagonal), 1 dst = upper-triangular transpose
+                         of src's lower triangle, 2 dst = 0 */
+  int32_t pad;
+} sso_copy_rec;
+
+typedef struct {
+  int32_t kind;       /* 0 gemm64, 1 gemm128, 2 diag-block factor, 3 copy */
+  int32_t first;      /* first record of this phase in its table */
+  int32_t count;      /* number of records (= CTAs) */
+  int32_t reserved;
+} sso_phase;
+
+/* Batched pi-damped SPD inverse (and optional upper Cholesky factor of the result).
+ *   for matrix i:  M_i = src_i + v_i * I,  v_i = r_i * pi  (role 0, "A")  or  r_i / pi  (role 1, "G")
+ *                  pi  = sqrt( (tr A / d_A) / (tr G / d_G) ) of the pair (i, partner_i); partner -1 => pi = 1
+ *                  dst_i <- M_i^-1 (both triangles);   std_i <- U with U^T U = dst_i (upper), if requested
+ * Replaces: torchsso/curv/curvature.py:302-312 and :334-340 (pi, add_value_to_diagonal),
+ *           torchsso/utils/inv_cupy.py:27-132 (cuSOLVER potrf + potrs against identity),
+ *           torchsso/curv/curvature.py:317-321 with torchsso/utils/cholesky_cupy.py:9-14.
+ * All arrays are HOST arrays of length n_mats; work_i is d_i*d_i floats of scratch.
+ * dev_mem (device, sso_kron_plan_dev_bytes bytes) receives the tables; host_only != 0 builds
+ * the plan without touching the device (for inspecting the task program on a CPU).
+ * Returns a plan handle > 0, or a negative error. */
+size_t sso_kron_plan_dev_bytes(int n_mats, const int64_t* dims, int with_std);
+int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src, float* const* dst,
+                             float* const* work, float* const* std_out /* nullable */,
+                             const int32_t* partner, const int32_t* role,
+                             void* dev_mem, size_t dev_mem_bytes, int host_only);
+/* damp_r_dev: per-matrix r = sqrt(damping); info_dev: per-matrix status (2 ints: inverse, std) */
+int sso_kron_plan_run(int64_t plan, const float* damp_r_dev, int* info_dev,
+                      int do_inverse, int do_std, void* stream);
+
+/* Kronecker precondition  dW|db <- G^-1 [dW|db] A^-1  for a set of layers, in place.
+ * Replaces: torchsso/curv/cov/linear.py:69-84, torchsso/curv/cov/conv.py:76-92 (cat, 2 mm, 2 copies).
+ * HOST arrays of length n_layers; gb_i may be NULL (no bias => d_A is the weight's column
+ * count, else columns + 1); tmp_i is dG_i*dA_i floats of scratch. */
+size_t sso_precond_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t* dG);
+int64_t sso_precond_plan_create(int n_layers, const int64_t* dA, const int64_t* dG,
+                                float* const* A_inv, float* const* G_inv,
+                                float* const* gw, float* const* gb, float* const* tmp,
+                                void* dev_mem, size_t dev_mem_bytes, int host_only);
+int sso_precond_plan_run(int64_t plan, void* stream);
+
+/* Posterior sampling  [W|b] <- [W|b] + s * U_G E U_A  (W, b pre-loaded with the mean by the
+ * caller; E is dG x dA standard normal, supplied).  U_* upper triangular.
+ * Replaces: torchsso/curv/cov/linear.py:86-100, torchsso/curv/cov/conv.py:94-108. */
+size_t sso_sample_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t* dG);
+int64_t sso_sample_plan_create(int n_layers, const int64_t* dA, const int64_t* dG,
+                               float* const* U_A, float* const* U_G, float* const* noise,
+                               float* const* w, float* const* b, float* const* tmp,
+                               void* dev_mem, size_t dev_mem_bytes, int host_only);
+int sso_sample_plan_run(int64_t plan, float std_scale, void* stream);
+
+int sso_plan_destroy(int64_t plan);
+
+/* Plan introspection (host side; used to check the task program without a GPU). */
+int sso_plan_num_phases(int64_t plan);
+int sso_plan_get_phase(int64_t plan, int index, sso_phase* out);
+int sso_plan_num_tasks(int64_t plan);
+int sso_plan_copy_tasks(int64_t plan, sso_tile_task* out, int capacity);
+int sso_plan_num_diag_recs(int64_t plan);
+int sso_plan_copy_diag_recs(int64_t plan, sso_diag_rec* out, int capacity);
+int sso_plan_num_copy_recs(int64_t plan);
+int sso_plan_copy_copy_recs(int64_t plan, sso_copy_rec* out, int capacity);
+
+/* Run one ad-hoc list of tile tasks that already sits in device memory. */
+int sso_run_tile_tasks(const sso_tile_task* tasks_dev, int count, int tile /* 64 or 128 */, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSO_B200_H_ */

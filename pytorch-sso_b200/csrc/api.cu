@@ -1,0 +1,79 @@
+// extern "C" entry points for factor construction plus library-wide state.
+#include "common.cuh"
+
+namespace sso {
+
+thread_local std::string g_last_error;
+}  // namespace sso
+
+#include "factor_params.cuh"
+
+namespace sso {
+size_t factor_simt_workspace_bytes(int64_t rows, int64_t d);
+int factor_simt_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
+size_t factor_tc_workspace_bytes(int64_t rows, int64_t d);
+bool factor_tc_supported(const FactorParams& p, int dtype);
+int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
+}  // namespace sso
+
+using namespace sso;
+
+extern "C" {
+
+int sso_version(void) { return SSO_VERSION; }
+const char* sso_last_error(void) { return g_last_error.c_str(); }
+
+size_t sso_factor_workspace_bytes(int64_t rows, int64_t d, int impl) {
+  const size_t a = factor_simt_workspace_bytes(rows, d);
+  const size_t b = factor_tc_workspace_bytes(rows, d);
+  if (impl == SSO_IMPL_SIMT) return a;
+  if (impl == SSO_IMPL_TCGEN05) return b;
+  return a > b ? a : b;
+}
+
+int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64_t h, int64_t w,
+                           int64_t sn, int64_t sc, int64_t sh, int64_t sw, int kh, int kw,
+                           int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                           int append_ones, const float* sample_weight, float alpha, float beta,
+                           float* out, int64_t ldo, void* workspace, size_t workspace_bytes, int impl,
+                           void* stream) {
+  SSO_CHECK_ARG(x != nullptr && out != nullptr, "factor: null pointer");
+  SSO_CHECK_ARG(n > 0 && c > 0 && h > 0 && w > 0, "factor: bad input dims");
+  SSO_CHECK_ARG(kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 &&
+                    pad_w >= 0, "factor: bad conv geometry");
+  const int64_t ho = (h + 2 * pad_h - (int64_t)dil_h * (kh - 1) - 1) / stride_h + 1;
+  const int64_t wo = (w + 2 * pad_w - (int64_t)dil_w * (kw - 1) - 1) / stride_w + 1;
+  SSO_CHECK_ARG(ho > 0 && wo > 0, "factor: empty output");
+  const int64_t dcols = c * kh * kw;
+  const int64_t d = dcols + (append_ones ? 1 : 0);
+  SSO_CHECK_ARG(d <= 65536 && n < ((int64_t)1 << 31) && ho * wo < ((int64_t)1 << 31), "factor: shape too large");
+  SSO_CHECK_ARG(ldo >= d, "factor: ldo < d");
+  FactorParams p{};
+  p.x = x; p.weight = sample_weight; p.out = out; p.partial = nullptr;
+  p.sn = sn; p.sc = sc; p.sh = sh; p.sw = sw; p.ldo = ldo;
+  p.rows = n * ho * wo;
+  p.n = (int)n; p.c = (int)c; p.h = (int)h; p.w = (int)w; p.ho = (int)ho; p.wo = (int)wo;
+  p.kh = kh; p.kw = kw; p.stride_h = stride_h; p.stride_w = stride_w;
+  p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
+  p.d = (int)d; p.dcols = (int)dcols;
+  p.alpha = alpha; p.beta = beta;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (impl == SSO_IMPL_TCGEN05) {
+    SSO_CHECK_ARG(factor_tc_supported(p, dtype), "factor: shape not supported by the tcgen05 path");
+    return factor_tc_launch(p, dtype, workspace, workspace_bytes, st);
+  }
+  if (impl == SSO_IMPL_AUTO && factor_tc_supported(p, dtype))
+    return factor_tc_launch(p, dtype, workspace, workspace_bytes, st);
+  return factor_simt_launch(p, dtype, workspace, workspace_bytes, st);
+}
+
+int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride,
+                    int64_t col_stride, int append_ones, const float* row_weight, float alpha,
+                    float beta, float* out, int64_t ldo, void* workspace, size_t workspace_bytes,
+                    int impl, void* stream) {
+  return sso_factor_syrk_im2col(x, dtype, rows, cols, 1, 1, row_stride, col_stride, 0, 0, 1, 1, 1, 1, 0, 0,
+                                1, 1, append_ones, row_weight, alpha, beta, out, ldo, workspace,
+                                workspace_bytes, impl, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,287 @@
+// HBM-streaming kernels of the K-FAC path: EMA / scaled accumulation over flat factor pools,
+// BatchNorm diagonal curvature, diagonal inverse + precondition, triangular pack / unpack.
+// All are bandwidth bound: 16-byte vector accesses where alignment allows, grids sized as a
+// multiple of the 148 SMs with a grid-stride loop.
+#include "common.cuh"
+
+namespace sso {
+
+constexpr int kSMs = 148;
+
+__device__ __forceinline__ float ema_op(float data, float ema, float beta, float omb) {
+  return fmaf(beta, data, omb * ema);
+}
+
+// dst <- a*src + b*dst  (b == 0: dst is not read)
+__global__ void __launch_bounds__(256) axpby_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                    int64_t count, float a, float b) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+  if (vec) {
+    const int64_t n4 = count >> 2;
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    for (int64_t i = tid; i < n4; i += stride) {
+      const float4 s = __ldg(s4 + i);
+      float4 o;
+      if (b == 0.f) {
+        o = make_float4(a * s.x, a * s.y, a * s.z, a * s.w);
+      } else {
+        const float4 d = d4[i];
+        o = make_float4(fmaf(a, s.x, b * d.x), fmaf(a, s.y, b * d.y), fmaf(a, s.z, b * d.z), fmaf(a, s.w, b * d.w));
+      }
+      d4[i] = o;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < count; i += stride)
+      dst[i] = (b == 0.f) ? a * src[i] : fmaf(a, src[i], b * dst[i]);
+  } else {
+    for (int64_t i = tid; i < count; i += stride)
+      dst[i] = (b == 0.f) ? a * src[i] : fmaf(a, src[i], b * dst[i]);
+  }
+}
+
+static int grid_for(int64_t count, int per_thread) {
+  const int64_t want = ceil_div64(count, (int64_t)256 * per_thread);
+  const int64_t cap = (int64_t)kSMs * 8;
+  return (int)std::max<int64_t>(1, std::min(want, cap));
+}
+
+// ------------------------------------------------------------------------------------------
+// BatchNorm diagonal curvature
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) bn_plane_sums_pcontig(const T* __restrict__ y, const T* __restrict__ g,
+                                                             int n, int c, int hw, int64_t syn, int64_t syc, int64_t syp,
+                                                             int64_t sgn, int64_t sgc, int64_t sgp,
+                                                             const float* __restrict__ scale,
+                                                             const float* __restrict__ shift,
+                                                             float* __restrict__ sx, float* __restrict__ sg) {
+  // one warp per (n, c) plane
+  const int warp = (int)(((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
+  if (warp >= n * c) return;
+  const int in = warp / c, ic = warp % c;
+  const float inv_scale = scale ? 1.f / scale[ic] : 1.f, sh = shift ? shift[ic] : 0.f;
+  const T* py = y + (int64_t)in * syn + (int64_t)ic * syc;
+  const T* pg = g + (int64_t)in * sgn + (int64_t)ic * sgc;
+  float ax = 0.f, ag = 0.f;
+  for (int p = lane; p < hw; p += 32) {
+    if (y) {
+      const float xv = (to_f32<T>(py[(int64_t)p * syp]) - sh) * inv_scale;
+      ax = fmaf(xv, xv, ax);
+    }
+    if (g) {
+      const float gv = to_f32<T>(pg[(int64_t)p * sgp]);
+      ag = fmaf(gv, gv, ag);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ax += __shfl_xor_sync(0xffffffffu, ax, o);
+    ag += __shfl_xor_sync(0xffffffffu, ag, o);
+  }
+  if (lane == 0) {
+    if (y) sx[warp] = ax;
+    if (g) sg[warp] = ag;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bn_plane_sums_ccontig(const T* __restrict__ y, const T* __restrict__ g,
+                                                             int n, int c, int hw, int64_t syn, int64_t syc, int64_t syp,
+                                                             int64_t sgn, int64_t sgc, int64_t sgp,
+                                                             const float* __restrict__ scale,
+                                                             const float* __restrict__ shift,
+                                                             float* __restrict__ sx, float* __restrict__ sg) {
+  // block = 32 channels x 8 pixel lanes; grid = (ceil(c/32), n)
+  __shared__ float rx[8][33], rg[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int ic = blockIdx.x * 32 + tx, in = blockIdx.y;
+  float ax = 0.f, ag = 0.f;
+  if (ic < c) {
+    const float inv_scale = scale ? 1.f / scale[ic] : 1.f, sh = shift ? shift[ic] : 0.f;
+    const T* py = y + (int64_t)in * syn + (int64_t)ic * syc;
+    const T* pg = g + (int64_t)in * sgn + (int64_t)ic * sgc;
+    for (int p = ty; p < hw; p += 8) {
+      if (y) {
+        const float xv = (to_f32<T>(py[(int64_t)p * syp]) - sh) * inv_scale;
+        ax = fmaf(xv, xv, ax);
+      }
+      if (g) {
+        const float gv = to_f32<T>(pg[(int64_t)p * sgp]);
+        ag = fmaf(gv, gv, ag);
+      }
+    }
+  }
+  rx[ty][tx] = ax;
+  rg[ty][tx] = ag;
+  __syncthreads();
+  if (ty == 0 && ic < c) {
+    float tx_sum = 0.f, tg_sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      tx_sum += rx[i][tx];
+      tg_sum += rg[i][tx];
+    }
+    if (y) sx[(int64_t)in * c + ic] = tx_sum;
+    if (g) sg[(int64_t)in * c + ic] = tg_sum;
+  }
+}
+
+__global__ void bn_finish_kernel(const float* __restrict__ sx, const float* __restrict__ sg,
+                                 const float* __restrict__ weight, int n, int c, float alpha,
+                                 float beta, float* __restrict__ w_out, float* __restrict__ b_out) {
+  const int ic = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ic >= c) return;
+  float aw = 0.f, ab = 0.f;
+  for (int in = 0; in < n; ++in) {
+    const float p = weight ? weight[in] : 1.f;
+    const float gsum = p * sg[(int64_t)in * c + ic];
+    aw = fmaf(sx[(int64_t)in * c + ic], gsum, aw);
+    ab += gsum;
+  }
+  const float s = alpha / (float)n;
+  w_out[ic] = (beta == 0.f) ? s * aw : fmaf(beta, w_out[ic], s * aw);
+  if (b_out) b_out[ic] = (beta == 0.f) ? s * ab : fmaf(beta, b_out[ic], s * ab);
+}
+
+template <typename T>
+static int bn_sums_typed(const void* y, const void* g, int64_t n, int64_t c, int64_t hw, int64_t syn,
+                         int64_t syc, int64_t syp, int64_t sgn, int64_t sgc, int64_t sgp,
+                         const float* scale, const float* shift, float* sx, float* sg, cudaStream_t st) {
+  const T* ty = reinterpret_cast<const T*>(y);
+  const T* tg = reinterpret_cast<const T*>(g);
+  if (syc == 1 && sgc == 1 && hw > 1) {
+    dim3 grid((unsigned)ceil_div64(c, 32), (unsigned)n);
+    bn_plane_sums_ccontig<T><<<grid, 256, 0, st>>>(ty, tg, (int)n, (int)c, (int)hw, syn, syc, syp, sgn, sgc,
+                                                    sgp, scale, shift, sx, sg);
+  } else {
+    const int64_t warps = n * c;
+    bn_plane_sums_pcontig<T><<<(unsigned)ceil_div64(warps * 32, 256), 256, 0, st>>>(
+        ty, tg, (int)n, (int)c, (int)hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg);
+  }
+  SSO_LAUNCH_OK("bn_plane_sums");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// diagonal inverse / precondition
+// ------------------------------------------------------------------------------------------
+__global__ void diag_inv_precond_kernel(const float* __restrict__ ema, float* __restrict__ inv,
+                                        float* __restrict__ grad, int64_t count, float damping,
+                                        int use_sqrt, int update_inv) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+    float v;
+    if (update_inv) {
+      float x = ema[i];
+      if (use_sqrt) x = sqrtf(x);
+      v = 1.f / (x + damping);
+      inv[i] = v;
+    } else {
+      v = inv[i];
+    }
+    if (grad) grad[i] *= v;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// triangular pack / unpack over a table of row runs
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) tri_pack_kernel(const sso_tri_rec* __restrict__ recs, float scale) {
+  const sso_tri_rec r = recs[blockIdx.x];
+  for (int row = r.row0; row < r.row0 + r.nrows; ++row) {
+    const int64_t base = (int64_t)r.n * row - (int64_t)row * (row + 1) / 2;
+    const float* src = r.m + (int64_t)row * r.ld;
+    for (int x = row + threadIdx.x; x < r.n; x += 256) r.packed[base + x] = scale * src[x];
+  }
+}
+__global__ void __launch_bounds__(256) tri_unpack_kernel(const sso_tri_rec* __restrict__ recs, float scale) {
+  const sso_tri_rec r = recs[blockIdx.x];
+  for (int row = r.row0; row < r.row0 + r.nrows; ++row) {
+    float* dst = r.m + (int64_t)row * r.ld;
+    for (int x = threadIdx.x; x < r.n; x += 256) {
+      const int lo = min(row, x), hi = max(row, x);
+      dst[x] = scale * r.packed[(int64_t)r.n * lo - (int64_t)lo * (lo + 1) / 2 + hi];
+    }
+  }
+}
+
+}  // namespace sso
+
+using namespace sso;
+
+extern "C" {
+
+int sso_axpby(const float* src, float* dst, int64_t count, float a, float b, void* stream) {
+  SSO_CHECK_ARG(src && dst && count >= 0, "axpby: bad argument");
+  if (count == 0) return 0;
+  axpby_kernel<<<grid_for(count, 16), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(src, dst, count, a, b);
+  SSO_LAUNCH_OK("axpby_kernel");
+  return 0;
+}
+
+int sso_ema_update(const float* data, float* ema, int64_t count, float beta, int first, void* stream) {
+  // first (or beta == 1): ema <- data; else ema <- beta*data + (1-beta)*ema
+  if (first || beta == 1.f) return sso_axpby(data, ema, count, 1.f, 0.f, stream);
+  return sso_axpby(data, ema, count, beta, 1.f - beta, stream);
+}
+
+int sso_bn_plane_sums(const void* y, const void* g, int dtype, int64_t n, int64_t c, int64_t hw,
+                      int64_t syn, int64_t syc, int64_t syp, int64_t sgn, int64_t sgc, int64_t sgp,
+                      const float* scale, const float* shift, float* sx, float* sg, void* stream) {
+  SSO_CHECK_ARG((y && sx) || (g && sg), "bn_plane_sums: nothing to do");
+  SSO_CHECK_ARG(!y || sx, "bn_plane_sums: y without sx");
+  SSO_CHECK_ARG(!g || sg, "bn_plane_sums: g without sg");
+  SSO_CHECK_ARG(n > 0 && c > 0 && hw > 0 && n * c < (int64_t)1 << 26, "bn_plane_sums: bad shape");
+  if (!y) { syn = sgn; syc = sgc; syp = sgp; }
+  if (!g) { sgn = syn; sgc = syc; sgp = syp; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SSO_F32:
+      return bn_sums_typed<float>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, st);
+    case SSO_BF16:
+      return bn_sums_typed<__nv_bfloat16>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, st);
+    case SSO_F16:
+      return bn_sums_typed<__half>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, st);
+  }
+  return fail(-1, "bn_plane_sums: unknown dtype %d", dtype);
+}
+
+int sso_bn_diag_finish(const float* sx, const float* sg, const float* sample_weight, int64_t n, int64_t c,
+                       float alpha, float beta, float* w_out, float* b_out, void* stream) {
+  SSO_CHECK_ARG(sx && sg && w_out && n > 0 && c > 0, "bn_diag_finish: bad argument");
+  bn_finish_kernel<<<(unsigned)ceil_div64(c, 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      sx, sg, sample_weight, (int)n, (int)c, alpha, beta, w_out, b_out);
+  SSO_LAUNCH_OK("bn_finish_kernel");
+  return 0;
+}
+
+int sso_diag_inv_precondition(const float* ema, float* inv, float* grad, int64_t count, float damping,
+                              int use_sqrt, int update_inv, void* stream) {
+  SSO_CHECK_ARG(inv && count >= 0 && (ema || !update_inv), "diag_inv_precondition: bad argument");
+  if (count == 0) return 0;
+  diag_inv_precond_kernel<<<grid_for(count, 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ema, inv, grad, count, damping, use_sqrt, update_inv);
+  SSO_LAUNCH_OK("diag_inv_precond_kernel");
+  return 0;
+}
+
+int sso_tri_pack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream) {
+  SSO_CHECK_ARG(recs_dev && n_recs >= 0, "tri_pack: bad argument");
+  if (n_recs == 0) return 0;
+  tri_pack_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale);
+  SSO_LAUNCH_OK("tri_pack_kernel");
+  return 0;
+}
+
+int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream) {
+  SSO_CHECK_ARG(recs_dev && n_recs >= 0, "tri_unpack: bad argument");
+  if (n_recs == 0) return 0;
+  tri_unpack_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale);
+  SSO_LAUNCH_OK("tri_unpack_kernel");
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,798 @@
+// Tile-task engine: batched pi-damped SPD inverse, Cholesky factor, Kronecker precondition and
+// posterior sampling, each expressed as phases of independent tile tasks
+//     C[m x n] <- alpha * op(A) * op(B) + beta * C
+// (one kernel launch per phase, covering every matrix of every layer) plus a dense 64x64
+// diagonal-block factorisation done by one CTA in shared memory.
+//
+// Blocked algorithm per SPD matrix M (block size 64, nb = ceil(d/64)):
+//   Cholesky (right looking), step j:
+//       diag   : L_jj = chol(M_jj), also Linv_jj = L_jj^-1          (diag-block kernel)
+//       panel  : L_ij = M_ij * Linv_jj^T                 for i > j  (tile tasks)
+//       update : M_ik -= L_ij * L_kj^T                   for i >= k > j
+//   Triangular inverse by recursive doubling over block ranges [first | second]:
+//       Y   = L_21 * Inv_11          (into scratch)      Inv_21 = - Inv_22 * Y
+//   Inverse:  M^-1 = Linv^T * Linv   (lower tiles computed, mirrored into the upper triangle)
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace sso {
+
+constexpr int NB = 64;  // algorithmic block size of the factorisations
+
+// ------------------------------------------------------------------------------------------
+// device records
+// ------------------------------------------------------------------------------------------
+using DiagRec = sso_diag_rec;
+using CopyRec = sso_copy_rec;
+struct MatRec {       // per-matrix data for the trace / pi kernel
+  const float* src;
+  int32_t d;
+  int32_t partner;
+  int32_t role;
+  int32_t pad;
+};
+
+// ------------------------------------------------------------------------------------------
+// tile GEMM kernel
+// ------------------------------------------------------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(256) tile_task_kernel(const sso_tile_task* __restrict__ tasks) {
+  constexpr int TILE = 16 * MT;
+  constexpr int PER = TILE * KT / 256;  // elements per thread per operand per stage
+  __shared__ __align__(16) float As[KT * TILE];
+  __shared__ __align__(16) float Bs[KT * TILE];
+  const sso_tile_task t = tasks[blockIdx.x];
+  const int tid = threadIdx.x;
+  const bool ta = t.flags & 1u, tb = t.flags & 2u;
+  // operand element (idx, k):  A: ta ? A[k*lda+idx] : A[idx*lda+k];  B: tb ? B[idx*ldb+k] : B[k*ldb+idx]
+  const bool a_kcontig = !ta, b_kcontig = tb;
+
+  float ra[PER], rb[PER];
+  auto load_op = [&](const float* __restrict__ P, int ld, bool kcontig, int lim, int k0, float (&r)[PER]) {
+    if (kcontig) {
+      const int k = k0 + (tid & 31), g = tid >> 5;
+      const bool kok = k < t.k;
+#pragma unroll
+      for (int i = 0; i < PER / 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int idx = g * 4 + 32 * i + q;
+          r[i * 4 + q] = (kok && idx < lim) ? __ldg(P + (int64_t)idx * ld + k) : 0.f;
+        }
+    } else {
+      const int idx = tid % TILE, kb = tid / TILE;
+      const bool iok = idx < lim;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int k = k0 + kb + (256 / TILE) * i;
+        r[i] = (iok && k < t.k) ? __ldg(P + (int64_t)k * ld + idx) : 0.f;
+      }
+    }
+  };
+  auto store_op = [&](float* S, bool kcontig, const float (&r)[PER]) {
+    if (kcontig) {
+      const int k = tid & 31, g = tid >> 5;
+#pragma unroll
+      for (int i = 0; i < PER / 4; ++i)
+        *reinterpret_cast<float4*>(S + k * TILE + swz(k, g * 4 + 32 * i)) =
+            make_float4(r[i * 4], r[i * 4 + 1], r[i * 4 + 2], r[i * 4 + 3]);
+    } else {
+      const int idx = tid % TILE, kb = tid / TILE;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int k = kb + (256 / TILE) * i;
+        S[k * TILE + swz(k, idx)] = r[i];
+      }
+    }
+  };
+
+  float acc[MT][MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < MT; ++j) acc[i][j] = 0.f;
+  const int ty = tid >> 4, tx = tid & 15;
+  const int nkt = ceil_div(t.k, KT);
+  if (nkt > 0) {
+    load_op(t.A, t.lda, a_kcontig, t.m, 0, ra);
+    load_op(t.B, t.ldb, b_kcontig, t.n, 0, rb);
+    store_op(As, a_kcontig, ra);
+    store_op(Bs, b_kcontig, rb);
+  }
+  __syncthreads();
+  for (int kt = 0; kt < nkt; ++kt) {
+    if (kt + 1 < nkt) {
+      load_op(t.A, t.lda, a_kcontig, t.m, (kt + 1) * KT, ra);
+      load_op(t.B, t.ldb, b_kcontig, t.n, (kt + 1) * KT, rb);
+    }
+    TileCore<MT>::compute(As, Bs, ty, tx, acc);
+    __syncthreads();
+    if (kt + 1 < nkt) {
+      store_op(As, a_kcontig, ra);
+      store_op(Bs, b_kcontig, rb);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    const int r = TileCore<MT>::row_of(ty, i);
+    if (r >= t.m) continue;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      const int c = TileCore<MT>::col_of(tx, j);
+      if (c >= t.n) continue;
+      float* o = t.C + (int64_t)r * t.ldc + c;
+      float v = t.alpha * acc[i][j];
+      if (t.beta != 0.f) v = fmaf(t.beta, *o, v);
+      *o = v;
+      if (t.C2) t.C2[(int64_t)c * t.ldc2 + r] = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// diagonal block: Cholesky of a (<=64)x(<=64) SPD block and the inverse of its factor
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) diag_block_kernel(const DiagRec* __restrict__ recs,
+                                                         int* __restrict__ info) {
+  __shared__ float S[NB][NB + 1];
+  __shared__ float Inv[NB][NB + 1];
+  __shared__ float diag_inv[NB];
+  const DiagRec rec = recs[blockIdx.x];
+  const int tid = threadIdx.x, n = rec.size;
+  for (int e = tid; e < NB * NB; e += 256) {
+    const int r = e / NB, c = e % NB;
+    float v = (r == c) ? 1.f : 0.f;  // identity padding keeps the tail harmless
+    if (r < n && c < n) v = (c <= r) ? rec.L[(int64_t)r * rec.ld_l + c] : 0.f;
+    S[r][c] = v;
+  }
+  __syncthreads();
+  // right-looking column Cholesky on the lower triangle
+  for (int j = 0; j < n; ++j) {
+    if (tid == 0) {
+      float pv = S[j][j];
+      if (!(pv > 0.f)) {  // non-positive or NaN pivot: record once, keep going with 1
+        if (info) atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + j + 1);
+        pv = 1.f;
+      }
+      const float s = sqrtf(pv);
+      S[j][j] = s;
+      diag_inv[j] = 1.f / s;
+    }
+    __syncthreads();
+    const float dj = diag_inv[j];
+    for (int r = j + 1 + tid; r < n; r += 256) S[r][j] *= dj;
+    __syncthreads();
+    // trailing update of the lower triangle: S[r][c] -= S[r][j]*S[c][j], j < c <= r < n
+    const int rem = n - j - 1;
+    for (int e = tid; e < rem * rem; e += 256) {
+      const int r = j + 1 + e / rem, c = j + 1 + e % rem;
+      if (c <= r) S[r][c] -= S[r][j] * S[c][j];
+    }
+    __syncthreads();
+  }
+  // inverse of the lower-triangular factor, one column per thread (forward substitution)
+  if (tid < NB) {
+    const int c = tid;
+    for (int r = 0; r < NB; ++r) Inv[r][c] = 0.f;
+    if (c < n) {
+      Inv[c][c] = diag_inv[c];
+      for (int r = c + 1; r < n; ++r) {
+        float s = 0.f;
+        for (int k = c; k < r; ++k) s = fmaf(S[r][k], Inv[k][c], s);
+        Inv[r][c] = -s * diag_inv[r];
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < n * n; e += 256) {
+    const int r = e / n, c = e % n;
+    rec.L[(int64_t)r * rec.ld_l + c] = (c <= r) ? S[r][c] : 0.f;
+    rec.Linv[(int64_t)r * rec.ld_inv + c] = (c <= r) ? Inv[r][c] : 0.f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// traces -> per-matrix diagonal shift v = r*pi or r/pi
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) trace_kernel(const MatRec* __restrict__ mats,
+                                                    float* __restrict__ traces) {
+  __shared__ float red[256];
+  const MatRec m = mats[blockIdx.x];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < m.d; i += 256) s += m.src[(int64_t)i * m.d + i];
+  red[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) traces[blockIdx.x] = red[0];
+}
+__global__ void shift_kernel(const MatRec* __restrict__ mats, const float* __restrict__ traces,
+                             const float* __restrict__ damp_r, float* __restrict__ shift, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const MatRec m = mats[i];
+  float pi = 1.f;
+  if (m.partner >= 0) {
+    const MatRec o = mats[m.partner];
+    const float mine = traces[i] / (float)m.d, other = traces[m.partner] / (float)o.d;
+    // pi = sqrt(mean-diag(A) / mean-diag(G)), A = the role-0 member of the pair
+    pi = (m.role == 0) ? sqrtf(mine / other) : sqrtf(other / mine);
+  }
+  shift[i] = (m.role == 0) ? damp_r[i] * pi : damp_r[i] / pi;
+}
+
+__global__ void __launch_bounds__(256) copy_kernel(const CopyRec* __restrict__ recs,
+                                                   const float* __restrict__ shift) {
+  const CopyRec r = recs[blockIdx.x];
+  const float v = (r.mat >= 0) ? shift[r.mat] : 0.f;
+  const int64_t total = (int64_t)r.nrows * r.d;
+  for (int64_t e = threadIdx.x; e < total; e += 256) {
+    const int row = r.row0 + (int)(e / r.d), col = (int)(e % r.d);
+    if (r.mode == 2) {
+      r.dst[(int64_t)row * r.d + col] = 0.f;
+    } else if (r.mode == 1) {
+      // dst = L^T restricted to the upper triangle (row <= col reads L[col][row])
+      r.dst[(int64_t)row * r.d + col] = (row <= col) ? r.src[(int64_t)col * r.d + row] : 0.f;
+    } else {
+      float x = r.src[(int64_t)row * r.d + col];
+      if (row == col) x += v;
+      r.dst[(int64_t)row * r.d + col] = x;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// plans
+// ------------------------------------------------------------------------------------------
+struct Plan {
+  std::vector<sso_tile_task> tasks;
+  std::vector<DiagRec> diags;
+  std::vector<CopyRec> copies;
+  std::vector<MatRec> mats;
+  std::vector<sso_phase> inv_phases, std_phases, run_phases;  // kron: inv/std; others: run
+  // device tables
+  sso_tile_task* d_tasks = nullptr;
+  DiagRec* d_diags = nullptr;
+  CopyRec* d_copies = nullptr;
+  MatRec* d_mats = nullptr;
+  float* d_traces = nullptr;
+  float* d_shift = nullptr;
+  int first_scaled_task = -1, n_scaled_tasks = 0;  // sample plan: tasks whose alpha is std_scale
+  bool host_only = false;
+};
+
+static std::mutex g_mu;
+static std::map<int64_t, Plan*> g_plans;
+static int64_t g_next = 1;
+
+static int64_t register_plan(Plan* p) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_plans[g_next] = p;
+  return g_next++;
+}
+static Plan* find_plan(int64_t h) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_plans.find(h);
+  return it == g_plans.end() ? nullptr : it->second;
+}
+
+static size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+struct Builder {
+  Plan& p;
+  std::vector<sso_phase>* phases;
+  explicit Builder(Plan& plan, std::vector<sso_phase>* ph) : p(plan), phases(ph) {}
+  int task_begin() const { return (int)p.tasks.size(); }
+  void gemm(const float* A, int lda, bool ta, const float* B, int ldb, bool tb, float* C, int ldc,
+            int m, int n, int k, float alpha, float beta, float* C2 = nullptr, int ldc2 = 0) {
+    sso_tile_task t;
+    t.A = A; t.B = B; t.C = C; t.C2 = C2;
+    t.lda = lda; t.ldb = ldb; t.ldc = ldc; t.ldc2 = ldc2;
+    t.m = m; t.n = n; t.k = k;
+    t.flags = (ta ? 1u : 0u) | (tb ? 2u : 0u);
+    t.alpha = alpha; t.beta = beta;
+    p.tasks.push_back(t);
+  }
+  void end_phase(int kind, int first, int count) {
+    if (count <= 0) return;
+    sso_phase ph;
+    ph.kind = kind; ph.first = first; ph.count = count; ph.reserved = 0;
+    phases->push_back(ph);
+  }
+};
+
+struct Mat {  // one square matrix being factorised
+  int d, nb;
+  float* W;    // holds M, then L (lower)
+  float* Li;   // receives L^-1 (lower)
+  float* T;    // where the finished inverse goes
+  int mat_index;
+};
+static inline int bsz(const Mat& m, int b) { return std::min(NB, m.d - b * NB); }
+static inline float* blk(float* base, int d, int bi, int bj) { return base + (int64_t)bi * NB * d + (int64_t)bj * NB; }
+
+// Cholesky of every matrix in `ms` (in place in W, block inverses into Li's diagonal blocks).
+static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot) {
+  int max_nb = 0;
+  for (auto& m : ms) max_nb = std::max(max_nb, m.nb);
+  for (int j = 0; j < max_nb; ++j) {
+    int first = (int)b.p.diags.size();
+    for (auto& m : ms)
+      if (j < m.nb) {
+        DiagRec r;
+        r.L = blk(m.W, m.d, j, j); r.Linv = blk(m.Li, m.d, j, j);
+        r.ld_l = m.d; r.ld_inv = m.d; r.size = bsz(m, j); r.mat = m.mat_index; r.row0 = j * NB;
+        r.info_slot = info_slot;
+        b.p.diags.push_back(r);
+      }
+    b.end_phase(2, first, (int)b.p.diags.size() - first);
+    first = b.task_begin();
+    for (auto& m : ms)
+      for (int i = j + 1; i < m.nb; ++i)
+        b.gemm(blk(m.W, m.d, i, j), m.d, false, blk(m.Li, m.d, j, j), m.d, true,
+               blk(m.W, m.d, i, j), m.d, bsz(m, i), NB, NB, 1.f, 0.f);
+    b.end_phase(0, first, b.task_begin() - first);
+    first = b.task_begin();
+    for (auto& m : ms)
+      for (int i = j + 1; i < m.nb; ++i)
+        for (int k = j + 1; k <= i; ++k)
+          b.gemm(blk(m.W, m.d, i, j), m.d, false, blk(m.W, m.d, k, j), m.d, true,
+                 blk(m.W, m.d, i, k), m.d, bsz(m, i), bsz(m, k), NB, -1.f, 1.f);
+    b.end_phase(0, first, b.task_begin() - first);
+  }
+}
+
+// T <- Li^T * Li (symmetric; lower tiles computed and mirrored).  128-wide tiles when they pay.
+static void emit_lauum(Builder& b, const std::vector<Mat>& ms) {
+  for (int pass = 0; pass < 2; ++pass) {
+    const int tile = pass == 0 ? 64 : 128;
+    const int first = b.task_begin();
+    for (auto& m : ms) {
+      const bool big = m.d >= 512;
+      if (big != (pass == 1)) continue;
+      const int nt = (m.d + tile - 1) / tile;
+      for (int i = 0; i < nt; ++i)
+        for (int j = 0; j <= i; ++j) {
+          const int mi = std::min(tile, m.d - i * tile), nj = std::min(tile, m.d - j * tile);
+          float* C = m.T + (int64_t)i * tile * m.d + (int64_t)j * tile;
+          float* C2 = (i == j) ? nullptr : m.T + (int64_t)j * tile * m.d + (int64_t)i * tile;
+          // rows k >= i*tile of Li contribute: A = Li[k, i-cols]^T, B = Li[k, j-cols]
+          const float* A = m.Li + (int64_t)i * tile * m.d + (int64_t)i * tile;
+          const float* B = m.Li + (int64_t)i * tile * m.d + (int64_t)j * tile;
+          b.gemm(A, m.d, true, B, m.d, false, C, m.d, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.d);
+        }
+    }
+    b.end_phase(pass == 0 ? 0 : 1, first, b.task_begin() - first);
+  }
+}
+
+static void emit_copy(Builder& b, const float* src, float* dst, int d, int mat, int mode) {
+  const int rows_per = std::max(1, 16384 / d);
+  for (int r0 = 0; r0 < d; r0 += rows_per) {
+    CopyRec c;
+    c.src = src; c.dst = dst; c.d = d; c.row0 = r0; c.nrows = std::min(rows_per, d - r0);
+    c.mat = mat; c.mode = mode; c.pad = 0;
+    b.p.copies.push_back(c);
+  }
+}
+
+static size_t plan_table_bytes(size_t tasks, size_t diags, size_t copies, size_t mats) {
+  return align_up(tasks * sizeof(sso_tile_task)) + align_up(diags * sizeof(DiagRec)) +
+         align_up(copies * sizeof(CopyRec)) + align_up(mats * sizeof(MatRec)) +
+         2 * align_up(mats * sizeof(float));
+}
+
+static int upload(Plan& p, void* dev_mem, size_t dev_bytes) {
+  const size_t need = plan_table_bytes(p.tasks.size(), p.diags.size(), p.copies.size(), p.mats.size());
+  SSO_CHECK_ARG(dev_mem != nullptr && dev_bytes >= need, "plan device memory too small: need %zu, got %zu",
+                need, dev_bytes);
+  char* q = reinterpret_cast<char*>(dev_mem);
+  p.d_tasks = reinterpret_cast<sso_tile_task*>(q); q += align_up(p.tasks.size() * sizeof(sso_tile_task));
+  p.d_diags = reinterpret_cast<DiagRec*>(q); q += align_up(p.diags.size() * sizeof(DiagRec));
+  p.d_copies = reinterpret_cast<CopyRec*>(q); q += align_up(p.copies.size() * sizeof(CopyRec));
+  p.d_mats = reinterpret_cast<MatRec*>(q); q += align_up(p.mats.size() * sizeof(MatRec));
+  p.d_traces = reinterpret_cast<float*>(q); q += align_up(p.mats.size() * sizeof(float));
+  p.d_shift = reinterpret_cast<float*>(q);
+  if (!p.tasks.empty())
+    SSO_CUDA_OK(cudaMemcpy(p.d_tasks, p.tasks.data(), p.tasks.size() * sizeof(sso_tile_task), cudaMemcpyHostToDevice));
+  if (!p.diags.empty())
+    SSO_CUDA_OK(cudaMemcpy(p.d_diags, p.diags.data(), p.diags.size() * sizeof(DiagRec), cudaMemcpyHostToDevice));
+  if (!p.copies.empty())
+    SSO_CUDA_OK(cudaMemcpy(p.d_copies, p.copies.data(), p.copies.size() * sizeof(CopyRec), cudaMemcpyHostToDevice));
+  if (!p.mats.empty())
+    SSO_CUDA_OK(cudaMemcpy(p.d_mats, p.mats.data(), p.mats.size() * sizeof(MatRec), cudaMemcpyHostToDevice));
+  return 0;
+}
+
+static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* info, cudaStream_t st) {
+  for (const sso_phase& ph : phases) {
+    switch (ph.kind) {
+      case 0: tile_task_kernel<4><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first); break;
+      case 1: tile_task_kernel<8><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first); break;
+      case 2: diag_block_kernel<<<ph.count, 256, 0, st>>>(p.d_diags + ph.first, info); break;
+      case 3: copy_kernel<<<ph.count, 256, 0, st>>>(p.d_copies + ph.first, p.d_shift); break;
+      default: return fail(-1, "bad phase kind %d", ph.kind);
+    }
+    SSO_LAUNCH_OK("plan phase");
+  }
+  return 0;
+}
+
+// task-count estimate without building (used for the *_dev_bytes queries): build and measure.
+static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* const* dst,
+                        float* const* work, float* const* std_out, const int32_t* partner,
+                        const int32_t* role) {
+  Plan* p = new Plan();
+  std::vector<Mat> ms(n);
+  for (int i = 0; i < n; ++i) {
+    MatRec mr;
+    mr.src = src ? src[i] : nullptr; mr.d = (int)dims[i];
+    mr.partner = partner ? partner[i] : -1; mr.role = role ? role[i] : 0; mr.pad = 0;
+    p->mats.push_back(mr);
+    ms[i].d = (int)dims[i]; ms[i].nb = (ms[i].d + NB - 1) / NB;
+    ms[i].W = dst ? dst[i] : nullptr;   // the output buffer first holds M + vI, then L
+    ms[i].Li = work ? work[i] : nullptr;
+    ms[i].T = nullptr;
+    ms[i].mat_index = i;
+  }
+  // ---- inverse: dst <- (src + vI)^-1.
+  // Buffers: W = dst holds M + vI, then its factor L in the lower blocks; Li = work (zeroed
+  // first, because 128-wide tiles of the last stage also read the blocks just above the
+  // diagonal) receives L^-1.  The triangular inverse needs scratch for Y = L21 * Inv11: block
+  // Y(i,j), i > j, is stored transposed in W's block (j,i), which a lower-triangular L never
+  // uses.  Finally Li^T Li overwrites W, i.e. lands in dst.
+  {
+    Builder b(*p, &p->inv_phases);
+    int first = (int)p->copies.size();
+    for (int i = 0; i < n; ++i) {
+      emit_copy(b, src ? src[i] : nullptr, ms[i].W, ms[i].d, i, 0);
+      emit_copy(b, nullptr, ms[i].Li, ms[i].d, -1, 2);
+    }
+    b.end_phase(3, first, (int)p->copies.size() - first);
+    emit_cholesky(b, ms, 0);
+    // triangular inverse by recursive doubling over block ranges [lo,mid) | [mid,hi)
+    int max_nb = 0;
+    for (auto& m : ms) max_nb = std::max(max_nb, m.nb);
+    for (int s = 1; s < max_nb; s *= 2) {
+      first = b.task_begin();
+      for (auto& m : ms)
+        for (int lo = 0; lo + s < m.nb; lo += 2 * s) {
+          const int mid = lo + s, hi = std::min(lo + 2 * s, m.nb);
+          for (int i = mid; i < hi; ++i)
+            for (int j = lo; j < mid; ++j)
+              // Y(i,j)^T = sum_{k in [j,mid)} Inv11(k,j)^T * L(i,k)^T  -> W block (j,i)
+              b.gemm(blk(m.Li, m.d, j, j), m.d, true, blk(m.W, m.d, i, j), m.d, true,
+                     blk(m.W, m.d, j, i), m.d, NB, bsz(m, i), (mid - j) * NB, 1.f, 0.f);
+        }
+      b.end_phase(0, first, b.task_begin() - first);
+      first = b.task_begin();
+      for (auto& m : ms)
+        for (int lo = 0; lo + s < m.nb; lo += 2 * s) {
+          const int mid = lo + s, hi = std::min(lo + 2 * s, m.nb);
+          for (int i = mid; i < hi; ++i)
+            for (int j = lo; j < mid; ++j) {
+              const int kk = std::min((i - mid + 1) * NB, m.d - mid * NB);
+              // Inv21(i,j) = - sum_k Inv22(i,k) * Y(k,j),  Y(k,j) stored at W(j,k) transposed
+              b.gemm(blk(m.Li, m.d, i, mid), m.d, false, blk(m.W, m.d, j, mid), m.d, true,
+                     blk(m.Li, m.d, i, j), m.d, bsz(m, i), NB, kk, -1.f, 0.f);
+            }
+        }
+      b.end_phase(0, first, b.task_begin() - first);
+    }
+    for (auto& m : ms) m.T = m.W;  // L is dead now; the inverse overwrites it
+    emit_lauum(b, ms);
+  }
+  // ---- std: U = chol(dst)^T.  Work copy of dst into `work`, factor there, then write the
+  // transposed factor into std_out.  Block inverses produced on the way land in std_out and
+  // are overwritten by the final transposing copy.
+  if (std_out) {
+    Builder b(*p, &p->std_phases);
+    std::vector<Mat> cs(n);
+    int first = (int)p->copies.size();
+    for (int i = 0; i < n; ++i) {
+      cs[i] = ms[i];
+      cs[i].W = work[i];
+      cs[i].Li = std_out[i];
+      emit_copy(b, dst[i], work[i], ms[i].d, -1, 0);
+    }
+    b.end_phase(3, first, (int)p->copies.size() - first);
+    emit_cholesky(b, cs, 1);
+    first = (int)p->copies.size();
+    for (int i = 0; i < n; ++i) emit_copy(b, work[i], std_out[i], ms[i].d, -1, 1);
+    b.end_phase(3, first, (int)p->copies.size() - first);
+  }
+  return p;
+}
+
+}  // namespace sso
+
+using namespace sso;
+
+extern "C" {
+
+size_t sso_kron_plan_dev_bytes(int n_mats, const int64_t* dims, int with_std) {
+  if (n_mats <= 0 || !dims) return 0;
+  std::vector<float*> fake(n_mats, nullptr);
+  Plan* p = build_kron(n_mats, dims, fake.data(), fake.data(), fake.data(),
+                       with_std ? fake.data() : nullptr, nullptr, nullptr);
+  const size_t bytes = plan_table_bytes(p->tasks.size(), p->diags.size(), p->copies.size(), p->mats.size());
+  delete p;
+  return bytes;
+}
+
+int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src, float* const* dst,
+                             float* const* work, float* const* std_out, const int32_t* partner,
+                             const int32_t* role, void* dev_mem, size_t dev_mem_bytes, int host_only) {
+  SSO_CHECK_ARG(n_mats > 0 && dims && src && dst && work, "kron plan: null argument");
+  for (int i = 0; i < n_mats; ++i) {
+    SSO_CHECK_ARG(dims[i] > 0 && dims[i] <= 32768, "kron plan: bad dim %lld", (long long)dims[i]);
+    SSO_CHECK_ARG(src[i] && dst[i] && work[i], "kron plan: null matrix pointer at %d", i);
+    if (partner && partner[i] >= 0) SSO_CHECK_ARG(partner[i] < n_mats, "kron plan: bad partner");
+  }
+  Plan* p = build_kron(n_mats, dims, src, dst, work, std_out, partner, role);
+  p->host_only = host_only != 0;
+  if (!p->host_only) {
+    const int rc = upload(*p, dev_mem, dev_mem_bytes);
+    if (rc != 0) { delete p; return rc; }
+  }
+  return register_plan(p);
+}
+
+int sso_kron_plan_run(int64_t plan, const float* damp_r_dev, int* info_dev, int do_inverse,
+                      int do_std, void* stream) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr, "unknown plan %lld", (long long)plan);
+  SSO_CHECK_ARG(!p->host_only, "plan %lld was built host-only", (long long)plan);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int n = (int)p->mats.size();
+  if (info_dev) SSO_CUDA_OK(cudaMemsetAsync(info_dev, 0, 2 * n * sizeof(int), st));
+  if (do_inverse) {
+    SSO_CHECK_ARG(damp_r_dev != nullptr, "kron run: damping table is null");
+    trace_kernel<<<n, 256, 0, st>>>(p->d_mats, p->d_traces);
+    SSO_LAUNCH_OK("trace_kernel");
+    shift_kernel<<<ceil_div(n, 128), 128, 0, st>>>(p->d_mats, p->d_traces, damp_r_dev, p->d_shift, n);
+    SSO_LAUNCH_OK("shift_kernel");
+    const int rc = run_phases(*p, p->inv_phases, info_dev, st);
+    if (rc) return rc;
+  }
+  if (do_std) {
+    SSO_CHECK_ARG(!p->std_phases.empty(), "plan %lld has no std program", (long long)plan);
+    const int rc = run_phases(*p, p->std_phases, info_dev, st);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// ---- precondition --------------------------------------------------------------------------
+static Plan* build_precond(int n, const int64_t* dA, const int64_t* dG, float* const* A_inv,
+                           float* const* G_inv, float* const* gw, float* const* gb, float* const* tmp) {
+  Plan* p = new Plan();
+  Builder b(*p, &p->run_phases);
+  constexpr int T = 128;
+  // T = G_inv * [gw | gb]     (columns of the weight block, then the bias column)
+  int first = b.task_begin();
+  for (int l = 0; l < n; ++l) {
+    const int a = (int)dA[l], g = (int)dG[l];
+    const bool bias = gb && gb[l];
+    const int wcols = bias ? a - 1 : a;
+    for (int i = 0; i < g; i += T)
+      for (int j = 0; j < wcols; j += T)
+        b.gemm(G_inv[l] + (int64_t)i * g, g, false, gw[l] + j, wcols, false,
+               tmp[l] + (int64_t)i * a + j, a, std::min(T, g - i), std::min(T, wcols - j), g, 1.f, 0.f);
+    if (bias)
+      for (int i = 0; i < g; i += T)
+        b.gemm(G_inv[l] + (int64_t)i * g, g, false, gb[l], 1, false,
+               tmp[l] + (int64_t)i * a + wcols, a, std::min(T, g - i), 1, g, 1.f, 0.f);
+  }
+  b.end_phase(1, first, b.task_begin() - first);
+  // [gw | gb] = T * A_inv
+  first = b.task_begin();
+  for (int l = 0; l < n; ++l) {
+    const int a = (int)dA[l], g = (int)dG[l];
+    const bool bias = gb && gb[l];
+    const int wcols = bias ? a - 1 : a;
+    for (int i = 0; i < g; i += T)
+      for (int j = 0; j < wcols; j += T)
+        b.gemm(tmp[l] + (int64_t)i * a, a, false, A_inv[l] + j, a, false,
+               gw[l] + (int64_t)i * wcols + j, wcols, std::min(T, g - i), std::min(T, wcols - j), a, 1.f, 0.f);
+    if (bias)
+      for (int i = 0; i < g; i += T)
+        b.gemm(tmp[l] + (int64_t)i * a, a, false, A_inv[l] + wcols, a, false,
+               gb[l] + i, 1, std::min(T, g - i), 1, a, 1.f, 0.f);
+  }
+  b.end_phase(1, first, b.task_begin() - first);
+  return p;
+}
+
+size_t sso_precond_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t* dG) {
+  size_t tasks = 0;
+  for (int l = 0; l < n_layers; ++l) {
+    const size_t ti = (dG[l] + 127) / 128, tj = (dA[l] + 127) / 128 + 1;
+    tasks += 2 * ti * tj;
+  }
+  return plan_table_bytes(tasks, 0, 0, 0);
+}
+
+int64_t sso_precond_plan_create(int n_layers, const int64_t* dA, const int64_t* dG,
+                                float* const* A_inv, float* const* G_inv, float* const* gw,
+                                float* const* gb, float* const* tmp, void* dev_mem,
+                                size_t dev_mem_bytes, int host_only) {
+  SSO_CHECK_ARG(n_layers > 0 && dA && dG && A_inv && G_inv && gw && tmp, "precond plan: null argument");
+  for (int l = 0; l < n_layers; ++l)
+    SSO_CHECK_ARG(dA[l] > 0 && dG[l] > 0 && A_inv[l] && G_inv[l] && gw[l] && tmp[l],
+                  "precond plan: bad layer %d", l);
+  Plan* p = build_precond(n_layers, dA, dG, A_inv, G_inv, gw, gb, tmp);
+  p->host_only = host_only != 0;
+  if (!p->host_only) {
+    const int rc = upload(*p, dev_mem, dev_mem_bytes);
+    if (rc != 0) { delete p; return rc; }
+  }
+  return register_plan(p);
+}
+
+int sso_precond_plan_run(int64_t plan, void* stream) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && !p->host_only, "unknown or host-only plan %lld", (long long)plan);
+  return run_phases(*p, p->run_phases, nullptr, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---- posterior sampling --------------------------------------------------------------------
+static Plan* build_sample(int n, const int64_t* dA, const int64_t* dG, float* const* U_A,
+                          float* const* U_G, float* const* noise, float* const* w, float* const* bvec,
+                          float* const* tmp) {
+  Plan* p = new Plan();
+  Builder b(*p, &p->run_phases);
+  constexpr int T = 128;
+  // tmp = U_G * E : row block i only needs k >= i (upper triangular U_G)
+  int first = b.task_begin();
+  for (int l = 0; l < n; ++l) {
+    const int a = (int)dA[l], g = (int)dG[l];
+    for (int i = 0; i < g; i += T)
+      for (int j = 0; j < a; j += T)
+        b.gemm(U_G[l] + (int64_t)i * g + i, g, false, noise[l] + (int64_t)i * a + j, a, false,
+               tmp[l] + (int64_t)i * a + j, a, std::min(T, g - i), std::min(T, a - j), g - i, 1.f, 0.f);
+  }
+  b.end_phase(1, first, b.task_begin() - first);
+  // [w | b] += s * tmp * U_A : column block j only needs k < j + T (upper triangular U_A)
+  first = b.task_begin();
+  p->first_scaled_task = first;
+  for (int l = 0; l < n; ++l) {
+    const int a = (int)dA[l], g = (int)dG[l];
+    const bool bias = bvec && bvec[l];
+    const int wcols = bias ? a - 1 : a;
+    for (int i = 0; i < g; i += T) {
+      for (int j = 0; j < wcols; j += T)
+        b.gemm(tmp[l] + (int64_t)i * a, a, false, U_A[l] + j, a, false,
+               w[l] + (int64_t)i * wcols + j, wcols, std::min(T, g - i), std::min(T, wcols - j),
+               std::min(a, j + T), 1.f, 1.f);
+      if (bias)
+        b.gemm(tmp[l] + (int64_t)i * a, a, false, U_A[l] + wcols, a, false, bvec[l] + i, 1,
+               std::min(T, g - i), 1, a, 1.f, 1.f);
+    }
+  }
+  p->n_scaled_tasks = b.task_begin() - first;
+  b.end_phase(1, first, b.task_begin() - first);
+  return p;
+}
+
+size_t sso_sample_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t* dG) {
+  return sso_precond_plan_dev_bytes(n_layers, dA, dG);
+}
+
+int64_t sso_sample_plan_create(int n_layers, const int64_t* dA, const int64_t* dG, float* const* U_A,
+                               float* const* U_G, float* const* noise, float* const* w,
+                               float* const* b, float* const* tmp, void* dev_mem,
+                               size_t dev_mem_bytes, int host_only) {
+  SSO_CHECK_ARG(n_layers > 0 && dA && dG && U_A && U_G && noise && w && tmp, "sample plan: null argument");
+  Plan* p = build_sample(n_layers, dA, dG, U_A, U_G, noise, w, b, tmp);
+  p->host_only = host_only != 0;
+  if (!p->host_only) {
+    const int rc = upload(*p, dev_mem, dev_mem_bytes);
+    if (rc != 0) { delete p; return rc; }
+  }
+  return register_plan(p);
+}
+
+__global__ void set_alpha_kernel(sso_tile_task* tasks, int count, float alpha) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) tasks[i].alpha = alpha;
+}
+
+int sso_sample_plan_run(int64_t plan, float std_scale, void* stream) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && !p->host_only, "unknown or host-only plan %lld", (long long)plan);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (p->n_scaled_tasks > 0) {
+    set_alpha_kernel<<<ceil_div(p->n_scaled_tasks, 256), 256, 0, st>>>(p->d_tasks + p->first_scaled_task,
+                                                                     p->n_scaled_tasks, std_scale);
+    SSO_LAUNCH_OK("set_alpha_kernel");
+  }
+  return run_phases(*p, p->run_phases, nullptr, st);
+}
+
+// ---- generic ---------------------------------------------------------------------------------
+int sso_plan_destroy(int64_t plan) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_plans.find(plan);
+  if (it == g_plans.end()) return fail(-1, "unknown plan %lld", (long long)plan);
+  delete it->second;
+  g_plans.erase(it);
+  return 0;
+}
+
+static const std::vector<sso_phase> all_phases(const Plan& p) {
+  std::vector<sso_phase> v(p.inv_phases);
+  v.insert(v.end(), p.std_phases.begin(), p.std_phases.end());
+  v.insert(v.end(), p.run_phases.begin(), p.run_phases.end());
+  return v;
+}
+
+int sso_plan_num_phases(int64_t plan) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr, "unknown plan");
+  return (int)all_phases(*p).size();
+}
+int sso_plan_get_phase(int64_t plan, int index, sso_phase* out) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && out != nullptr, "unknown plan");
+  const auto v = all_phases(*p);
+  SSO_CHECK_ARG(index >= 0 && index < (int)v.size(), "phase index out of range");
+  *out = v[index];
+  return 0;
+}
+int sso_plan_num_tasks(int64_t plan) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr, "unknown plan");
+  return (int)p->tasks.size();
+}
+int sso_plan_copy_tasks(int64_t plan, sso_tile_task* out, int capacity) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && out != nullptr, "unknown plan");
+  const int n = std::min(capacity, (int)p->tasks.size());
+  std::copy(p->tasks.begin(), p->tasks.begin() + n, out);
+  return n;
+}
+
+int sso_plan_num_diag_recs(int64_t plan) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr, "unknown plan");
+  return (int)p->diags.size();
+}
+int sso_plan_copy_diag_recs(int64_t plan, sso_diag_rec* out, int capacity) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && out != nullptr, "unknown plan");
+  const int n = std::min(capacity, (int)p->diags.size());
+  std::copy(p->diags.begin(), p->diags.begin() + n, out);
+  return n;
+}
+int sso_plan_num_copy_recs(int64_t plan) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr, "unknown plan");
+  return (int)p->copies.size();
+}
+int sso_plan_copy_copy_recs(int64_t plan, sso_copy_rec* out, int capacity) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && out != nullptr, "unknown plan");
+  const int n = std::min(capacity, (int)p->copies.size());
+  std::copy(p->copies.begin(), p->copies.begin() + n, out);
+  return n;
+}
+
+int sso_run_tile_tasks(const sso_tile_task* tasks_dev, int count, int tile, void* stream) {
+  SSO_CHECK_ARG(tasks_dev != nullptr && count > 0, "run_tile_tasks: empty");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (tile == 64) tile_task_kernel<4><<<count, 256, 0, st>>>(tasks_dev);
+  else if (tile == 128) tile_task_kernel<8><<<count, 256, 0, st>>>(tasks_dev);
+  else return fail(-1, "tile must be 64 or 128");
+  SSO_LAUNCH_OK("tile_task_kernel");
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,37 @@
+// Launch parameters shared by the factor-construction kernels.
+#pragma once
+#include <stdint.h>
+
+namespace sso {
+
+struct FactorParams {
+  const void* x;
+  const float* weight;  // per-sample, nullable
+  float* out;
+  float* partial;  // workspace [tile][split][128*128]
+  int64_t sn, sc, sh, sw;
+  int64_t ldo;
+  int64_t rows;  // n*ho*wo
+  int n, c, h, w, ho, wo;
+  int kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int d;        // columns incl. the ones column
+  int dcols;    // c*kh*kw
+  int splits;
+  int rows_per_split;
+  float alpha, beta;
+};
+
+struct RowInfo {   // one im2col row (n, ho, wo)
+  int64_t base;    // n*sn
+  int ih0, iw0;    // top-left input coordinate of the patch
+  float wgt;       // sample weight (A operand only)
+  int valid;
+};
+struct ColInfo {   // one im2col column (c, kh, kw) or the ones column
+  int64_t off;     // c*sc
+  int dh, dw;      // kh*dil_h, kw*dil_w
+  int kind;        // 0 data, 1 ones, 2 out of range
+  int pad;
+};
+
+}  // namespace sso

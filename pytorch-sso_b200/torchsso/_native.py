@@ -1,0 +1,374 @@
+"""ctypes binding of libsso_b200.so (the C ABI declared in include/sso_b200.h).
+
+There is no CPU or pure-torch fallback behind these wrappers: if the shared library is
+missing or a call fails, a RuntimeError is raised.  Build it with
+``python pytorch-sso_b200/build.py`` (needs nvcc; cross-compiles without a GPU).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, 'lib', 'libsso_b200.so')
+
+F32, BF16, F16 = 0, 1, 2
+IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2
+_DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+_lib = None
+_lock = threading.Lock()
+
+c_i64, c_i32, c_f32, c_vp, c_sz = C.c_int64, C.c_int, C.c_float, C.c_void_p, C.c_size_t
+
+
+class TileTask(C.Structure):
+    _fields_ = [('A', c_vp), ('B', c_vp), ('C', c_vp), ('C2', c_vp),
+                ('lda', C.c_int32), ('ldb', C.c_int32), ('ldc', C.c_int32), ('ldc2', C.c_int32),
+                ('m', C.c_int32), ('n', C.c_int32), ('k', C.c_int32), ('flags', C.c_uint32),
+                ('alpha', c_f32), ('beta', c_f32)]
+
+
+class DiagRec(C.Structure):
+    _fields_ = [('L', c_vp), ('Linv', c_vp), ('ld_l', C.c_int32), ('ld_inv', C.c_int32),
+                ('size', C.c_int32), ('mat', C.c_int32), ('row0', C.c_int32), ('info_slot', C.c_int32)]
+
+
+class CopyRec(C.Structure):
+    _fields_ = [('src', c_vp), ('dst', c_vp), ('d', C.c_int32), ('row0', C.c_int32),
+                ('nrows', C.c_int32), ('mat', C.c_int32), ('mode', C.c_int32), ('pad', C.c_int32)]
+
+
+class Phase(C.Structure):
+    _fields_ = [('kind', C.c_int32), ('first', C.c_int32), ('count', C.c_int32), ('reserved', C.c_int32)]
+
+
+TRI_REC_DTYPE = np.dtype([('m', np.uint64), ('packed', np.uint64), ('n', np.int32), ('ld', np.int32),
+                          ('row0', np.int32), ('nrows', np.int32)])
+
+# name -> (restype, argtypes); every symbol include/sso_b200.h declares
+SIGNATURES = {
+    'sso_version': (c_i32, []),
+    'sso_last_error': (C.c_char_p, []),
+    'sso_factor_workspace_bytes': (c_sz, [c_i64, c_i64, c_i32]),
+    'sso_factor_syrk_im2col': (c_i32, [c_vp, c_i32] + [c_i64] * 8 + [c_i32] * 8 +
+                               [c_i32, c_vp, c_f32, c_f32, c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
+    'sso_factor_syrk': (c_i32, [c_vp, c_i32, c_i64, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32, c_f32,
+                                c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
+    'sso_bn_plane_sums': (c_i32, [c_vp, c_vp, c_i32] + [c_i64] * 9 + [c_vp] * 5),
+    'sso_bn_diag_finish': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_f32, c_f32, c_vp, c_vp, c_vp]),
+    'sso_ema_update': (c_i32, [c_vp, c_vp, c_i64, c_f32, c_i32, c_vp]),
+    'sso_axpby': (c_i32, [c_vp, c_vp, c_i64, c_f32, c_f32, c_vp]),
+    'sso_diag_inv_precondition': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_f32, c_i32, c_i32, c_vp]),
+    'sso_tri_pack': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
+    'sso_tri_unpack': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
+    'sso_kron_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_i32]),
+    'sso_kron_plan_create': (c_i64, [c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_i32]),
+    'sso_kron_plan_run': (c_i32, [c_i64, c_vp, c_vp, c_i32, c_i32, c_vp]),
+    'sso_precond_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_vp]),
+    'sso_precond_plan_create': (c_i64, [c_i32] + [c_vp] * 8 + [c_sz, c_i32]),
+    'sso_precond_plan_run': (c_i32, [c_i64, c_vp]),
+    'sso_sample_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_vp]),
+    'sso_sample_plan_create': (c_i64, [c_i32] + [c_vp] * 9 + [c_sz, c_i32]),
+    'sso_sample_plan_run': (c_i32, [c_i64, c_f32, c_vp]),
+    'sso_plan_destroy': (c_i32, [c_i64]),
+    'sso_plan_num_phases': (c_i32, [c_i64]),
+    'sso_plan_get_phase': (c_i32, [c_i64, c_i32, c_vp]),
+    'sso_plan_num_tasks': (c_i32, [c_i64]),
+    'sso_plan_copy_tasks': (c_i32, [c_i64, c_vp, c_i32]),
+    'sso_plan_num_diag_recs': (c_i32, [c_i64]),
+    'sso_plan_copy_diag_recs': (c_i32, [c_i64, c_vp, c_i32]),
+    'sso_plan_num_copy_recs': (c_i32, [c_i64]),
+    'sso_plan_copy_copy_recs': (c_i32, [c_i64, c_vp, c_i32]),
+    'sso_run_tile_tasks': (c_i32, [c_vp, c_i32, c_i32, c_vp]),
+}
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        'libsso_b200.so not found at %s: build it with '
+                        '`python pytorch-sso_b200/build.py` (there is no fallback path)' % LIB_PATH)
+                handle = C.CDLL(LIB_PATH)
+                for name, (res, args) in SIGNATURES.items():
+                    fn = getattr(handle, name)       # AttributeError if a symbol is missing
+                    fn.restype, fn.argtypes = res, args
+                _lib = handle
+    return _lib
+
+
+def _check(rc):
+    if rc < 0:
+        raise RuntimeError('sso_b200: %s (code %d)' % (lib().sso_last_error().decode(), rc))
+    return rc
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError('%s must live on a CUDA device: the K-FAC kernels have no CPU path' % what)
+
+
+_workspaces = {}
+
+
+def workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+    """Per-device scratch, grown on demand and reused (all launches are stream ordered)."""
+    if nbytes == 0:
+        return None
+    key = (device.type, device.index)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError('unsupported dtype %s (fp32, bf16, fp16 only)' % t.dtype)
+
+
+def factor_im2col(x: torch.Tensor, kernel_size, stride, padding, dilation, append_ones: bool,
+                  sample_weight: Optional[torch.Tensor], alpha: float, beta: float,
+                  out: torch.Tensor, impl: int = IMPL_AUTO):
+    """out <- alpha * sum_r w u_r u_r^T + beta * out for the im2col rows u_r of x [n,c,h,w]."""
+    _require_cuda(x, 'factor input')
+    n, c, h, w = x.shape
+    kh, kw = kernel_size
+    ho = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+    wo = (w + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+    d = c * kh * kw + (1 if append_ones else 0)
+    assert out.shape == (d, d) and out.dtype == torch.float32 and out.stride(1) == 1, (out.shape, d)
+    rows = n * ho * wo
+    L = lib()
+    ws = workspace(x.device, L.sso_factor_workspace_bytes(rows, d, impl))
+    sn, sc, sh, sw = x.stride()
+    _check(L.sso_factor_syrk_im2col(
+        x.data_ptr(), _dtype_code(x), n, c, h, w, sn, sc, sh, sw, kh, kw, stride[0], stride[1],
+        padding[0], padding[1], dilation[0], dilation[1], int(append_ones), _ptr(sample_weight),
+        alpha, beta, out.data_ptr(), out.stride(0), _ptr(ws), 0 if ws is None else ws.numel(),
+        impl, _stream()))
+
+
+def factor_rows(x: torch.Tensor, append_ones: bool, row_weight: Optional[torch.Tensor],
+                alpha: float, beta: float, out: torch.Tensor, impl: int = IMPL_AUTO):
+    """out <- alpha * [x 1]^T diag(w) [x 1] + beta * out for a 2-D x [rows, cols]."""
+    _require_cuda(x, 'factor input')
+    rows, cols = x.shape
+    d = cols + (1 if append_ones else 0)
+    assert out.shape == (d, d) and out.dtype == torch.float32 and out.stride(1) == 1
+    L = lib()
+    ws = workspace(x.device, L.sso_factor_workspace_bytes(rows, d, impl))
+    _check(L.sso_factor_syrk(
+        x.data_ptr(), _dtype_code(x), rows, cols, x.stride(0), x.stride(1), int(append_ones),
+        _ptr(row_weight), alpha, beta, out.data_ptr(), out.stride(0), _ptr(ws),
+        0 if ws is None else ws.numel(), impl, _stream()))
+
+
+def _plane_strides(t: torch.Tensor):
+    """(n, c, hw) element strides of a [n,c] or [n,c,h,w] tensor whose (h,w) plane is
+    addressable with one stride; returns None if it is not."""
+    if t.dim() == 2:
+        return t.stride(0), t.stride(1), 0
+    n, c, h, w = t.shape
+    sn, sc, sh, sw = t.stride()
+    if h == 1 or sh == w * sw:
+        return sn, sc, sw
+    return None
+
+
+def bn_plane_sums(y: Optional[torch.Tensor], g: Optional[torch.Tensor], scale, shift,
+                  sx: Optional[torch.Tensor], sg: Optional[torch.Tensor]):
+    ref = y if y is not None else g
+    _require_cuda(ref, 'batch-norm tensor')
+    n, c = ref.shape[0], ref.shape[1]
+    hw = ref.numel() // (n * c)
+    sy = (0, 0, 0)
+    if y is not None:
+        sy = _plane_strides(y)
+        if sy is None:
+            y = y.contiguous()
+            sy = _plane_strides(y)
+    sgs = (0, 0, 0)
+    if g is not None:
+        sgs = _plane_strides(g)
+        if sgs is None:
+            g = g.contiguous()
+            sgs = _plane_strides(g)
+    _check(lib().sso_bn_plane_sums(_ptr(y), _ptr(g), _dtype_code(ref), n, c, hw, *sy, *sgs,
+                                   _ptr(scale), _ptr(shift), _ptr(sx), _ptr(sg), _stream()))
+
+
+def bn_diag_finish(sx, sg, sample_weight, n, c, alpha, beta, w_out, b_out):
+    _check(lib().sso_bn_diag_finish(sx.data_ptr(), sg.data_ptr(), _ptr(sample_weight), n, c, alpha,
+                                    beta, w_out.data_ptr(), _ptr(b_out), _stream()))
+
+
+def ema_update(data: torch.Tensor, ema: torch.Tensor, beta: float, first: bool):
+    _require_cuda(data, 'curvature data')
+    assert data.is_contiguous() and ema.is_contiguous() and data.numel() == ema.numel()
+    _check(lib().sso_ema_update(data.data_ptr(), ema.data_ptr(), data.numel(), beta, int(first), _stream()))
+
+
+def axpby(src: torch.Tensor, dst: torch.Tensor, a: float, b: float):
+    _require_cuda(src, 'tensor')
+    assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
+    assert src.dtype == torch.float32 and dst.dtype == torch.float32
+    _check(lib().sso_axpby(src.data_ptr(), dst.data_ptr(), src.numel(), a, b, _stream()))
+
+
+def diag_inv_precondition(ema, inv, grad, damping: float, use_sqrt: bool, update_inv: bool):
+    _require_cuda(inv, 'diagonal curvature')
+    _check(lib().sso_diag_inv_precondition(_ptr(ema), inv.data_ptr(), _ptr(grad), inv.numel(), damping,
+                                           int(use_sqrt), int(update_inv), _stream()))
+
+
+def tri_records(mats: Sequence[torch.Tensor], packed: torch.Tensor, offsets: Sequence[int],
+                rows_per_rec: int = 0) -> torch.Tensor:
+    """Device table of row runs for sso_tri_pack / sso_tri_unpack."""
+    recs = []
+    for m, off in zip(mats, offsets):
+        n = m.shape[0]
+        step = rows_per_rec or max(1, 16384 // n)
+        for r0 in range(0, n, step):
+            recs.append((m.data_ptr(), packed.data_ptr() + 4 * off, n, m.stride(0), r0, min(step, n - r0)))
+    arr = np.array(recs, dtype=TRI_REC_DTYPE)
+    return torch.from_numpy(arr.view(np.uint8).copy()).to(packed.device)
+
+
+def tri_pack(table: torch.Tensor, scale: float = 1.0):
+    _check(lib().sso_tri_pack(table.data_ptr(), table.numel() // TRI_REC_DTYPE.itemsize, scale, _stream()))
+
+
+def tri_unpack(table: torch.Tensor, scale: float = 1.0):
+    _check(lib().sso_tri_unpack(table.data_ptr(), table.numel() // TRI_REC_DTYPE.itemsize, scale, _stream()))
+
+
+def _i64(vals):
+    return (c_i64 * len(vals))(*[int(v) for v in vals])
+
+
+def _i32(vals):
+    return (C.c_int32 * len(vals))(*[int(v) for v in vals])
+
+
+def _ptrs(tensors):
+    return (c_vp * len(tensors))(*[None if t is None else (t if isinstance(t, int) else t.data_ptr())
+                                   for t in tensors])
+
+
+class Plan:
+    """Owner of one engine plan (handle + the device memory that holds its tables)."""
+
+    def __init__(self, handle: int, dev_mem: Optional[torch.Tensor], keep):
+        if handle <= 0:
+            _check(int(handle))
+        self.handle = handle
+        self._dev_mem = dev_mem
+        self._keep = keep          # tensors whose addresses are baked into the plan
+
+    def __del__(self):
+        try:
+            if self.handle > 0 and _lib is not None:
+                _lib.sso_plan_destroy(self.handle)
+        except Exception:
+            pass
+
+    # introspection (host side)
+    def phases(self):
+        L = lib()
+        out = []
+        for i in range(_check(L.sso_plan_num_phases(self.handle))):
+            ph = Phase()
+            _check(L.sso_plan_get_phase(self.handle, i, C.byref(ph)))
+            out.append((ph.kind, ph.first, ph.count))
+        return out
+
+    def tasks(self):
+        L = lib()
+        n = _check(L.sso_plan_num_tasks(self.handle))
+        arr = (TileTask * max(n, 1))()
+        _check(L.sso_plan_copy_tasks(self.handle, arr, n))
+        return arr, n
+
+    def diag_recs(self):
+        L = lib()
+        n = _check(L.sso_plan_num_diag_recs(self.handle))
+        arr = (DiagRec * max(n, 1))()
+        _check(L.sso_plan_copy_diag_recs(self.handle, arr, n))
+        return arr, n
+
+    def copy_recs(self):
+        L = lib()
+        n = _check(L.sso_plan_num_copy_recs(self.handle))
+        arr = (CopyRec * max(n, 1))()
+        _check(L.sso_plan_copy_copy_recs(self.handle, arr, n))
+        return arr, n
+
+
+def kron_plan(dims, src, dst, work, std, partner, role, device, host_only=False) -> Plan:
+    L = lib()
+    n = len(dims)
+    d = _i64(dims)
+    nbytes = L.sso_kron_plan_dev_bytes(n, d, int(std is not None))
+    mem = None if host_only else torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+    h = L.sso_kron_plan_create(n, d, _ptrs(src), _ptrs(dst), _ptrs(work),
+                               None if std is None else _ptrs(std), _i32(partner), _i32(role),
+                               _ptr(mem), nbytes, int(host_only))
+    return Plan(h, mem, (src, dst, work, std))
+
+
+def kron_plan_run(plan: Plan, damp_r: torch.Tensor, info: Optional[torch.Tensor], do_inverse: bool,
+                  do_std: bool):
+    _check(lib().sso_kron_plan_run(plan.handle, _ptr(damp_r), _ptr(info), int(do_inverse), int(do_std),
+                                   _stream()))
+
+
+def precond_plan(dA, dG, A_inv, G_inv, gw, gb, tmp, device, host_only=False) -> Plan:
+    L = lib()
+    n = len(dA)
+    a, g = _i64(dA), _i64(dG)
+    nbytes = L.sso_precond_plan_dev_bytes(n, a, g)
+    mem = None if host_only else torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+    h = L.sso_precond_plan_create(n, a, g, _ptrs(A_inv), _ptrs(G_inv), _ptrs(gw), _ptrs(gb), _ptrs(tmp),
+                                  _ptr(mem), nbytes, int(host_only))
+    return Plan(h, mem, (A_inv, G_inv, gw, gb, tmp))
+
+
+def precond_plan_run(plan: Plan):
+    _check(lib().sso_precond_plan_run(plan.handle, _stream()))
+
+
+def sample_plan(dA, dG, U_A, U_G, noise, w, b, tmp, device, host_only=False) -> Plan:
+    L = lib()
+    n = len(dA)
+    a, g = _i64(dA), _i64(dG)
+    nbytes = L.sso_sample_plan_dev_bytes(n, a, g)
+    mem = None if host_only else torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+    h = L.sso_sample_plan_create(n, a, g, _ptrs(U_A), _ptrs(U_G), _ptrs(noise), _ptrs(w), _ptrs(b),
+                                 _ptrs(tmp), _ptr(mem), nbytes, int(host_only))
+    return Plan(h, mem, (U_A, U_G, noise, w, b, tmp))
+
+
+def sample_plan_run(plan: Plan, std_scale: float):
+    _check(lib().sso_sample_plan_run(plan.handle, std_scale, _stream()))
