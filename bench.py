@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the K-FAC curvature hot path:  ResNet-50 K-FAC images/sec.
+
+Workload ("resnet50_kfac_b32"): ResNet-50 (bottleneck [3,4,6,3], width 64), K-FAC (Fisher, 1 MC
+sample) on every Conv2d/Linear (Kronecker factors, largest A is 4608^2) and diagonal curvature
+on every BatchNorm2d; synthetic inputs N(0,1) of shape 3x224x224, 32 per GPU, uniform labels;
+bf16 activations (autocast) with fp32 factors; factors every step, inverses every 10 steps.
+One "step" = closure (forward, sampling backward, loss backward, with the factor kernels in the
+hooks) + optimizer step.  N > 1: data parallel, factors reduce-scattered to owner ranks,
+updated parameters all-gathered (launch with torch.distributed.run, one rank per GPU).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]            # this repository's CUDA path
+  python bench.py --impl reference [...]                          # the CPU restatement of the
+        reference's path (oracle/), timed on the host cores on a bounded sample of the workload
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, 'pytorch-sso_b200'))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.nn as nn  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+KRON = {'Linear': 'Kron', 'Conv2d': 'Kron', 'BatchNorm1d': 'Diag', 'BatchNorm2d': 'Diag'}
+CURV_KW = {'ema_decay': 0.95, 'damping': 1e-3}
+INV_INTERVAL = 10
+METRIC = 'ResNet-50 K-FAC images/sec'
+
+
+# ---------------------------------------------------------------------------------------------
+# model: ResNet-50, ImageNet stem, functional relu (no in-place module activations needed)
+# ---------------------------------------------------------------------------------------------
+class Bottleneck(nn.Module):
+    def __init__(self, cin, width, stride, downsample):
+        super().__init__()
+        self.conv1 = nn.Conv2d(cin, width, 1, bias=False)
+        self.bn1 = nn.BatchNorm2d(width)
+        self.conv2 = nn.Conv2d(width, width, 3, stride=stride, padding=1, bias=False)
+        self.bn2 = nn.BatchNorm2d(width)
+        self.conv3 = nn.Conv2d(width, width * 4, 1, bias=False)
+        self.bn3 = nn.BatchNorm2d(width * 4)
+        self.downsample = downsample
+
+    def forward(self, x):
+        idt = x if self.downsample is None else self.downsample(x)
+        out = F.relu(self.bn1(self.conv1(x)))
+        out = F.relu(self.bn2(self.conv2(out)))
+        out = self.bn3(self.conv3(out))
+        return F.relu(out + idt)
+
+
+class ResNet50(nn.Module):
+    def __init__(self, num_classes=1000, layers=(3, 4, 6, 3), width=64):
+        super().__init__()
+        self.num_classes = num_classes
+        self.conv1 = nn.Conv2d(3, width, 7, stride=2, padding=3, bias=False)
+        self.bn1 = nn.BatchNorm2d(width)
+        cin, stages = width, []
+        for i, nblk in enumerate(layers):
+            w = width * 2 ** i
+            for b in range(nblk):
+                stride = 2 if (b == 0 and i > 0) else 1
+                ds = None
+                if b == 0:
+                    ds = nn.Sequential(nn.Conv2d(cin, w * 4, 1, stride=stride, bias=False),
+                                       nn.BatchNorm2d(w * 4))
+                stages.append(Bottleneck(cin, w, stride, ds))
+                cin = w * 4
+        self.blocks = nn.Sequential(*stages)
+        self.fc = nn.Linear(cin, num_classes)
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode='fan_out', nonlinearity='relu')
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.bn1(self.conv1(x))), 3, stride=2, padding=1)
+        x = self.blocks(x)
+        x = F.adaptive_avg_pool2d(x, 1).flatten(1)
+        return self.fc(x)
+
+
+def synthetic_batch(batch, num_classes, seed, device='cpu', pin=False):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((batch, 3, 224, 224), generator=g)
+    y = torch.randint(0, num_classes, (batch,), generator=g)
+    if pin:
+        x, y = x.pin_memory(), y.pin_memory()
+    return x.to(device), y.to(device)
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+         'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(['nvidia-smi', '-i', str(self.index), '--query-gpu=' + self.Q,
+                                      '--format=csv,noheader,nounits'], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([f.strip() for f in out.split(',')])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0, set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+                for nm, v in zip(names, s[2:6]):
+                    if v.lower().startswith('active'):
+                        reasons.add(nm)
+            except Exception:
+                continue
+        mhz.sort()
+        return {'sm_mhz': mhz[len(mhz) // 2] if mhz else None, 'sm_max_mhz': mx or None,
+                'reasons': sorted(reasons), 'samples': len(mhz)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference path on the host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_port_images_per_sec(batch, steps, seed=0):
+    """Times oracle.kfac_step.OracleKFAC (torch CPU ops, all host threads) on ResNet-50 with a
+    reduced batch: `steps` steps without inverse + one step with the inverses, combined as the
+    workload's 1-in-10 inverse schedule.  Returns (images/sec, cores, sample description)."""
+    from oracle.kfac_step import OracleKFAC
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    torch.manual_seed(seed)
+    model = ResNet50()
+    opt = OracleKFAC(model, 'Fisher', ema_decay=CURV_KW['ema_decay'], damping=CURV_KW['damping'], lr=1e-3)
+    x, y = synthetic_batch(batch, 1000, seed)
+    mc = torch.randint(0, 1000, (1, batch), generator=torch.Generator().manual_seed(seed + 1))
+    t0 = time.perf_counter()
+    opt.update_inv = True
+    opt.step(x, y, mc)
+    t_inv = time.perf_counter() - t0
+    opt.update_inv = False
+    ts = []
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        opt.step(x, y, mc)
+        ts.append(time.perf_counter() - t0)
+    t_plain = sorted(ts)[len(ts) // 2]
+    per_step = t_plain + max(0.0, t_inv - t_plain) / INV_INTERVAL
+    sample = ('ResNet-50 K-FAC step at batch %d (full model, all 107 curvature groups): 1 step with '
+              'inverses (%.1f s) + %d without (median %.1f s), combined 1-in-%d'
+              % (batch, t_inv, len(ts), t_plain, INV_INTERVAL))
+    return batch / per_step, cores, sample, per_step
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    val, cores, sample, per_step = cpu_port_images_per_sec(args.cpu_batch, max(1, min(args.steps, 2)))
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'images/sec', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': per_step * 1e3,
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+        'data': 'synthetic',
+        'config': {'workload': 'resnet50_kfac_b32', 'batch_per_gpu': 32, 'inverse_every': INV_INTERVAL,
+                   'note': 'CPU restatement of the reference path (the reference GPU path needs '
+                           'CuPy/ChainerMN, absent here); bounded sample at batch %d' % args.cpu_batch},
+        'cpu_baseline': {'value': val, 'unit': 'images/sec', 'cores': cores, 'kind': 'port', 'sample': sample},
+        'e2e': {'value': val, 'unit': 'images/sec', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def measured_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d.get('hbm_gbs', 6650.0), d.get('bf16_tflops_sustained', 1400.0), 'measured'
+    return 6650.0, 1400.0, 'fallback'
+
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+    import torchsso
+    from torchsso import _native as nat
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    if not torch.cuda.is_available():
+        raise RuntimeError('bench.py needs a CUDA device (use --impl reference for the CPU arm)')
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=dev)
+    nat.lib()
+    torch.backends.cudnn.benchmark = True
+    torch.manual_seed(0)
+    model = ResNet50().to(dev).to(memory_format=torch.channels_last)
+    kw = dict(lr=1e-3)
+    if world > 1:
+        opt = torchsso.optim.DistributedSecondOrderOptimizer(model, 'Fisher', KRON, CURV_KW, **kw)
+    else:
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, CURV_KW, **kw)
+    B = args.batch
+    x_pin, y_pin = synthetic_batch(B, 1000, 1000 * rank, pin=True)
+    x_dev = x_pin.to(dev).contiguous(memory_format=torch.channels_last)
+    y_dev = y_pin.to(dev)
+    state = {'step': 0}
+
+    def one_step(x, y):
+        # Fisher closure with the forward under autocast
+        closure = fisher_closure(torchsso, opt, model, x, y)
+        opt.update_inv = (state['step'] % INV_INTERVAL == 0)
+        loss, _ = opt.step(closure=closure)
+        state['step'] += 1
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(nsteps, e2e):
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = nat.launch_count()
+        ev0.record()
+        last = None
+        for _ in range(nsteps):
+            if e2e:
+                x = x_pin.to(dev, non_blocking=True).contiguous(memory_format=torch.channels_last)
+                y = y_pin.to(dev, non_blocking=True)
+                last = one_step(x, y).item()
+            else:
+                last = one_step(x_dev, y_dev)
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, nat.launch_count() - l0, last
+
+    # warm-up (also builds plans and cuDNN algorithm choices); first step inverts
+    for _ in range(max(args.warmup, 3)):
+        one_step(x_dev, y_dev)
+    # align the inverse schedule so that every timed window of K steps sees K/10 inverses
+    state['step'] = 1
+    nat.FACTOR_TIMING = []
+    with ClockSampler(local_rank) as clocks:
+        ms, launches, last_loss = timed(args.steps, e2e=False)
+    torch.cuda.synchronize()
+    ft = nat.FACTOR_TIMING
+    nat.FACTOR_TIMING = None
+    f_ms = sum(a.elapsed_time(b) for a, b, _, _ in ft)
+    f_flops = sum(f for _, _, f, _ in ft)
+    state['step'] = 1
+    ms_e2e, _, last_e2e = timed(args.steps, e2e=True)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    hbm_peak, tf_peak, peak_src = measured_peaks()
+    ips = world * B * args.steps / (ms / 1e3)
+    ips_e2e = world * B * args.steps / (ms_e2e / 1e3)
+    achieved_tf = f_flops / (f_ms / 1e3) / 1e12 if f_ms > 0 else 0.0
+    line = {
+        'metric': METRIC, 'value': ips, 'unit': 'images/sec', 'n_gpus': world, 'steps': args.steps,
+        'warmup': max(args.warmup, 3), 'ms_per_step': ms / args.steps, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16 activations, f32 factors', 'data': 'synthetic',
+        'config': {'workload': 'resnet50_kfac_b32', 'batch_per_gpu': B, 'global_batch': B * world,
+                   'image': '3x224x224', 'curvature': 'Fisher MC(1): Kron conv/linear + diag BN',
+                   'factors_every': 1, 'inverse_every': INV_INTERVAL,
+                   'parallelism': 'dp%d, factors reduce-scattered to owners' % world if world > 1 else 'single',
+                   'l2_policy': 'per-step inputs (%.0f MB activations + 615 MB factor pools) exceed the 126 MB L2'
+                                % (B * 3 * 224 * 224 * 2 / 1e6),
+                   'final_loss': float(last_loss)},
+        'clocks': clocks.summary(),
+        'e2e': {'value': ips_e2e, 'unit': 'images/sec',
+                'h2d_bytes_per_step': int(x_pin.numel() * 4 + y_pin.numel() * 8), 'd2h_bytes_per_step': 4,
+                'final_loss': float(last_e2e)},
+        'gpu_launches': int(launches),
+        'roofline': {'bound': 'tensor', 'kernel': 'factor construction (all Kron layers, A and G)',
+                     'achieved': achieved_tf, 'peak': tf_peak, 'unit': 'TFLOP/s',
+                     'frac': achieved_tf / tf_peak if tf_peak else None, 'traffic': None,
+                     'peak_source': peak_src + ' (bf16 dense, sustained)',
+                     'launches': len(ft), 'total_ms': f_ms,
+                     'flops_rule': '2*rows*d^2 per factor (what the reference einsum performs)'},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        val, cores, sample, _ = cpu_port_images_per_sec(args.cpu_batch, 1)
+        line['cpu_baseline'] = {'value': val, 'unit': 'images/sec', 'cores': cores, 'kind': 'port',
+                                'sample': sample}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def fisher_closure(torchsso, opt, model, x, y):
+    """torchsso.get_closure_for_fisher with the forward pass under bf16 autocast."""
+    class _AutocastModel:
+        num_classes = getattr(model, 'num_classes', None)
+
+        def __call__(self, inp):
+            with torch.autocast('cuda', dtype=torch.bfloat16):
+                return model(inp).float()
+    return torchsso.get_closure_for_fisher(opt, _AutocastModel(), x, y, approx_type='mc', num_mc=1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--batch', type=int, default=32, help='images per GPU')
+    ap.add_argument('--cpu-batch', type=int, default=4, help='batch of the bounded CPU sample')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == '__main__':
+    main()

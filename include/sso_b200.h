@@ -36,6 +36,8 @@ enum { SSO_IMPL_AUTO = 0, SSO_IMPL_SIMT = 1, SSO_IMPL_TCGEN05 = 2 };
 
 int sso_version(void);
 const char* sso_last_error(void);
+/* kernels launched by this library since it was loaded (bookkeeping for benchmarks) */
+uint64_t sso_launch_count(void);
 
 /* ---------------------------------------------------------------------------------------
  * Kronecker factor construction (symmetric rank-k update with the im2col gather fused in).
@@ -122,7 +124,19 @@ typedef struct {
   int32_t row0, nrows;
 } sso_tri_rec;
 int sso_tri_pack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream);
-int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream);
+/* symmetric != 0: both triangles are written; 0: upper triangle only, zeros below (for the
+ * triangular factors exchanged by the variational optimizer) */
+int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, int symmetric, void* stream);
+
+/* dst[0:count] <- scale * src[0:count] for a device table of flat segments, one launch.
+ * Replaces the per-array device-to-device copies of Packer.pack / unpack for non-square arrays
+ * (torchsso/utils/chainer_communicators/_utility.py:35-57). */
+typedef struct {
+  const float* src;
+  float* dst;
+  int64_t count;
+} sso_seg_rec;
+int sso_copy_segments(const sso_seg_rec* recs_dev, int n_recs, float scale, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Tile-task engine.  All dense algebra after factor construction (pi-damped SPD inverse,

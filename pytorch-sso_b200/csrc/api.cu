@@ -4,6 +4,7 @@
 namespace sso {
 
 thread_local std::string g_last_error;
+unsigned long long g_launches = 0;
 }  // namespace sso
 
 #include "factor_params.cuh"
@@ -22,6 +23,7 @@ extern "C" {
 
 int sso_version(void) { return SSO_VERSION; }
 const char* sso_last_error(void) { return g_last_error.c_str(); }
+uint64_t sso_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
 
 size_t sso_factor_workspace_bytes(int64_t rows, int64_t d, int impl) {
   const size_t a = factor_simt_workspace_bytes(rows, d);

@@ -15,6 +15,8 @@ namespace sso {
 
 // Last error text, per host thread (backward hooks call in from autograd's thread).
 extern thread_local std::string g_last_error;
+// Number of kernels this library has launched (all threads); read with sso_launch_count().
+extern unsigned long long g_launches;
 
 inline int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 inline int fail(int code, const char* fmt, ...) {
@@ -42,6 +44,7 @@ inline int fail(int code, const char* fmt, ...) {
 
 #define SSO_LAUNCH_OK(name)                                                                 \
   do {                                                                                      \
+    __atomic_add_fetch(&::sso::g_launches, 1ull, __ATOMIC_RELAXED);                         \
     cudaError_t e__ = cudaGetLastError();                                                   \
     if (e__ != cudaSuccess)                                                                 \
       return ::sso::fail(-3, "launch of %s failed: %s", name, cudaGetErrorString(e__));     \

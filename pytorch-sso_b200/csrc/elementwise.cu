@@ -197,14 +197,32 @@ __global__ void __launch_bounds__(256) tri_pack_kernel(const sso_tri_rec* __rest
     for (int x = row + threadIdx.x; x < r.n; x += 256) r.packed[base + x] = scale * src[x];
   }
 }
-__global__ void __launch_bounds__(256) tri_unpack_kernel(const sso_tri_rec* __restrict__ recs, float scale) {
+__global__ void __launch_bounds__(256) tri_unpack_kernel(const sso_tri_rec* __restrict__ recs, float scale,
+                                                         int symmetric) {
   const sso_tri_rec r = recs[blockIdx.x];
   for (int row = r.row0; row < r.row0 + r.nrows; ++row) {
     float* dst = r.m + (int64_t)row * r.ld;
     for (int x = threadIdx.x; x < r.n; x += 256) {
       const int lo = min(row, x), hi = max(row, x);
-      dst[x] = scale * r.packed[(int64_t)r.n * lo - (int64_t)lo * (lo + 1) / 2 + hi];
+      const float v = scale * r.packed[(int64_t)r.n * lo - (int64_t)lo * (lo + 1) / 2 + hi];
+      dst[x] = (symmetric || x >= row) ? v : 0.f;
     }
+  }
+}
+
+// scaled copies of many flat segments in one launch (one CTA per record)
+__global__ void __launch_bounds__(256) copy_segments_kernel(const sso_seg_rec* __restrict__ recs, float scale) {
+  const sso_seg_rec r = recs[blockIdx.x];
+  const bool vec = ((reinterpret_cast<uintptr_t>(r.src) | reinterpret_cast<uintptr_t>(r.dst)) & 15) == 0;
+  if (vec) {
+    const int64_t n4 = r.count >> 2;
+    for (int64_t i = threadIdx.x; i < n4; i += 256) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(r.src) + i);
+      reinterpret_cast<float4*>(r.dst)[i] = make_float4(scale * v.x, scale * v.y, scale * v.z, scale * v.w);
+    }
+    for (int64_t i = (n4 << 2) + threadIdx.x; i < r.count; i += 256) r.dst[i] = scale * r.src[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < r.count; i += 256) r.dst[i] = scale * r.src[i];
   }
 }
 
@@ -276,11 +294,19 @@ int sso_tri_pack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* str
   return 0;
 }
 
-int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* stream) {
+int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, int symmetric, void* stream) {
   SSO_CHECK_ARG(recs_dev && n_recs >= 0, "tri_unpack: bad argument");
   if (n_recs == 0) return 0;
-  tri_unpack_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale);
+  tri_unpack_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale, symmetric);
   SSO_LAUNCH_OK("tri_unpack_kernel");
+  return 0;
+}
+
+int sso_copy_segments(const sso_seg_rec* recs_dev, int n_recs, float scale, void* stream) {
+  SSO_CHECK_ARG(recs_dev && n_recs >= 0, "copy_segments: bad argument");
+  if (n_recs == 0) return 0;
+  copy_segments_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale);
+  SSO_LAUNCH_OK("copy_segments_kernel");
   return 0;
 }
 

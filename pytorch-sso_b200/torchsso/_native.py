@@ -55,6 +55,7 @@ TRI_REC_DTYPE = np.dtype([('m', np.uint64), ('packed', np.uint64), ('n', np.int3
 SIGNATURES = {
     'sso_version': (c_i32, []),
     'sso_last_error': (C.c_char_p, []),
+    'sso_launch_count': (C.c_uint64, []),
     'sso_factor_workspace_bytes': (c_sz, [c_i64, c_i64, c_i32]),
     'sso_factor_syrk_im2col': (c_i32, [c_vp, c_i32] + [c_i64] * 8 + [c_i32] * 8 +
                                [c_i32, c_vp, c_f32, c_f32, c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
@@ -66,7 +67,8 @@ SIGNATURES = {
     'sso_axpby': (c_i32, [c_vp, c_vp, c_i64, c_f32, c_f32, c_vp]),
     'sso_diag_inv_precondition': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_f32, c_i32, c_i32, c_vp]),
     'sso_tri_pack': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
-    'sso_tri_unpack': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
+    'sso_tri_unpack': (c_i32, [c_vp, c_i32, c_f32, c_i32, c_vp]),
+    'sso_copy_segments': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
     'sso_kron_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_i32]),
     'sso_kron_plan_create': (c_i64, [c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_i32]),
     'sso_kron_plan_run': (c_i32, [c_i64, c_vp, c_vp, c_i32, c_i32, c_vp]),
@@ -126,6 +128,26 @@ def _require_cuda(t: torch.Tensor, what: str):
         raise RuntimeError('%s must live on a CUDA device: the K-FAC kernels have no CPU path' % what)
 
 
+def launch_count() -> int:
+    return int(lib().sso_launch_count())
+
+
+# Optional per-call timing of the factor kernels: set to a list and every factor call appends
+# (start_event, end_event, flops, bytes); the benchmark reads it after synchronising.
+FACTOR_TIMING = None
+
+
+def _timed_factor(fn, flops, nbytes):
+    if FACTOR_TIMING is None:
+        return fn()
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    fn()
+    b.record()
+    FACTOR_TIMING.append((a, b, flops, nbytes))
+
+
 _workspaces = {}
 
 
@@ -163,11 +185,11 @@ def factor_im2col(x: torch.Tensor, kernel_size, stride, padding, dilation, appen
     L = lib()
     ws = workspace(x.device, L.sso_factor_workspace_bytes(rows, d, impl))
     sn, sc, sh, sw = x.stride()
-    _check(L.sso_factor_syrk_im2col(
+    _timed_factor(lambda: _check(L.sso_factor_syrk_im2col(
         x.data_ptr(), _dtype_code(x), n, c, h, w, sn, sc, sh, sw, kh, kw, stride[0], stride[1],
         padding[0], padding[1], dilation[0], dilation[1], int(append_ones), _ptr(sample_weight),
         alpha, beta, out.data_ptr(), out.stride(0), _ptr(ws), 0 if ws is None else ws.numel(),
-        impl, _stream()))
+        impl, _stream())), 2.0 * rows * d * d, x.numel() * x.element_size() + 4 * d * d)
 
 
 def factor_rows(x: torch.Tensor, append_ones: bool, row_weight: Optional[torch.Tensor],
@@ -179,10 +201,11 @@ def factor_rows(x: torch.Tensor, append_ones: bool, row_weight: Optional[torch.T
     assert out.shape == (d, d) and out.dtype == torch.float32 and out.stride(1) == 1
     L = lib()
     ws = workspace(x.device, L.sso_factor_workspace_bytes(rows, d, impl))
-    _check(L.sso_factor_syrk(
+    _timed_factor(lambda: _check(L.sso_factor_syrk(
         x.data_ptr(), _dtype_code(x), rows, cols, x.stride(0), x.stride(1), int(append_ones),
         _ptr(row_weight), alpha, beta, out.data_ptr(), out.stride(0), _ptr(ws),
-        0 if ws is None else ws.numel(), impl, _stream()))
+        0 if ws is None else ws.numel(), impl, _stream())),
+        2.0 * rows * d * d, x.numel() * x.element_size() + 4 * d * d)
 
 
 def _plane_strides(t: torch.Tensor):
@@ -260,8 +283,29 @@ def tri_pack(table: torch.Tensor, scale: float = 1.0):
     _check(lib().sso_tri_pack(table.data_ptr(), table.numel() // TRI_REC_DTYPE.itemsize, scale, _stream()))
 
 
-def tri_unpack(table: torch.Tensor, scale: float = 1.0):
-    _check(lib().sso_tri_unpack(table.data_ptr(), table.numel() // TRI_REC_DTYPE.itemsize, scale, _stream()))
+def tri_unpack(table: torch.Tensor, scale: float = 1.0, symmetric: bool = True):
+    _check(lib().sso_tri_unpack(table.data_ptr(), table.numel() // TRI_REC_DTYPE.itemsize, scale,
+                                int(symmetric), _stream()))
+
+
+SEG_REC_DTYPE = np.dtype([('src', np.uint64), ('dst', np.uint64), ('count', np.int64)])
+
+
+def seg_records(pairs, device, chunk: int = 1 << 16) -> torch.Tensor:
+    """Device table for sso_copy_segments from (src, dst) pairs of equal-sized flat fp32 tensors."""
+    recs = []
+    for src, dst in pairs:
+        assert src.numel() == dst.numel() and src.is_contiguous() and dst.is_contiguous()
+        assert src.dtype == torch.float32 and dst.dtype == torch.float32
+        n = src.numel()
+        for o in range(0, n, chunk):
+            recs.append((src.data_ptr() + 4 * o, dst.data_ptr() + 4 * o, min(chunk, n - o)))
+    arr = np.array(recs, dtype=SEG_REC_DTYPE)
+    return torch.from_numpy(arr.view(np.uint8).copy()).to(device)
+
+
+def copy_segments(table: torch.Tensor, scale: float = 1.0):
+    _check(lib().sso_copy_segments(table.data_ptr(), table.numel() // SEG_REC_DTYPE.itemsize, scale, _stream()))
 
 
 def _i64(vals):

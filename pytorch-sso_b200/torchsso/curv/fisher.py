@@ -1,0 +1,63 @@
+"""Closure factory for Fisher curvatures (same protocol as
+torchsso/curv/fisher/__init__.py:34-90): forward once, then one extra backward pass per Monte
+Carlo target (or per class for the exact Fisher) with parameter gradients frozen so that only
+the curvature hooks see those passes, then the real backward for the loss gradient."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .layers import Fisher
+
+_APPROX_TYPE_MC = 'mc'
+
+
+def sample_targets(prob: torch.Tensor, num_mc: int) -> torch.Tensor:
+    """[num_mc, n] class indices drawn from the model's predictive distribution.
+    A module-level function so that a parity harness can substitute a deterministic draw."""
+    return torch.distributions.Categorical(prob).sample((num_mc,))
+
+
+def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num_mc=1):
+
+    def set_sampling(on: bool):
+        for group in optimizer.param_groups:
+            curv = group['curv']
+            if on:
+                curv.turn_on_backward()
+            else:
+                curv.turn_off_backward()
+            for param in group['params']:
+                param.requires_grad = not on
+
+    def closure():
+        for group in optimizer.param_groups:
+            assert isinstance(group['curv'], Fisher), f"Invalid Curvature type: {type(group['curv'])}."
+        if approx_type is not None and approx_type != _APPROX_TYPE_MC:
+            raise ValueError('Invalid approx type: {}'.format(approx_type))
+
+        optimizer.zero_grad()
+        output = model(data)
+        prob = F.softmax(output, dim=1)
+
+        set_sampling(True)
+        if approx_type == _APPROX_TYPE_MC:
+            mc_targets = sample_targets(prob.detach(), num_mc)
+            weight = torch.full_like(prob[:, 0], 1.0 / num_mc).detach()
+            for group in optimizer.param_groups:
+                group['curv'].prob = weight
+            for i in range(num_mc):
+                F.cross_entropy(output, mc_targets[i]).backward(retain_graph=True)
+        else:
+            for i in range(model.num_classes):
+                weight = prob[:, i].detach().float().contiguous()
+                for group in optimizer.param_groups:
+                    group['curv'].prob = weight
+                F.cross_entropy(output, torch.full_like(target, i)).backward(retain_graph=True)
+        set_sampling(False)
+
+        loss = F.cross_entropy(output, target)
+        loss.backward()
+        return loss, output
+
+    return closure

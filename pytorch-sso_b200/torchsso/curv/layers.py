@@ -1,0 +1,316 @@
+"""Curvature classes per layer type, resolved by name (``shape + type + module class``) exactly
+as torchsso/optim/secondorder.py:148-156 does: Kron{Cov,Fisher}{Linear,Conv2d},
+Diag{Cov,Fisher}{Linear,Conv2d}, DiagCovBatchNorm{1d,2d}, DiagFisherBatchNorm2d and the full
+Cov* placeholders.
+
+Hot classes (Kron Linear/Conv2d, Diag BatchNorm) run on libsso_b200 kernels.  The diagonal
+Linear/Conv2d curvatures (per-sample squared gradients, torchsso/curv/cov/linear.py:28-45,
+torchsso/curv/cov/conv.py:15-42) are outside the accelerated path and are computed with plain
+torch ops on the device.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native as nat
+from ..utils.accumulator import TensorAccumulator
+from .curvature import Curvature, DiagCurvature, KronCurvature
+
+
+class Fisher(object):
+    """Mixin for Fisher curvatures: the closure built by get_closure_for_fisher runs extra
+    backward passes ("sampling passes", do_backward True) weighted by ``prob`` and then the real
+    backward (do_backward False), which finalises the accumulated curvature
+    (torchsso/curv/fisher/__init__.py:7-31)."""
+
+    def __init__(self):
+        self.prob = None
+        self._do_backward = True
+        self._acc_cov = TensorAccumulator()
+
+    @property
+    def do_backward(self):
+        return self._do_backward
+
+    def turn_on_backward(self):
+        self._do_backward = True
+
+    def turn_off_backward(self):
+        self._do_backward = False
+
+    def accumulate_cov(self, cov):
+        self._acc_cov.update(cov)
+
+    def finalize(self):
+        return self._acc_cov.get()
+
+    def update_as_presoftmax(self, prob):
+        raise NotImplementedError('This method supports only torchsso.KronFisherLinear.')
+
+
+def _weights(curv, n, device):
+    """Per-sample weights of the current sampling pass as an fp32 device vector (or None)."""
+    if not isinstance(curv, Fisher):
+        return None
+    assert curv.prob is not None
+    w = curv.prob.detach().reshape(n)
+    if w.dtype != torch.float32 or not w.is_contiguous():
+        w = w.float().contiguous()
+    return w
+
+
+# ---------------------------------------------------------------------------------------------
+# Kronecker-factored
+# ---------------------------------------------------------------------------------------------
+class _KronFactors(KronCurvature):
+    """Shared driver: A in the forward hook, G (optionally prob-weighted and accumulated over
+    sampling passes) in the backward hook, both by the fused factor kernel."""
+
+    def _factor_A(self, x, out):
+        raise NotImplementedError
+
+    def _factor_G(self, g, weight, alpha_scale, beta, out):
+        raise NotImplementedError
+
+    def update_in_forward(self, x):
+        self._factor_A(x, self._views('data')[0])
+
+    def update_in_backward(self, g):
+        fisher = isinstance(self, Fisher)
+        if fisher and not self.do_backward:
+            # real backward: the sampling passes already left  n^2 * sum_pass G_pass  in place
+            self._g_passes = 0
+            self._have.add('data')
+            return
+        n = g.shape[0]
+        beta = 1.0 if (fisher and self._g_passes > 0) else 0.0
+        self._factor_G(g, _weights(self, n, g.device), float(n) * float(n), beta, self._views('data')[1])
+        if fisher:
+            self._g_passes += 1
+        self._have.add('data')
+
+
+class KronCovLinear(_KronFactors):
+    """A = [x 1]^T [x 1] / n, G = g^T g / n (then * n^2).  torchsso/curv/cov/linear.py:48-115."""
+
+    def _get_shape(self):
+        f_out, f_in = self._module.weight.shape
+        da = f_in + 1 if self.bias else f_in
+        return (da, da), (f_out, f_out)
+
+    def _factor_A(self, x, out):
+        x2 = x.reshape(-1, x.shape[-1])
+        nat.factor_rows(x2, self.bias, None, 1.0 / x2.shape[0], 0.0, out)
+
+    def _factor_G(self, g, weight, scale, beta, out):
+        g2 = g.reshape(-1, g.shape[-1])
+        nat.factor_rows(g2, False, weight, scale / g2.shape[0], beta, out)
+
+
+class KronCovConv2d(_KronFactors):
+    """A = U^T U / n over the im2col rows U of the input (never materialised), G = g g^T / (n h w)
+    with g viewed [c_out, n h w] (then * n^2).  torchsso/curv/cov/conv.py:45-124."""
+
+    def _get_shape(self):
+        c_out, c_in, kh, kw = self._module.weight.shape
+        da = c_in * kh * kw + (1 if self.bias else 0)
+        return (da, da), (c_out, c_out)
+
+    def _factor_A(self, x, out):
+        m = self._module
+        if m.groups != 1 or isinstance(m.padding, str):
+            raise NotImplementedError('grouped / string-padded convolutions have no Kronecker curvature here')
+        nat.factor_im2col(x, m.kernel_size, m.stride, m.padding, m.dilation, self.bias, None,
+                          1.0 / x.shape[0], 0.0, out)
+
+    def _factor_G(self, g, weight, scale, beta, out):
+        n, c, h, w = g.shape
+        nat.factor_im2col(g, (1, 1), (1, 1), (0, 0), (1, 1), False, weight, scale / (n * h * w), beta, out)
+
+
+class KronFisherLinear(KronCovLinear, Fisher):
+
+    def __init__(self, *args, **kwargs):
+        KronCovLinear.__init__(self, *args, **kwargs)
+        Fisher.__init__(self)
+
+    def update_as_presoftmax(self, prob):
+        # G = (diag(sum_n p) - p^T p / n) / n   (torchsso/curv/fisher/linear.py:59-63)
+        n = prob.shape[0]
+        G = self._views('data')[1]
+        nat.factor_rows(prob.detach(), False, None, -1.0 / (n * n), 0.0, G)
+        G.diagonal().add_(prob.detach().float().sum(dim=0) / n)
+        self._have.add('data')
+
+
+class KronFisherConv2d(KronCovConv2d, Fisher):
+
+    def __init__(self, *args, **kwargs):
+        KronCovConv2d.__init__(self, *args, **kwargs)
+        Fisher.__init__(self)
+
+
+# ---------------------------------------------------------------------------------------------
+# diagonal BatchNorm (accelerated)
+# ---------------------------------------------------------------------------------------------
+class _DiagBatchNorm(DiagCurvature):
+    """w = mean_n[(sum_hw xhat^2)(sum_hw p g^2)], b = mean_n[sum_hw p g^2], scaled by n^2, where
+    xhat = (out - beta)/gamma is recovered from the layer OUTPUT (torchsso/curv/curvature.py:123-134,
+    torchsso/curv/cov/batchnorm.py:10-49).  The per-(n,c) sums of xhat^2 are taken in the forward
+    hook, so later in-place edits of the output (ReLU, residual add) cannot disturb them."""
+
+    def __init__(self, *args, **kwargs):
+        super(_DiagBatchNorm, self).__init__(*args, **kwargs)
+        self._sx = None
+        self._sg = None
+        self._passes = 0
+
+    def _plane(self, n, c, device):
+        if self._sx is None or self._sx.numel() != n * c:
+            self._sx = torch.empty(n * c, dtype=torch.float32, device=device)
+            self._sg = torch.empty(n * c, dtype=torch.float32, device=device)
+        return self._sx, self._sg
+
+    def update_in_forward(self, out):
+        bn = self._module
+        if bn.weight is None:
+            raise NotImplementedError('affine=False normalisation has no parameters to precondition')
+        sx, _ = self._plane(out.shape[0], out.shape[1], out.device)
+        nat.bn_plane_sums(out, None, bn.weight.detach(), bn.bias.detach(), sx, None)
+
+    def update_in_backward(self, g):
+        fisher = isinstance(self, Fisher)
+        if fisher and not self.do_backward:
+            self._passes = 0
+            self._have.add('data')
+            return
+        n, c = g.shape[0], g.shape[1]
+        sx, sg = self._plane(n, c, g.device)
+        nat.bn_plane_sums(None, g, None, None, None, sg)
+        beta = 1.0 if (fisher and self._passes > 0) else 0.0
+        views = self._views('data')
+        nat.bn_diag_finish(sx, sg, _weights(self, n, g.device), n, c, float(n) * float(n), beta,
+                           views[0], views[1] if len(views) > 1 else None)
+        if fisher:
+            self._passes += 1
+        self._have.add('data')
+
+
+class DiagCovBatchNorm1d(_DiagBatchNorm):
+    pass
+
+
+class DiagCovBatchNorm2d(_DiagBatchNorm):
+    pass
+
+
+class DiagFisherBatchNorm2d(DiagCovBatchNorm2d, Fisher):
+
+    def __init__(self, *args, **kwargs):
+        DiagCovBatchNorm2d.__init__(self, *args, **kwargs)
+        Fisher.__init__(self)
+
+
+# ---------------------------------------------------------------------------------------------
+# diagonal Linear / Conv2d (not accelerated: torch device ops)
+# ---------------------------------------------------------------------------------------------
+class _DiagTorch(DiagCurvature):
+
+    def _store(self, new, scale):
+        fisher = isinstance(self, Fisher)
+        views = self._views('data')
+        first = not (fisher and self._passes > 0)
+        for v, t in zip(views, new):
+            if first:
+                v.copy_(t * scale)
+            else:
+                v.add_(t * scale)
+        if fisher:
+            self._passes += 1
+        self._have.add('data')
+
+    def update_in_backward(self, g):
+        fisher = isinstance(self, Fisher)
+        if not hasattr(self, '_passes'):
+            self._passes = 0
+        if fisher and not self.do_backward:
+            self._passes = 0
+            return
+        n = g.shape[0]
+        p = _weights(self, n, g.device)
+        self._store(self._per_sample_sq(g.float(), p), float(n) * float(n))
+
+
+class DiagCovLinear(_DiagTorch):
+
+    def _per_sample_sq(self, g, p):
+        x = self._module.data_input.float()
+        n = x.shape[0]
+        gg = g * g if p is None else g * g * p.reshape(n, 1)
+        out = [gg.t() @ (x * x) / n]
+        if self.bias:
+            out.append(gg.mean(dim=0))
+        return out
+
+
+class DiagCovConv2d(_DiagTorch):
+
+    def _per_sample_sq(self, g, p):
+        m = self._module
+        x = self._module.data_input.float()
+        cols = F.unfold(x, m.kernel_size, m.dilation, m.padding, m.stride)   # n, ckk, L
+        n, c_out = g.shape[0], g.shape[1]
+        g2 = g.reshape(n, c_out, -1)
+        per = torch.einsum('bik,bjk->bij', g2, cols)                         # n, c_out, ckk
+        sq = per * per if p is None else per * per * p.reshape(n, 1, 1)
+        out = [sq.mean(dim=0).reshape(m.weight.shape)]
+        if self.bias:
+            gg = g2 * g2 if p is None else g2 * g2 * p.reshape(n, 1, 1)
+            out.append(gg.sum(dim=2).mean(dim=0))
+        return out
+
+
+class DiagFisherLinear(DiagCovLinear, Fisher):
+
+    def __init__(self, *args, **kwargs):
+        DiagCovLinear.__init__(self, *args, **kwargs)
+        Fisher.__init__(self)
+
+
+class DiagFisherConv2d(DiagCovConv2d, Fisher):
+
+    def __init__(self, *args, **kwargs):
+        DiagCovConv2d.__init__(self, *args, **kwargs)
+        Fisher.__init__(self)
+
+
+# ---------------------------------------------------------------------------------------------
+# full-matrix placeholders (the reference ships them without a precondition step)
+# ---------------------------------------------------------------------------------------------
+class _FullPlaceholder(Curvature):
+
+    def update_in_backward(self, grad_output):
+        pass
+
+    def step(self, update_std=False, update_inv=True):
+        pass
+
+    def precondition_grad(self, params):
+        pass
+
+
+class CovLinear(_FullPlaceholder):
+    pass
+
+
+class CovConv2d(_FullPlaceholder):
+    pass
+
+
+class CovBatchNorm1d(_FullPlaceholder):
+    pass
+
+
+class CovBatchNorm2d(_FullPlaceholder):
+    pass

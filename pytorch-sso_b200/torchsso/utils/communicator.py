@@ -1,0 +1,244 @@
+"""Factor / update exchange for data-parallel K-FAC over torch.distributed (NCCL on NVLink).
+
+Replaces the ChainerMN communicator of the reference
+(torchsso/utils/chainer_communicators/pure_nccl_communicator.py:114-309 with the Packer of
+_utility.py:16-104).  Semantics kept: after ``reduce_scatterv_data`` the owner rank of every
+layer holds the WORLD MEAN of that layer's gradients and curvature data (symmetric factors
+travel as packed upper triangles); after ``allgatherv_data`` every rank holds the owners'
+values.  What differs is the mechanism: the reference all-reduces the whole buffer twice
+(every rank receives everything); here the first exchange is a true reduce-scatter over
+equal, padded per-owner segments and the second a true all-gather, so each rank moves
+(N-1)/N of ONE segment set instead of two full buffers, and pack / scale / unpack are one
+kernel launch each over a device-side table.
+
+The class works on "arrays": for every rank a list of ``(tensor, triangular)`` pairs in a
+fixed order, where ``triangular`` means "square matrix, send the upper triangle".
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+Arrays = List[List[Tuple[torch.Tensor, bool]]]
+
+
+def assign_owners(costs: Sequence[float], world: int, mode: str = 'inverse_cost') -> List[List[int]]:
+    """Partition group indices over ranks.
+
+    'contiguous'   : numpy.array_split of the index range (torchsso/optim/secondorder.py:341-346).
+    'inverse_cost' : longest-processing-time greedy on ``costs`` (d_A^3 + d_G^3 per layer), ties
+                     and zero-cost groups going to the rank with the fewest groups; each rank's
+                     list is returned in ascending index order."""
+    n = len(costs)
+    if mode == 'contiguous':
+        return [part.tolist() for part in np.array_split(np.arange(n), world)]
+    if mode != 'inverse_cost':
+        raise ValueError('unknown balance mode: %s' % mode)
+    load = [0.0] * world
+    count = [0] * world
+    parts = [[] for _ in range(world)]
+    for i in sorted(range(n), key=lambda i: (-costs[i], i)):
+        r = min(range(world), key=lambda r: (load[r], count[r], r))
+        parts[r].append(i)
+        load[r] += costs[i]
+        count[r] += 1
+    return [sorted(p) for p in parts]
+
+
+def packed_numel(t: torch.Tensor, triangular: bool) -> int:
+    if triangular:
+        n = t.shape[0]
+        return n * (n + 1) // 2
+    return t.numel()
+
+
+class DevicePacker:
+    """Pack / unpack with the sm_100a kernels (one launch per direction per table)."""
+
+    def __init__(self):
+        self._tables = {}
+
+    def _table(self, arrays, buf, offset, direction):
+        from torchsso import _native as nat
+        key = (direction, buf.data_ptr(), offset, tuple((t.data_ptr(), tri) for t, tri in arrays))
+        ent = self._tables.get(key)
+        if ent is None:
+            flat_pairs, tri_mats, tri_offs, off = [], [], [], offset
+            for t, tri in arrays:
+                k = packed_numel(t, tri)
+                if tri:
+                    tri_mats.append(t)
+                    tri_offs.append(off)
+                else:
+                    assert t.is_contiguous(), 'exchange arrays must be contiguous'
+                    seg = buf[off: off + k]
+                    flat_pairs.append((t.reshape(-1), seg) if direction == 'pack' else (seg, t.reshape(-1)))
+                off += k
+            seg_tab = nat.seg_records(flat_pairs, buf.device) if flat_pairs else None
+            tri_tab = nat.tri_records(tri_mats, buf, tri_offs) if tri_mats else None
+            if len(self._tables) > 64:
+                self._tables.clear()
+            ent = (seg_tab, tri_tab)
+            self._tables[key] = ent
+        return ent
+
+    def pack(self, arrays, buf, offset, scale):
+        from torchsso import _native as nat
+        seg_tab, tri_tab = self._table(arrays, buf, offset, 'pack')
+        if seg_tab is not None:
+            nat.copy_segments(seg_tab, scale)
+        if tri_tab is not None:
+            nat.tri_pack(tri_tab, scale)
+
+    def unpack(self, arrays, buf, offset, symmetric=True):
+        from torchsso import _native as nat
+        seg_tab, tri_tab = self._table(arrays, buf, offset, 'unpack')
+        if seg_tab is not None:
+            nat.copy_segments(seg_tab, 1.0)
+        if tri_tab is not None:
+            nat.tri_unpack(tri_tab, 1.0, symmetric)
+
+
+class KFACCommunicator:
+
+    def __init__(self, group=None, packer=None):
+        if not dist.is_initialized():
+            raise RuntimeError('torch.distributed is not initialised')
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        self.packer = packer if packer is not None else DevicePacker()
+        self.indices = None
+        self._optimizer = None
+        self._bufs = {}
+        self.last_bytes = {'rsv': 0, 'agv': 0}
+
+    # ---- wiring ----------------------------------------------------------------------------
+    def setup(self, optimizer):
+        self._optimizer = optimizer
+
+    def _buffer(self, name, numel, device):
+        b = self._bufs.get(name)
+        if b is None or b.numel() < numel or b.device != device:
+            b = torch.zeros(numel, dtype=torch.float32, device=device)
+            self._bufs[name] = b
+        return b[:numel]
+
+    @staticmethod
+    def segment_sizes(arrays: Arrays):
+        sizes = [sum(packed_numel(t, tri) for t, tri in local) for local in arrays]
+        seg = max(sizes) if sizes else 0
+        seg = (seg + 63) // 64 * 64       # equal, 256-byte aligned segments
+        return sizes, seg
+
+    # ---- the two collectives -----------------------------------------------------------------
+    def reduce_scatterv_arrays(self, arrays: Arrays):
+        """Owner r ends up with the world mean of every array in arrays[r]."""
+        sizes, seg = self.segment_sizes(arrays)
+        if seg == 0:
+            return
+        device = next(t for local in arrays for t, _ in local).device
+        send = self._buffer('rsv_send', seg * self.size, device)
+        recv = self._buffer('rsv_recv', seg, device)
+        for r, local in enumerate(arrays):
+            if local:
+                self.packer.pack(local, send, r * seg, 1.0 / self.size)
+        if self.size > 1:
+            self._reduce_scatter(recv, send, seg)
+        else:
+            recv = send[:seg]
+        if arrays[self.rank]:
+            self.packer.unpack(arrays[self.rank], recv, 0, True)
+        self.last_bytes['rsv'] = 4 * seg * self.size
+
+    def allgatherv_arrays(self, arrays: Arrays, symmetric=True):
+        """Every rank ends up with rank r's values of every array in arrays[r]."""
+        sizes, seg = self.segment_sizes(arrays)
+        if seg == 0:
+            return
+        device = next(t for local in arrays for t, _ in local).device
+        send = self._buffer('agv_send', seg, device)
+        recv = self._buffer('agv_recv', seg * self.size, device)
+        if arrays[self.rank]:
+            self.packer.pack(arrays[self.rank], send, 0, 1.0)
+        if self.size > 1:
+            self._all_gather(recv, send, seg)
+        else:
+            recv = send
+        for r, local in enumerate(arrays):
+            if local and r != self.rank:
+                self.packer.unpack(local, recv, r * seg, symmetric)
+        self.last_bytes['agv'] = 4 * seg * self.size
+
+    def _reduce_scatter(self, recv, send, seg):
+        backend = dist.get_backend(self.group)
+        if backend == 'nccl':
+            dist.reduce_scatter_tensor(recv, send, op=dist.ReduceOp.SUM, group=self.group)
+        else:   # gloo has no reduce-scatter: reduce everything, keep the own segment
+            dist.all_reduce(send, op=dist.ReduceOp.SUM, group=self.group)
+            recv.copy_(send[self.rank * seg:(self.rank + 1) * seg])
+
+    def _all_gather(self, recv, send, seg):
+        backend = dist.get_backend(self.group)
+        if backend == 'nccl':
+            dist.all_gather_into_tensor(recv, send, group=self.group)
+        else:
+            parts = [recv[r * seg:(r + 1) * seg] for r in range(self.size)]
+            dist.all_gather(parts, send, group=self.group)
+
+    # ---- optimizer-facing API (names of the reference communicator) ------------------------------
+    def extract(self, param_groups, extractors) -> Arrays:
+        """Arrays per owner rank: for every owned group, in order, what each extractor names:
+        'grad' (flat-pool gradient views), 'param.data', 'mean.data', 'curv.data', 'curv.std'."""
+        opt = self._optimizer
+        arrays = []
+        for local_indices in self.indices:
+            local = []
+            for i in local_indices:
+                group = param_groups[i]
+                for ex in extractors:
+                    if ex == 'grad':
+                        local += [(opt._grad_view[p], False) for p in group['params']]
+                    elif ex == 'param.data':
+                        local += [(p.data, False) for p in group['params']]
+                    elif ex == 'mean.data':
+                        local += [(m.data, False) for m in group['mean']]
+                    elif ex in ('curv.data', 'curv.std'):
+                        curv = group['curv']
+                        if curv is None:
+                            continue
+                        role = ex.split('.')[1]
+                        if role == 'std' and group.get('std_scale', 0) <= 0:
+                            continue
+                        for x in curv._views(role):
+                            tri = x.dim() == 2 and x.shape[0] == x.shape[1]
+                            local.append((x, tri))
+                    else:
+                        raise ValueError('unknown extractor %r' % (ex,))
+            arrays.append(local)
+        return arrays
+
+    def reduce_scatterv_data(self, param_groups, extractors):
+        self.reduce_scatterv_arrays(self.extract(param_groups, extractors))
+        # the owner now holds averaged curvature data for its groups
+        for i in self.indices[self.rank]:
+            curv = param_groups[i]['curv']
+            if curv is not None:
+                curv._have.add('data')
+
+    def allgatherv_data(self, param_groups, extractors):
+        has_std = 'curv.std' in extractors
+        self.allgatherv_arrays(self.extract(param_groups, extractors), symmetric=not has_std)
+        if has_std:
+            for group in param_groups:
+                curv = group['curv']
+                if curv is not None and group.get('std_scale', 0) > 0:
+                    curv._have.add('std')
+
+
+def create_communicator(group=None, packer=None, **unused):
+    """Communicator over the default (or given) process group; one process per GPU, NCCL backend."""
+    return KFACCommunicator(group=group, packer=packer)

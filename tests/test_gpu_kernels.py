@@ -1,0 +1,329 @@
+"""Kernel-level parity on the GPU: every C-ABI entry point against the CPU oracle (evaluated in
+fp64 on the same seeded inputs).  Tolerances: factors 1e-5 relative Frobenius, inverses /
+preconditioned updates / Cholesky factors 1e-4."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import kfac_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+FACTOR_TOL = 1e-5
+INV_TOL = 1e-4
+
+
+@pytest.fixture(scope='module')
+def nat():
+    from torchsso import _native
+    _native.lib()
+    return _native
+
+
+def rel(a, b):
+    a = a.detach().double().cpu()
+    b = b.detach().double().cpu()
+    return ((a - b).norm() / b.norm().clamp_min(1e-300)).item()
+
+
+def dev(t):
+    return t.cuda()
+
+
+# ------------------------------------------------------------------------------------ factors
+@pytest.mark.parametrize('rows,cols,bias', [(128, 784, True), (128, 1000, True), (128, 10, False),
+                                            (32, 2048, True), (300, 147, False), (5000, 64, False),
+                                            (9000, 129, True), (1, 7, True)])
+def test_factor_rows_matches_oracle(nat, rows, cols, bias):
+    x = cases.make_normal((rows, cols), 10 + rows + cols)
+    d = cols + int(bias)
+    out = torch.full((d, d), float('nan'), device='cuda')
+    nat.factor_rows(dev(x), bias, None, 1.0 / rows, 0.0, out, nat.IMPL_SIMT)
+    ref = ko.linear_factor_A(x.double(), bias)
+    assert rel(out, ref) < FACTOR_TOL
+    assert torch.equal(out, out.t())
+
+
+def test_factor_rows_weighted_accumulate_and_strides(nat):
+    rows, cols = 200, 96
+    g = cases.make_normal((rows, cols), 3)
+    p = torch.rand(rows, generator=torch.Generator().manual_seed(5))
+    ref = ko.linear_factor_G(g.double(), p.double())
+    out = torch.zeros((cols, cols), device='cuda')
+    nat.factor_rows(dev(g), False, dev(p), 0.5 / rows, 0.0, out, nat.IMPL_SIMT)
+    nat.factor_rows(dev(g), False, dev(p), 0.5 / rows, 1.0, out, nat.IMPL_SIMT)   # accumulate
+    assert rel(out, ref) < FACTOR_TOL
+    # column-major view of the same matrix (rows contiguous)
+    gt = dev(g).t().contiguous().t()
+    assert gt.stride() == (1, rows)
+    out2 = torch.empty((cols, cols), device='cuda')
+    nat.factor_rows(gt, False, dev(p), 1.0 / rows, 0.0, out2, nat.IMPL_SIMT)
+    assert rel(out2, ref) < FACTOR_TOL
+
+
+def test_factor_rows_bf16_input(nat):
+    x = cases.make_normal((512, 200), 8).bfloat16()
+    out = torch.empty((201, 201), device='cuda')
+    nat.factor_rows(dev(x), True, None, 1.0 / 512, 0.0, out, nat.IMPL_SIMT)
+    assert rel(out, ko.linear_factor_A(x.double(), True)) < FACTOR_TOL
+
+
+CONVS = [
+    # n, c, h, w, k, stride, pad, dil, bias
+    (4, 3, 12, 12, (5, 5), (1, 1), (2, 2), (1, 1), True),
+    (3, 8, 9, 7, (3, 3), (2, 2), (1, 1), (1, 1), False),
+    (2, 5, 10, 10, (3, 2), (1, 2), (0, 1), (2, 1), True),
+    (2, 64, 14, 14, (1, 1), (1, 1), (0, 0), (1, 1), False),
+    (2, 3, 30, 30, (7, 7), (2, 2), (3, 3), (1, 1), False),
+    (8, 16, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1), True),      # 8192 rows: split path
+    (2, 130, 6, 6, (3, 3), (1, 1), (1, 1), (1, 1), False),      # d = 1170: many tiles
+]
+
+
+@pytest.mark.parametrize('cfg', CONVS)
+@pytest.mark.parametrize('channels_last', [False, True])
+def test_factor_conv_A_matches_oracle(nat, cfg, channels_last):
+    n, c, h, w, k, s, p, d, bias = cfg
+    x = cases.make_normal((n, c, h, w), 21 + c + h)
+    ref = ko.conv_factor_A(x.double(), k, s, p, d, bias)
+    xd = dev(x)
+    if channels_last:
+        xd = xd.contiguous(memory_format=torch.channels_last)
+    out = torch.full(tuple(ref.shape), float('nan'), device='cuda')
+    nat.factor_im2col(xd, k, s, p, d, bias, None, 1.0 / n, 0.0, out, nat.IMPL_SIMT)
+    assert rel(out, ref) < FACTOR_TOL
+    assert torch.equal(out, out.t())
+
+
+@pytest.mark.parametrize('channels_last', [False, True])
+def test_factor_conv_G_weighted(nat, channels_last):
+    n, c, h, w = 6, 40, 7, 7
+    g = cases.make_normal((n, c, h, w), 77)
+    p = torch.rand(n, generator=torch.Generator().manual_seed(1))
+    ref = ko.conv_factor_G(g.double(), p.double()) * (n * n)
+    gd = dev(g)
+    if channels_last:
+        gd = gd.contiguous(memory_format=torch.channels_last)
+    out = torch.empty((c, c), device='cuda')
+    nat.factor_im2col(gd, (1, 1), (1, 1), (0, 0), (1, 1), False, dev(p), n * n / (n * h * w), 0.0, out,
+                      nat.IMPL_SIMT)
+    assert rel(out, ref) < FACTOR_TOL
+
+
+def test_factor_conv_bf16_channels_last(nat):
+    n, c, h, w = 4, 32, 14, 14
+    x = cases.make_normal((n, c, h, w), 5).bfloat16()
+    ref = ko.conv_factor_A(x.double(), (3, 3), (1, 1), (1, 1), (1, 1), False)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    out = torch.empty(tuple(ref.shape), device='cuda')
+    nat.factor_im2col(xd, (3, 3), (1, 1), (1, 1), (1, 1), False, None, 1.0 / n, 0.0, out, nat.IMPL_SIMT)
+    assert rel(out, ref) < FACTOR_TOL
+
+
+def test_factor_is_deterministic(nat):
+    x = dev(cases.make_normal((8, 16, 32, 32), 3))
+    a = torch.empty((144, 144), device='cuda')
+    b = torch.empty((144, 144), device='cuda')
+    for o in (a, b):
+        nat.factor_im2col(x, (3, 3), (1, 1), (1, 1), (1, 1), False, None, 1.0 / 8, 0.0, o, nat.IMPL_SIMT)
+    assert torch.equal(a, b)
+
+
+def test_factor_rejects_bad_arguments(nat):
+    x = dev(cases.make_normal((4, 4), 1))
+    out = torch.empty((4, 4), device='cuda')
+    with pytest.raises(RuntimeError):
+        nat._check(nat.lib().sso_factor_syrk(x.data_ptr(), 0, 4, 4, 4, 1, 0, None, 1.0, 0.0,
+                                             out.data_ptr(), 2, None, 0, 1, None))   # ldo < d
+    with pytest.raises(RuntimeError):
+        nat._check(nat.lib().sso_factor_syrk(None, 0, 4, 4, 4, 1, 0, None, 1.0, 0.0,
+                                             out.data_ptr(), 4, None, 0, 1, None))
+
+
+# ------------------------------------------------------------------------------------ batch norm
+@pytest.mark.parametrize('shape', [(6, 5, 4, 4), (4, 70, 7, 7), (8, 33), (3, 64, 1, 1)])
+@pytest.mark.parametrize('channels_last', [False, True])
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_bn_diag_matches_oracle(nat, shape, channels_last, dtype):
+    if channels_last and len(shape) != 4:
+        pytest.skip('2-D input has no channels_last form')
+    y = cases.make_normal(shape, 31).to(dtype)
+    g = cases.make_normal(shape, 32).to(dtype)
+    c = shape[1]
+    gamma = 1.0 + 0.1 * cases.make_normal((c,), 33)
+    beta = 0.1 * cases.make_normal((c,), 34)
+    p = torch.rand(shape[0], generator=torch.Generator().manual_seed(2))
+    xhat = ko.bn_restore_input(y.double(), gamma.double(), beta.double())
+    ref = ko.bn_diag(xhat, g.double(), p.double(), True)
+    n = shape[0]
+    yd, gd = dev(y), dev(g)
+    if channels_last:
+        yd = yd.contiguous(memory_format=torch.channels_last)
+        gd = gd.contiguous(memory_format=torch.channels_last)
+    sx = torch.empty(n * c, device='cuda')
+    sg = torch.empty(n * c, device='cuda')
+    nat.bn_plane_sums(yd, None, dev(gamma), dev(beta), sx, None)
+    nat.bn_plane_sums(None, gd, None, None, None, sg)
+    w_out = torch.empty(c, device='cuda')
+    b_out = torch.empty(c, device='cuda')
+    nat.bn_diag_finish(sx, sg, dev(p), n, c, 1.0, 0.0, w_out, b_out)
+    assert rel(w_out, ref[0]) < 2e-5
+    assert rel(b_out, ref[1]) < 2e-5
+
+
+# ------------------------------------------------------------------------------------ streaming
+def test_ema_axpby_diag(nat):
+    n = 100003
+    data = dev(cases.make_normal((n,), 1))
+    ema = dev(cases.make_normal((n,), 2)).abs_()
+    ref = ko.ema_update(data.cpu(), ema.cpu(), 0.95)
+    nat.ema_update(data, ema, 0.95, False)
+    assert rel(ema, ref) < 1e-6
+    first = torch.empty_like(ema)
+    nat.ema_update(data, first, 0.95, True)
+    assert torch.equal(first, data)
+    # unaligned views
+    a, b = data[1:5001], ema[3:5003].clone()
+    exp = 2.0 * a + 0.5 * b
+    nat.axpby(a, b, 2.0, 0.5)
+    assert rel(b, exp) < 1e-6
+    e = dev(cases.make_normal((999,), 4)).abs_()
+    inv = torch.empty_like(e)
+    grad = dev(cases.make_normal((999,), 5))
+    g0 = grad.clone()
+    nat.diag_inv_precondition(e, inv, grad, 1e-3, False, True)
+    ref_inv = ko.diag_inverse(e.cpu().double(), 1e-3)
+    assert rel(inv, ref_inv) < 1e-6
+    assert rel(grad, g0.cpu().double() * ref_inv) < 1e-6
+
+
+def test_tri_pack_unpack_roundtrip(nat):
+    mats, packed_ref, offs, off = [], [], [], 0
+    for i, n in enumerate([1, 7, 64, 129, 300]):
+        m = cases.make_normal((n, n), 40 + i)
+        m = m + m.t()
+        mats.append(dev(m))
+        packed_ref.append(ko.tri_pack(m))
+        offs.append(off)
+        off += n * (n + 1) // 2
+    buf = torch.full((off,), float('nan'), device='cuda')
+    table = nat.tri_records(mats, buf, offs)
+    nat.tri_pack(table, 0.5)
+    assert torch.equal(buf.cpu(), 0.5 * torch.cat(packed_ref))
+    outs = [torch.full_like(m, float('nan')) for m in mats]
+    nat.tri_unpack(nat.tri_records(outs, buf, offs), 2.0, True)
+    for o, m in zip(outs, mats):
+        assert torch.equal(o, m)
+    up = [torch.full_like(m, float('nan')) for m in mats]
+    nat.tri_unpack(nat.tri_records(up, buf, offs), 2.0, False)
+    for o, m in zip(up, mats):
+        assert torch.equal(o, torch.triu(m))
+
+
+# ------------------------------------------------------------------------------------ engine
+def spd_pair(da, dg, seed):
+    xa = cases.make_normal((max(4 * da, 64), da), seed)
+    xg = cases.make_normal((max(4 * dg, 64), dg), seed + 1) * 0.1
+    return (xa.t() @ xa) / xa.shape[0], (xg.t() @ xg) / xg.shape[0]
+
+
+@pytest.mark.parametrize('dims', [[(10, 28)], [(64, 65), (147, 10)], [(513, 130), (785, 1000)],
+                                  [(1601, 128)]])
+def test_kron_inverse_and_std_match_oracle(nat, dims):
+    damping = 1e-3
+    src, dst, work, std, sizes, partner, role = [], [], [], [], [], [], []
+    refs = []
+    for i, (da, dg) in enumerate(dims):
+        A, G = spd_pair(da, dg, 50 + 2 * i)
+        refs.append((A, G))
+        for which, m in enumerate((A, G)):
+            sizes.append(m.shape[0])
+            src.append(dev(m))
+            dst.append(torch.full_like(src[-1], float('nan')))
+            work.append(torch.full_like(src[-1], float('nan')))
+            std.append(torch.full_like(src[-1], float('nan')))
+            partner.append(2 * i + 1 - which)
+            role.append(which)
+    plan = nat.kron_plan(sizes, src, dst, work, std, partner, role, torch.device('cuda'))
+    damp = torch.full((len(sizes),), math.sqrt(damping), device='cuda')
+    info = torch.zeros(2 * len(sizes), dtype=torch.int32, device='cuda')
+    nat.kron_plan_run(plan, damp, info, True, True)
+    assert int(info.abs().sum()) == 0
+    for i, (A, G) in enumerate(refs):
+        Ai, Gi = ko.kron_damped_inverse(A.double(), G.double(), damping)
+        for got, ref in ((dst[2 * i], Ai), (dst[2 * i + 1], Gi)):
+            assert rel(got, ref) < INV_TOL
+            assert torch.equal(got, got.t())
+        for got, ref in ((std[2 * i], Ai), (std[2 * i + 1], Gi)):
+            assert rel(got, ko.cholesky_upper(ref)) < INV_TOL
+            assert torch.equal(got, torch.triu(got))
+    # second run on the same buffers gives the same bits (no atomics, fixed order)
+    first = [d.clone() for d in dst]
+    nat.kron_plan_run(plan, damp, info, True, False)
+    for a, b in zip(first, dst):
+        assert torch.equal(a, b)
+
+
+def test_kron_inverse_reports_non_spd(nat):
+    d = 70
+    A, _ = spd_pair(d, 8, 3)
+    A[66, 66] = -5.0
+    src = dev(A)
+    dst, work = torch.empty_like(src), torch.empty_like(src)
+    plan = nat.kron_plan([d], [src], [dst], [work], None, [-1], [0], torch.device('cuda'))
+    info = torch.zeros(2, dtype=torch.int32, device='cuda')
+    nat.kron_plan_run(plan, torch.zeros(1, device='cuda'), info, True, False)
+    assert int(info[0]) == 67          # 1-based index of the failing pivot
+    assert int(info[1]) == 0
+
+
+def test_utils_inv_and_cholesky(nat):
+    import torchsso
+    A, _ = spd_pair(200, 8, 9)
+    A = A + 0.1 * torch.eye(200)
+    got = torchsso.utils.inv(dev(A))
+    assert rel(got, ko.spd_inverse(A.double())) < INV_TOL
+    U = torchsso.utils.cholesky(dev(A))
+    assert rel(U, ko.cholesky_upper(A.double())) < INV_TOL
+    with pytest.raises(RuntimeError):
+        torchsso.utils.inv(A)          # CPU tensor: no fallback
+
+
+@pytest.mark.parametrize('da,dg,bias', [(21, 16, True), (785, 1000, True), (1001, 10, True),
+                                        (576, 64, False), (1153, 256, True)])
+def test_precondition_matches_oracle(nat, da, dg, bias):
+    Ai, Gi = spd_pair(da, dg, 60)
+    wc = da - 1 if bias else da
+    gw = cases.make_normal((dg, wc), 61) * 0.1
+    gb = cases.make_normal((dg,), 62) * 0.1 if bias else None
+    rw, rb = ko.kron_precondition(Ai.double(), Gi.double(), gw.double(), None if gb is None else gb.double())
+    dgw, dgb = dev(gw), None if gb is None else dev(gb)
+    tmp = torch.empty(dg * da, device='cuda')
+    plan = nat.precond_plan([da], [dg], [dev(Ai)], [dev(Gi)], [dgw], [dgb], [tmp], torch.device('cuda'))
+    nat.precond_plan_run(plan)
+    assert rel(dgw, rw) < INV_TOL
+    if bias:
+        assert rel(dgb, rb) < INV_TOL
+
+
+@pytest.mark.parametrize('da,dg,bias', [(28, 6, True), (577, 64, True), (300, 129, False)])
+def test_sample_matches_oracle(nat, da, dg, bias):
+    UA = torch.triu(cases.make_normal((da, da), 70))
+    UG = torch.triu(cases.make_normal((dg, dg), 71))
+    wc = da - 1 if bias else da
+    mw = cases.make_normal((dg, wc), 72)
+    mb = cases.make_normal((dg,), 73) if bias else None
+    E = cases.make_normal((dg, da), 74)
+    s = 0.0123
+    rw, rb = ko.kron_sample(mw.double(), None if mb is None else mb.double(), UA.double(), UG.double(),
+                            E.double(), s)
+    w, b = dev(mw), None if mb is None else dev(mb)
+    tmp = torch.empty(dg * da, device='cuda')
+    plan = nat.sample_plan([da], [dg], [dev(UA)], [dev(UG)], [dev(E)], [w], [b], [tmp], torch.device('cuda'))
+    nat.sample_plan_run(plan, s)
+    assert rel(w, rw) < 1e-5
+    if bias:
+        assert rel(b, rb) < 1e-5

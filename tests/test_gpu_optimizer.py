@@ -1,0 +1,212 @@
+"""Step-level parity on the GPU: the torchsso optimizers of this repository, driven exactly like
+the reference's (same constructor arguments, same closure protocol), against golden vectors
+produced by the unmodified reference on CPU (tests/golden/make_golden.py).
+
+Random draws are aligned by substituting the Fisher target draw and ``torch.randn_like`` with
+the same seeded numpy streams the generator used.  Tolerances: factors 1e-5, inverses and
+updates 1e-4 on the first step (growing slowly afterwards, because parameters that differ in
+the 5th digit feed the next step), loss trajectories |dloss| <= 1e-3 * max(1, |loss|)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import cases
+from oracle.kfac_step import inverse_cdf_targets
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(__file__), 'golden')
+KRON = {'Linear': 'Kron', 'Conv2d': 'Kron', 'BatchNorm1d': 'Diag', 'BatchNorm2d': 'Diag'}
+
+
+def load(name):
+    return np.load(os.path.join(GOLD, name + '.npz'))
+
+
+def rel(a, b):
+    a = torch.as_tensor(np.asarray(a.detach().cpu() if torch.is_tensor(a) else a)).double()
+    b = torch.as_tensor(np.asarray(b)).double()
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+@pytest.fixture
+def torchsso_mod():
+    import torchsso
+    return torchsso
+
+
+def patch_targets(monkeypatch, torchsso, state):
+    def fake(prob, num_mc):
+        return inverse_cdf_targets(prob.detach().float().cpu(), state['u']).to(prob.device)
+    monkeypatch.setattr(torchsso.curv.fisher, 'sample_targets', fake)
+
+
+def check(gold, tag, opt, f_tol, i_tol, with_std=False):
+    for gi, group in enumerate(opt.param_groups):
+        curv = group['curv']
+        for j, e in enumerate(curv.ema):
+            assert rel(e, gold['%s/g%d/ema%d' % (tag, gi, j)]) < f_tol, (tag, gi, 'ema', j)
+        for j, e in enumerate(curv.inv):
+            assert rel(e, gold['%s/g%d/inv%d' % (tag, gi, j)]) < i_tol, (tag, gi, 'inv', j)
+        if with_std:
+            for j, e in enumerate(curv.std):
+                assert rel(e, gold['%s/g%d/std%d' % (tag, gi, j)]) < i_tol, (tag, gi, 'std', j)
+        for j, p in enumerate(group['params']):
+            assert rel(p, gold['%s/g%d/param%d' % (tag, gi, j)]) < f_tol * 10, (tag, gi, 'param', j)
+            assert rel(p.grad, gold['%s/g%d/grad%d' % (tag, gi, j)]) < i_tol * 3, (tag, gi, 'grad', j)
+
+
+def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch):
+    torchsso = torchsso_mod
+    gold = load('tiny_convnet_fisher')
+    state = {}
+    patch_targets(monkeypatch, torchsso, state)
+    model = cases.make_model('tiny_convnet', seed=1).cuda()
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON,
+                                              {'ema_decay': 0.95, 'damping': 1e-3}, lr=1e-2)
+    for t in range(4):
+        x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100 + t)
+        state['u'] = cases.make_uniform((2, 6), seed=200 + t)
+        opt.update_inv = (t != 2)
+        closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2)
+        loss, _ = opt.step(closure=closure)
+        opt.pool.check_info()
+        g = float(gold['step%d/loss' % t])
+        assert abs(loss.item() - g) <= 1e-3 * max(1.0, abs(g))
+        for gi, group in enumerate(opt.param_groups):
+            for j, d in enumerate(group['curv'].data):
+                assert rel(d, gold['step%d/g%d/data%d' % (t, gi, j)]) < 1e-5 * (1 + 3 * t), (t, gi, j)
+        check(gold, 'step%d' % t, opt, 1e-5 * (1 + 3 * t), 1e-4 * (1 + 3 * t))
+
+
+def test_tiny_convnet_fisher_exact(torchsso_mod):
+    torchsso = torchsso_mod
+    gold = load('tiny_convnet_fisher_exact')
+    model = cases.make_model('tiny_convnet', seed=2).cuda()
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON,
+                                              {'ema_decay': 1.0, 'damping': 1e-3}, lr=1e-2)
+    x, y = cases.make_batch((6, 3, 8, 8), 5, seed=300)
+    closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type=None)
+    loss, _ = opt.step(closure=closure)
+    assert abs(loss.item() - float(gold['step0/loss'])) < 1e-4
+    check(gold, 'step0', opt, 1e-5, 1e-4)
+
+
+def test_small_mlp_cov_momentum_l2_accsteps(torchsso_mod):
+    torchsso = torchsso_mod
+    gold = load('small_mlp_cov')
+    model = cases.make_model('small_mlp', seed=3).cuda()
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON, {'ema_decay': 0.9, 'damping': 1e-2},
+                                              lr=5e-2, momentum=0.9, l2_reg=1e-3, weight_decay=1e-4,
+                                              acc_steps=2)
+    upd = 0
+    for t in range(6):
+        x, y = cases.make_batch((8, 20), 4, seed=400 + t)
+        x, y = x.cuda(), y.cuda()
+
+        def closure():
+            opt.zero_grad()
+            o = model(x)
+            loss = F.cross_entropy(o, y)
+            loss.backward()
+            return loss, o
+        loss, _ = opt.step(closure=closure)
+        assert abs(loss.item() - float(gold['micro%d/loss' % t])) < 1e-4
+        if t % 2 == 1:
+            check(gold, 'step%d' % upd, opt, 1e-5 * (1 + 3 * upd), 1e-4 * (1 + 3 * upd))
+            upd += 1
+
+
+def test_tiny_vgg_vi(torchsso_mod, monkeypatch):
+    torchsso = torchsso_mod
+    gold = load('tiny_vgg_vi')
+    model = cases.make_model('tiny_vgg', seed=4).cuda()
+    state = {'seed': 0, 'count': 0}
+
+    def fake_randn_like(t, **kw):
+        s = state['seed'] * 1000 + state['count']
+        state['count'] += 1
+        return cases.make_normal(tuple(t.shape), s).to(device=t.device, dtype=t.dtype)
+
+    opt = torchsso.optim.VIOptimizer(model, 1000, 'Cov', KRON, {'ema_decay': 0.95, 'damping': 1e-3},
+                                     lr=1e-2, num_mc_samples=2, val_num_mc_samples=2, kl_weighting=1,
+                                     prior_variance=1)
+    monkeypatch.setattr(torch, 'randn_like', fake_randn_like)
+    for t in range(3):
+        x, y = cases.make_batch((8, 3, 8, 8), 6, seed=600 + t)
+        x, y = x.cuda(), y.cuda()
+        state['seed'], state['count'] = 700 + t, 0
+
+        def closure():
+            opt.zero_grad()
+            o = model(x)
+            loss = F.cross_entropy(o, y)
+            loss.backward()
+            return loss, o
+        loss, prob = opt.step(closure=closure)
+        opt.pool.check_info()
+        assert abs(loss.item() - float(gold['step%d/loss' % t])) < 1e-4
+        assert rel(prob, gold['step%d/prob' % t]) < 1e-4
+        check(gold, 'step%d' % t, opt, 2e-5 * (1 + 3 * t), 2e-4 * (1 + 3 * t), with_std=True)
+        for gi, group in enumerate(opt.param_groups):
+            for j, m in enumerate(group['mean']):
+                assert rel(m, gold['step%d/g%d/mean%d' % (t, gi, j)]) < 1e-4
+
+
+def test_mnist_mlp_100_step_trajectory(torchsso_mod, monkeypatch):
+    """784-1000-1000-10 MLP, batch 128, Fisher MC(1), EMA 0.95, damping 1e-3, lr 1e-2, inverse
+    every step, one fixed batch: the loss trajectory must follow the reference's CPU run."""
+    torchsso = torchsso_mod
+    gold = load('mnist_mlp_fisher')['losses']
+    state = {}
+    patch_targets(monkeypatch, torchsso, state)
+    model = cases.make_model('mnist_mlp', seed=0).cuda()
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON,
+                                              {'ema_decay': 0.95, 'damping': 1e-3}, lr=1e-2)
+    x, y = cases.make_batch((128, 1, 28, 28), 10, seed=0)
+    x, y = x.cuda(), y.cuda()
+    losses = []
+    for t in range(100):
+        state['u'] = cases.make_uniform((1, 128), seed=5000 + t)
+        closure = torchsso.get_closure_for_fisher(opt, model, x, y, approx_type='mc', num_mc=1)
+        loss, _ = opt.step(closure=closure)
+        losses.append(loss.item())
+    opt.pool.check_info()
+    worst = max(abs(a - b) / max(1.0, abs(b)) for a, b in zip(losses, gold))
+    assert worst <= 1e-3, (worst, losses[:5], gold[:5])
+
+
+def test_standalone_curvature_objects(torchsso_mod):
+    """Curvature classes are usable without an optimizer (private pool of one layer)."""
+    import torch.nn as nn
+    from oracle import kfac_oracle as ko
+    torchsso = torchsso_mod
+    lin = nn.Linear(12, 7).cuda()
+    curv = torchsso.KronCovLinear(lin, ema_decay=1.0, damping=1e-2)
+    x = cases.make_normal((9, 12), 1).cuda()
+    out = lin(x)
+    out.square().mean().backward()
+    A, G = curv.data
+    assert rel(A, ko.linear_factor_A(x.cpu().double(), True)) < 1e-5
+    curv.step()
+    Ai, Gi = ko.kron_damped_inverse(curv.ema[0].cpu().double(), curv.ema[1].cpu().double(), 1e-2)
+    assert rel(curv.inv[0], Ai) < 1e-4 and rel(curv.inv[1], Gi) < 1e-4
+    gw, gb = lin.weight.grad.clone(), lin.bias.grad.clone()
+    curv.precondition_grad([lin.weight, lin.bias])
+    rw, rb = ko.kron_precondition(Ai, Gi, gw.cpu().double(), gb.cpu().double())
+    assert rel(lin.weight.grad, rw) < 1e-4 and rel(lin.bias.grad, rb) < 1e-4
+
+
+def test_constructor_validation_matches_reference(torchsso_mod):
+    import torch.nn as nn
+    torchsso = torchsso_mod
+    model = nn.Sequential(nn.Linear(4, 3)).cuda()
+    with pytest.raises(ValueError, match='Invalid learning rate'):
+        torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON, {}, lr=-1)
+    with pytest.raises(ValueError, match='Invalid ema_decay'):
+        torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON, {'ema_decay': 2.0})
+    with pytest.raises(AssertionError, match='Failed to lookup Curvature class'):
+        torchsso.optim.SecondOrderOptimizer(model, 'Nope', KRON, {})
