@@ -38,6 +38,9 @@ int sso_version(void);
 const char* sso_last_error(void);
 /* kernels launched by this library since it was loaded (bookkeeping for benchmarks) */
 uint64_t sso_launch_count(void);
+/* process-wide switches: "tc_auto" (0/1: may SSO_IMPL_AUTO choose the tcgen05 factor kernel),
+ * "tc_flush" (stages of tensor-core accumulation between drains into fp32 registers) */
+int sso_configure(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------
  * Kronecker factor construction (symmetric rank-k update with the im2col gather fused in).

@@ -15,6 +15,8 @@ int factor_simt_launch(FactorParams p, int dtype, void* workspace, size_t worksp
 size_t factor_tc_workspace_bytes(int64_t rows, int64_t d);
 bool factor_tc_supported(const FactorParams& p, int dtype);
 int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
+void factor_tc_set_flush(int stages);
+static int g_tc_auto = 1;   // whether SSO_IMPL_AUTO may pick the tcgen05 kernel
 }  // namespace sso
 
 using namespace sso;
@@ -24,6 +26,14 @@ extern "C" {
 int sso_version(void) { return SSO_VERSION; }
 const char* sso_last_error(void) { return g_last_error.c_str(); }
 uint64_t sso_launch_count(void) { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
+int sso_configure(const char* key, int value) {
+  SSO_CHECK_ARG(key != nullptr, "configure: null key");
+  const std::string k(key);
+  if (k == "tc_auto") { g_tc_auto = value != 0; return 0; }
+  if (k == "tc_flush") { factor_tc_set_flush(value); return 0; }
+  return fail(-1, "configure: unknown key %s", key);
+}
 
 size_t sso_factor_workspace_bytes(int64_t rows, int64_t d, int impl) {
   const size_t a = factor_simt_workspace_bytes(rows, d);
@@ -64,7 +74,7 @@ int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64
     SSO_CHECK_ARG(factor_tc_supported(p, dtype), "factor: shape not supported by the tcgen05 path");
     return factor_tc_launch(p, dtype, workspace, workspace_bytes, st);
   }
-  if (impl == SSO_IMPL_AUTO && factor_tc_supported(p, dtype))
+  if (impl == SSO_IMPL_AUTO && g_tc_auto && factor_tc_supported(p, dtype))
     return factor_tc_launch(p, dtype, workspace, workspace_bytes, st);
   return factor_simt_launch(p, dtype, workspace, workspace_bytes, st);
 }

@@ -19,6 +19,10 @@ struct FactorParams {
   int splits;
   int rows_per_split;
   float alpha, beta;
+  // tensor-core path only
+  int* status;      // device word: 0 ok, else the code of the wait that gave up
+  int perm_c;       // > 0: kernel columns are ordered (kh, kw, c) with c < perm_c; 0: natural order
+  int perm_kk;      // kh*kw
 };
 
 struct RowInfo {   // one im2col row (n, ho, wo)

@@ -56,6 +56,7 @@ SIGNATURES = {
     'sso_version': (c_i32, []),
     'sso_last_error': (C.c_char_p, []),
     'sso_launch_count': (C.c_uint64, []),
+    'sso_configure': (c_i32, [C.c_char_p, c_i32]),
     'sso_factor_workspace_bytes': (c_sz, [c_i64, c_i64, c_i32]),
     'sso_factor_syrk_im2col': (c_i32, [c_vp, c_i32] + [c_i64] * 8 + [c_i32] * 8 +
                                [c_i32, c_vp, c_f32, c_f32, c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
@@ -126,6 +127,10 @@ def _stream():
 def _require_cuda(t: torch.Tensor, what: str):
     if not t.is_cuda:
         raise RuntimeError('%s must live on a CUDA device: the K-FAC kernels have no CPU path' % what)
+
+
+def configure(key: str, value: int):
+    _check(lib().sso_configure(key.encode(), int(value)))
 
 
 def launch_count() -> int:

@@ -46,6 +46,7 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
             weight = torch.full_like(prob[:, 0], 1.0 / num_mc).detach()
             for group in optimizer.param_groups:
                 group['curv'].prob = weight
+                group['curv'].prob_scale = 1.0 / num_mc
             for i in range(num_mc):
                 F.cross_entropy(output, mc_targets[i]).backward(retain_graph=True)
         else:
@@ -53,6 +54,7 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
                 weight = prob[:, i].detach().float().contiguous()
                 for group in optimizer.param_groups:
                     group['curv'].prob = weight
+                    group['curv'].prob_scale = None
                 F.cross_entropy(output, torch.full_like(target, i)).backward(retain_graph=True)
         set_sampling(False)
 

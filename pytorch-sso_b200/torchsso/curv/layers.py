@@ -26,6 +26,11 @@ class Fisher(object):
 
     def __init__(self):
         self.prob = None
+        # set together with ``prob`` when every sample has the same weight (Monte Carlo Fisher:
+        # 1/num_mc): the kernels then take the weight as part of their scalar alpha, which keeps
+        # 16-bit inputs on the tensor-core path (per-sample weights would have to be rounded
+        # into the operands)
+        self.prob_scale = None
         self._do_backward = True
         self._acc_cov = TensorAccumulator()
 
@@ -50,14 +55,16 @@ class Fisher(object):
 
 
 def _weights(curv, n, device):
-    """Per-sample weights of the current sampling pass as an fp32 device vector (or None)."""
+    """(per-sample weight vector or None, scalar weight) of the current sampling pass."""
     if not isinstance(curv, Fisher):
-        return None
+        return None, 1.0
+    if curv.prob_scale is not None:
+        return None, float(curv.prob_scale)
     assert curv.prob is not None
     w = curv.prob.detach().reshape(n)
     if w.dtype != torch.float32 or not w.is_contiguous():
         w = w.float().contiguous()
-    return w
+    return w, 1.0
 
 
 # ---------------------------------------------------------------------------------------------
@@ -85,7 +92,8 @@ class _KronFactors(KronCurvature):
             return
         n = g.shape[0]
         beta = 1.0 if (fisher and self._g_passes > 0) else 0.0
-        self._factor_G(g, _weights(self, n, g.device), float(n) * float(n), beta, self._views('data')[1])
+        w, ws = _weights(self, n, g.device)
+        self._factor_G(g, w, ws * float(n) * float(n), beta, self._views('data')[1])
         if fisher:
             self._g_passes += 1
         self._have.add('data')
@@ -190,7 +198,8 @@ class _DiagBatchNorm(DiagCurvature):
         nat.bn_plane_sums(None, g, None, None, None, sg)
         beta = 1.0 if (fisher and self._passes > 0) else 0.0
         views = self._views('data')
-        nat.bn_diag_finish(sx, sg, _weights(self, n, g.device), n, c, float(n) * float(n), beta,
+        w, ws = _weights(self, n, g.device)
+        nat.bn_diag_finish(sx, sg, w, n, c, ws * float(n) * float(n), beta,
                            views[0], views[1] if len(views) > 1 else None)
         if fisher:
             self._passes += 1
@@ -238,8 +247,8 @@ class _DiagTorch(DiagCurvature):
             self._passes = 0
             return
         n = g.shape[0]
-        p = _weights(self, n, g.device)
-        self._store(self._per_sample_sq(g.float(), p), float(n) * float(n))
+        p, ws = _weights(self, n, g.device)
+        self._store(self._per_sample_sq(g.float(), p), ws * float(n) * float(n))
 
 
 class DiagCovLinear(_DiagTorch):

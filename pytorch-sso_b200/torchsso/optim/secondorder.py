@@ -170,26 +170,35 @@ class SecondOrderOptimizer(Optimizer):
         return self.param_groups
 
     def zero_grad(self, set_to_none: bool = False):
-        """Zero the flat gradient buffer and make every ``p.grad`` a view of it (fp32 parameters)."""
+        """Zero the flat gradient buffer.  Parameters that are fp32 and contiguous get ``p.grad``
+        bound to their view of it, so autograd accumulates in place; others (channels_last
+        weights, 16-bit parameters) get ``None`` and are copied in after the backward pass."""
         self._grad_flat.zero_()
         for p, v in self._grad_view.items():
-            if p.dtype == torch.float32:
+            if p.dtype == torch.float32 and p.is_contiguous():
                 if p.grad is not v:
                     p.grad = v
             elif p.grad is not None:
                 p.grad = None
 
     def _harvest_grads(self):
-        """Make sure the flat buffer holds this closure's gradients (closures that reset grads
-        themselves, or non-fp32 parameters, leave them elsewhere)."""
+        """Make sure the flat buffer holds this closure's gradients and that every ``p.grad`` is
+        its view of the buffer (one multi-tensor copy for gradients that live elsewhere)."""
+        dsts, srcs = [], []
         for p, v in self._grad_view.items():
             g = p.grad
             if g is None:
                 v.zero_()
             elif g.data_ptr() != v.data_ptr() or g.dtype != torch.float32:
-                v.copy_(g)
-                if p.dtype == torch.float32:
-                    p.grad = v
+                dsts.append(v)
+                srcs.append(g)
+            if g is not v:
+                p.grad = None
+        if dsts:
+            torch._foreach_copy_(dsts, srcs)
+        for p, v in self._grad_view.items():
+            if p.grad is None:
+                p.grad = v
 
     def _accumulate(self, scale: float):
         if self._grad_acc is None:

@@ -123,6 +123,75 @@ def test_factor_conv_bf16_channels_last(nat):
     assert rel(out, ref) < FACTOR_TOL
 
 
+# tensor-core (tcgen05) path: channels-contiguous inputs, bf16 single pass and fp32 as 3xTF32
+TC_CONVS = [
+    # n, c, h, w, k, stride, pad, dil, bias
+    (2, 8, 6, 6, (3, 3), (1, 1), (1, 1), (1, 1), False),
+    (4, 64, 14, 14, (3, 3), (1, 1), (1, 1), (1, 1), True),
+    (4, 64, 14, 14, (3, 3), (2, 2), (1, 1), (1, 1), False),
+    (3, 16, 9, 11, (5, 3), (1, 2), (2, 0), (1, 2), True),
+    (4, 256, 14, 14, (1, 1), (1, 1), (0, 0), (1, 1), False),
+    (16, 32, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1), True),      # 16384 rows: several splits
+    (2, 136, 6, 6, (3, 3), (1, 1), (1, 1), (1, 1), False),       # d = 1224: 10 x 10 tiles, ragged edge
+]
+
+
+@pytest.mark.parametrize('cfg', TC_CONVS)
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32, torch.float16])
+def test_factor_tcgen05_conv_matches_oracle(nat, cfg, dtype):
+    n, c, h, w, k, s, p, d, bias = cfg
+    x = cases.make_normal((n, c, h, w), 91 + c + h).to(dtype)
+    ref = ko.conv_factor_A(x.double(), k, s, p, d, bias)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    out = torch.full(tuple(ref.shape), float('nan'), device='cuda')
+    nat.factor_im2col(xd, k, s, p, d, bias, None, 1.0 / n, 0.0, out, nat.IMPL_TCGEN05)
+    assert rel(out, ref) < FACTOR_TOL
+    assert torch.equal(out, out.t())
+    # accumulate on top (beta = 1) and compare with the fp32 SIMT kernel doing the same
+    simt = torch.empty_like(out)
+    nat.factor_im2col(xd, k, s, p, d, bias, None, 1.0 / n, 0.0, simt, nat.IMPL_SIMT)
+    nat.factor_im2col(xd, k, s, p, d, bias, None, 1.0 / n, 1.0, out, nat.IMPL_TCGEN05)
+    assert rel(out, 2 * simt) < FACTOR_TOL
+
+
+@pytest.mark.parametrize('rows,cols,bias,dtype', [(128, 784, True, torch.float32), (128, 1000, True, torch.float32),
+                                                  (4096, 256, True, torch.bfloat16), (1000, 2048, True, torch.bfloat16),
+                                                  (100352, 64, False, torch.bfloat16), (32768, 512, False, torch.float32),
+                                                  (77, 8, False, torch.float32)])
+def test_factor_tcgen05_rows_matches_oracle(nat, rows, cols, bias, dtype):
+    x = cases.make_normal((rows, cols), 7 + rows).clamp_min(-0.5).to(dtype)     # positive mean: long sums
+    d = cols + int(bias)
+    out = torch.full((d, d), float('nan'), device='cuda')
+    nat.factor_rows(dev(x), bias, None, 1.0 / rows, 0.0, out, nat.IMPL_TCGEN05)
+    assert rel(out, ko.linear_factor_A(x.double(), bias)) < FACTOR_TOL
+    again = torch.empty_like(out)
+    nat.factor_rows(dev(x), bias, None, 1.0 / rows, 0.0, again, nat.IMPL_TCGEN05)
+    assert torch.equal(out, again)                                                  # deterministic
+
+
+def test_factor_tcgen05_weighted_fp32_and_dispatch(nat):
+    rows, cols = 300, 96
+    g = cases.make_normal((rows, cols), 3)
+    p = torch.rand(rows, generator=torch.Generator().manual_seed(5))
+    ref = ko.linear_factor_G(g.double(), p.double())
+    out = torch.empty((cols, cols), device='cuda')
+    nat.factor_rows(dev(g), False, dev(p), 1.0 / rows, 0.0, out, nat.IMPL_TCGEN05)
+    assert rel(out, ref) < FACTOR_TOL
+    # 16-bit inputs with per-sample weights are not eligible (weights would be rounded into the
+    # operands): asking for the tensor-core kernel explicitly is an error, AUTO falls back
+    with pytest.raises(RuntimeError):
+        nat.factor_rows(dev(g).bfloat16(), False, dev(p), 1.0 / rows, 0.0, out, nat.IMPL_TCGEN05)
+    nat.factor_rows(dev(g).bfloat16(), False, dev(p), 1.0 / rows, 0.0, out, nat.IMPL_AUTO)
+    assert rel(out, ko.linear_factor_G(g.bfloat16().double(), p.double())) < FACTOR_TOL
+    # NCHW input is not channels-contiguous: explicit request fails, AUTO uses the SIMT kernel
+    x = dev(cases.make_normal((2, 8, 6, 6), 4))
+    o = torch.empty((72, 72), device='cuda')
+    with pytest.raises(RuntimeError):
+        nat.factor_im2col(x, (3, 3), (1, 1), (1, 1), (1, 1), False, None, 0.5, 0.0, o, nat.IMPL_TCGEN05)
+    nat.factor_im2col(x, (3, 3), (1, 1), (1, 1), (1, 1), False, None, 0.5, 0.0, o, nat.IMPL_AUTO)
+    assert rel(o, ko.conv_factor_A(x.cpu().double(), (3, 3), (1, 1), (1, 1), (1, 1), False)) < FACTOR_TOL
+
+
 def test_factor_is_deterministic(nat):
     x = dev(cases.make_normal((8, 16, 32, 32), 3))
     a = torch.empty((144, 144), device='cuda')
