@@ -237,9 +237,12 @@ def run_gpu_arm(args):
     else:
         opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, CURV_KW, **kw)
     B = args.batch
-    x_pin, y_pin = synthetic_batch(B, 1000, 1000 * rank, pin=True)
-    x_dev = x_pin.to(dev).contiguous(memory_format=torch.channels_last)
-    y_dev = y_pin.to(dev)
+    # a small pool of different synthetic batches, cycled: fresh data every step keeps the loss
+    # (and with it the curvature) stationary instead of memorising one batch
+    NB = 4
+    pinned = [synthetic_batch(B, 1000, 1000 * rank + i, pin=True) for i in range(NB)]
+    resident = [(xp.to(dev).contiguous(memory_format=torch.channels_last), yp.to(dev)) for xp, yp in pinned]
+    x_pin, y_pin = pinned[0]
     state = {'step': 0}
 
     def one_step(x, y):
@@ -261,13 +264,14 @@ def run_gpu_arm(args):
         l0 = nat.launch_count()
         ev0.record()
         last = None
-        for _ in range(nsteps):
+        for i in range(nsteps):
             if e2e:
-                x = x_pin.to(dev, non_blocking=True).contiguous(memory_format=torch.channels_last)
-                y = y_pin.to(dev, non_blocking=True)
+                xp, yp = pinned[i % NB]
+                x = xp.to(dev, non_blocking=True).contiguous(memory_format=torch.channels_last)
+                y = yp.to(dev, non_blocking=True)
                 last = one_step(x, y).item()
             else:
-                last = one_step(x_dev, y_dev)
+                last = one_step(*resident[i % NB])
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -278,8 +282,8 @@ def run_gpu_arm(args):
         return ms, nat.launch_count() - l0, last
 
     # warm-up (also builds plans and cuDNN algorithm choices); first step inverts
-    for _ in range(max(args.warmup, 3)):
-        one_step(x_dev, y_dev)
+    for i in range(max(args.warmup, 3)):
+        one_step(*resident[i % NB])
     # align the inverse schedule so that every timed window of K steps sees K/10 inverses
     state['step'] = 1
     nat.FACTOR_TIMING = []
