@@ -66,40 +66,49 @@ class DevicePacker:
         key = (direction, buf.data_ptr(), offset, tuple((t.data_ptr(), tri) for t, tri in arrays))
         ent = self._tables.get(key)
         if ent is None:
-            flat_pairs, tri_mats, tri_offs, off = [], [], [], offset
+            flat_pairs, tri_mats, tri_offs, strided, off = [], [], [], ([], []), offset
             for t, tri in arrays:
                 k = packed_numel(t, tri)
                 if tri:
                     tri_mats.append(t)
                     tri_offs.append(off)
-                else:
-                    assert t.is_contiguous(), 'exchange arrays must be contiguous'
+                elif t.is_contiguous() and t.dtype == torch.float32:
                     seg = buf[off: off + k]
                     flat_pairs.append((t.reshape(-1), seg) if direction == 'pack' else (seg, t.reshape(-1)))
+                else:
+                    # e.g. channels_last convolution weights: multi-tensor strided copy
+                    strided[0].append(t)
+                    strided[1].append(buf[off: off + k].view(t.shape))
                 off += k
             seg_tab = nat.seg_records(flat_pairs, buf.device) if flat_pairs else None
             tri_tab = nat.tri_records(tri_mats, buf, tri_offs) if tri_mats else None
             if len(self._tables) > 64:
                 self._tables.clear()
-            ent = (seg_tab, tri_tab)
+            ent = (seg_tab, tri_tab, strided)
             self._tables[key] = ent
         return ent
 
     def pack(self, arrays, buf, offset, scale):
         from torchsso import _native as nat
-        seg_tab, tri_tab = self._table(arrays, buf, offset, 'pack')
+        seg_tab, tri_tab, (tensors, views) = self._table(arrays, buf, offset, 'pack')
         if seg_tab is not None:
             nat.copy_segments(seg_tab, scale)
         if tri_tab is not None:
             nat.tri_pack(tri_tab, scale)
+        if tensors:
+            torch._foreach_copy_(views, tensors)
+            if scale != 1.0:
+                torch._foreach_mul_(views, scale)
 
     def unpack(self, arrays, buf, offset, symmetric=True):
         from torchsso import _native as nat
-        seg_tab, tri_tab = self._table(arrays, buf, offset, 'unpack')
+        seg_tab, tri_tab, (tensors, views) = self._table(arrays, buf, offset, 'unpack')
         if seg_tab is not None:
             nat.copy_segments(seg_tab, 1.0)
         if tri_tab is not None:
             nat.tri_unpack(tri_tab, 1.0, symmetric)
+        if tensors:
+            torch._foreach_copy_(tensors, views)
 
 
 class KFACCommunicator:
