@@ -76,6 +76,23 @@ int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols,
                     float alpha, float beta, float* out, int64_t ldo,
                     void* workspace, size_t workspace_bytes, int impl, void* stream);
 
+/* sso_factor_syrk for callers that are not allowed to allocate device memory when they need a
+ * factor (all device memory already given to their own pool, a fixed memory budget after start-up,
+ * or no tolerance for the implicit synchronisation of an allocation).  It has no counterpart in
+ * the reference, which allocates freely on every call.
+ * The split-partial scratch is a 16 MiB array inside the library image: every GPU that loads the
+ * library holds it until the process exits.  Shapes whose scratch need (sso_factor_workspace_bytes)
+ * is larger are rejected with an error and nothing is launched.  The first call on a device
+ * resolves the array's device address; make it before any stream capture begins.  All calls on a
+ * device share the array: calls whose GPU work can overlap (other streams or threads) race and
+ * must be serialised by the caller; calls on one stream are safe.  Nothing on this path calls
+ * cudaMalloc / cudaFree or an allocating library routine. */
+int sso_factor_syrk_noalloc(const void* x, int dtype, int64_t rows, int64_t cols,
+                            int64_t row_stride, int64_t col_stride,
+                            int append_ones, const float* row_weight,
+                            float alpha, float beta, float* out, int64_t ldo,
+                            int impl, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * BatchNorm diagonal curvature in two streaming stages, so that nothing activation-sized
  * is kept between forward and backward (in-place ReLU / residual adds may overwrite the

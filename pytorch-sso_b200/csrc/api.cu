@@ -1,4 +1,6 @@
 // extern "C" entry points for factor construction plus library-wide state.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sso {
@@ -86,6 +88,69 @@ int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols, int64_
   return sso_factor_syrk_im2col(x, dtype, rows, cols, 1, 1, row_stride, col_stride, 0, 0, 1, 1, 1, 1, 0, 0,
                                 1, 1, append_ones, row_weight, alpha, beta, out, ldo, workspace,
                                 workspace_bytes, impl, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Factor construction for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc (or anything that may call it) at the point
+// where they need a factor: an embedding runtime that handed all device memory to its own pool
+// at start-up, a service with a hard memory budget that forbids growth after initialisation, or
+// code running where an implicit device synchronisation (which cudaMalloc implies) is not
+// acceptable.  sso_factor_syrk needs scratch for its split partial tiles, so those callers get
+// this variant: the scratch is a fixed array that is part of the loaded library image.
+//
+//  * The array is kStaticScratchBytes (16 MiB) per GPU that loads the library and stays
+//    resident until the process exits, whether or not this entry point is ever used.
+//  * Problems whose scratch need (sso_factor_workspace_bytes) exceeds it are rejected with an
+//    error; nothing is launched.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+//    with that device current).  Make that first call before starting any stream capture.
+//  * All calls on a device share the one array and it keeps the previous call's contents.  The
+//    kernels overwrite every partial tile before reading it and the status word is cleared on the
+//    stream at the start of each call, so back-to-back calls on ONE stream are safe; calls whose
+//    GPU work may overlap (different streams, different host threads) race on the array and must
+//    be serialised by the caller.
+//  * No cudaMalloc, cudaFree or allocating library routine is called on this path.
+constexpr size_t kStaticScratchBytes = (size_t)16 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_scratch_mu;
+static void* g_scratch_addr[kMaxDevices] = {};
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address:
+// the address a kernel can use has to be asked for, once per device.
+static int static_scratch_address(void** out) {
+  int dev = -1;
+  SSO_CUDA_OK(cudaGetDevice(&dev));
+  SSO_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    SSO_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    SSO_CHECK_ARG(p != nullptr, "cudaGetSymbolAddress returned a null address");
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+
+int sso_factor_syrk_noalloc(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride,
+                            int64_t col_stride, int append_ones, const float* row_weight, float alpha,
+                            float beta, float* out, int64_t ldo, int impl, void* stream) {
+  SSO_CHECK_ARG(rows > 0 && cols > 0, "factor (no-alloc): bad shape");
+  const int64_t d = cols + (append_ones ? 1 : 0);
+  const size_t need = sso_factor_workspace_bytes(rows, d, impl);
+  SSO_CHECK_ARG(need <= kStaticScratchBytes,
+                "factor (no-alloc): %lld rows x %lld columns needs %zu bytes of scratch but the built-in "
+                "scratch holds %zu; use sso_factor_syrk with caller-provided scratch",
+                (long long)rows, (long long)d, need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != 0) return rc;
+  return sso_factor_syrk(x, dtype, rows, cols, row_stride, col_stride, append_ones, row_weight, alpha, beta,
+                         out, ldo, scratch, kStaticScratchBytes, impl, stream);
 }
 
 }  // extern "C"

@@ -62,6 +62,8 @@ SIGNATURES = {
                                [c_i32, c_vp, c_f32, c_f32, c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
     'sso_factor_syrk': (c_i32, [c_vp, c_i32, c_i64, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32, c_f32,
                                 c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
+    'sso_factor_syrk_noalloc': (c_i32, [c_vp, c_i32, c_i64, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32, c_f32,
+                                        c_vp, c_i64, c_i32, c_vp]),
     'sso_bn_plane_sums': (c_i32, [c_vp, c_vp, c_i32] + [c_i64] * 9 + [c_vp] * 5),
     'sso_bn_diag_finish': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_f32, c_f32, c_vp, c_vp, c_vp]),
     'sso_ema_update': (c_i32, [c_vp, c_vp, c_i64, c_f32, c_i32, c_vp]),
