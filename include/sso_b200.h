@@ -103,14 +103,19 @@ int sso_factor_syrk_noalloc(const void* x, int dtype, int64_t rows, int64_t cols
  *              b_out[c] <- alpha/n * sum_n      p_n * sg + beta * b_out[c]     (b_out nullable)
  * y / g are logical [n, c, hw] with element strides (s*n, s*c, s*p); either may be NULL to
  * run only the other half; scale/shift NULL mean 1/0; p = sample_weight or 1.
+ * Channels-contiguous tensors may be reduced in `splits` pieces of the pixel range (more blocks
+ * for large planes): sx / sg then hold [n, splits, c] partial sums, and the finishing call is told
+ * the split count of each.  sso_bn_plane_splits gives the count to use (1 = no splitting).
  * Replaces: torchsso/curv/curvature.py:123-134 (restore normalised input),
  *           torchsso/curv/cov/batchnorm.py:10-49, torchsso/curv/fisher/batchnorm.py:11-32.
  * ------------------------------------------------------------------------------------- */
+int sso_bn_plane_splits(int dtype, int64_t n, int64_t c, int64_t hw, int64_t stride_c);
 int sso_bn_plane_sums(const void* y, const void* g, int dtype, int64_t n, int64_t c, int64_t hw,
                       int64_t syn, int64_t syc, int64_t syp, int64_t sgn, int64_t sgc, int64_t sgp,
-                      const float* scale, const float* shift, float* sx, float* sg, void* stream);
+                      const float* scale, const float* shift, float* sx, float* sg, int splits,
+                      void* stream);
 int sso_bn_diag_finish(const float* sx, const float* sg, const float* sample_weight,
-                       int64_t n, int64_t c, float alpha, float beta,
+                       int64_t n, int64_t c, int splits_x, int splits_g, float alpha, float beta,
                        float* w_out, float* b_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------

@@ -2,6 +2,8 @@
 // BatchNorm diagonal curvature, diagonal inverse + precondition, triangular pack / unpack.
 // All are bandwidth bound: 16-byte vector accesses where alignment allows, grids sized as a
 // multiple of the 148 SMs with a grid-stride loop.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace sso {
@@ -129,16 +131,71 @@ __global__ void __launch_bounds__(256) bn_plane_sums_ccontig(const T* __restrict
   }
 }
 
+// Channels-contiguous planes, vectorised: a thread owns V = 16 bytes / sizeof(T) consecutive channels
+// and walks pixels; LP lanes cover one pixel's channels (LP*V >= c), 256/LP pixels are processed in
+// parallel per block, and the pixel range of one image is cut into `splits` blocks.  Partial sums go
+// to out[(n*splits + split)*c + channel]; the finishing kernel adds the splits.
+template <typename T, bool IS_Y>
+__global__ void __launch_bounds__(256) bn_plane_sums_vec(const T* __restrict__ t, int c, int hw, int64_t sn,
+                                                         int64_t sp, int lp, int splits,
+                                                         const float* __restrict__ scale,
+                                                         const float* __restrict__ shift,
+                                                         float* __restrict__ out) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ float red[256][V + 1];
+  const int cv = threadIdx.x % lp, pp = threadIdx.x / lp, npp = 256 / lp;
+  const int in = blockIdx.y, split = blockIdx.x;
+  const int per = (hw + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(hw, p0 + per);
+  const int c0 = cv * V;
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.f;
+  if (c0 < c) {
+    float isc[V], sh[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      isc[i] = (IS_Y && scale) ? 1.f / scale[c0 + i] : 1.f;
+      sh[i] = (IS_Y && shift) ? shift[c0 + i] : 0.f;
+    }
+    const T* base = t + (int64_t)in * sn + c0;
+    for (int p = p0 + pp; p < p1; p += npp) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)p * sp));
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const float v = (to_f32<T>(e[i]) - sh[i]) * isc[i];
+        acc[i] = fmaf(v, v, acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) red[threadIdx.x][i] = acc[i];
+  __syncthreads();
+  if (pp == 0 && c0 < c) {
+    float* o = out + ((int64_t)in * splits + split) * c + c0;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float sum = 0.f;
+      for (int q = 0; q < npp; ++q) sum += red[q * lp + cv][i];
+      o[i] = sum;
+    }
+  }
+}
+
 __global__ void bn_finish_kernel(const float* __restrict__ sx, const float* __restrict__ sg,
-                                 const float* __restrict__ weight, int n, int c, float alpha,
-                                 float beta, float* __restrict__ w_out, float* __restrict__ b_out) {
+                                 const float* __restrict__ weight, int n, int c, int splits_x, int splits_g,
+                                 float alpha, float beta, float* __restrict__ w_out, float* __restrict__ b_out) {
   const int ic = blockIdx.x * blockDim.x + threadIdx.x;
   if (ic >= c) return;
   float aw = 0.f, ab = 0.f;
   for (int in = 0; in < n; ++in) {
     const float p = weight ? weight[in] : 1.f;
-    const float gsum = p * sg[(int64_t)in * c + ic];
-    aw = fmaf(sx[(int64_t)in * c + ic], gsum, aw);
+    float xs = 0.f, gs = 0.f;
+    for (int q = 0; q < splits_x; ++q) xs += sx[((int64_t)in * splits_x + q) * c + ic];
+    for (int q = 0; q < splits_g; ++q) gs += sg[((int64_t)in * splits_g + q) * c + ic];
+    const float gsum = p * gs;
+    aw = fmaf(xs, gsum, aw);
     ab += gsum;
   }
   const float s = alpha / (float)n;
@@ -146,12 +203,50 @@ __global__ void bn_finish_kernel(const float* __restrict__ sx, const float* __re
   if (b_out) b_out[ic] = (beta == 0.f) ? s * ab : fmaf(beta, b_out[ic], s * ab);
 }
 
+// pixel-range splits of the vectorised kernel for a [n, c, hw] tensor (1 when it is not used)
+static int bn_vec_lanes(int64_t c, int vec) {
+  if (c % vec != 0 || c / vec > 256) return 0;
+  int lp = 1;
+  while (lp < c / vec) lp <<= 1;
+  return lp;
+}
+static int bn_vec_splits(int64_t n, int64_t c, int64_t hw, int vec) {
+  const int lp = bn_vec_lanes(c, vec);
+  if (lp == 0 || hw <= 1) return 1;
+  const int npp = 256 / lp;
+  int64_t s = ceil_div64(3 * kSMs, n);                       // about three waves of blocks
+  const int64_t most = std::max<int64_t>(1, hw / (4 * npp)); // at least four pixels per lane
+  if (s > most) s = most;
+  return (int)std::max<int64_t>(1, s);
+}
+
 template <typename T>
 static int bn_sums_typed(const void* y, const void* g, int64_t n, int64_t c, int64_t hw, int64_t syn,
                          int64_t syc, int64_t syp, int64_t sgn, int64_t sgc, int64_t sgp,
-                         const float* scale, const float* shift, float* sx, float* sg, cudaStream_t st) {
+                         const float* scale, const float* shift, float* sx, float* sg, int splits,
+                         cudaStream_t st) {
   const T* ty = reinterpret_cast<const T*>(y);
   const T* tg = reinterpret_cast<const T*>(g);
+  constexpr int V = 16 / sizeof(T);
+  const int lp = bn_vec_lanes(c, V);
+  auto vec_ok = [&](const T* p, int64_t sc_, int64_t sn_, int64_t sp_) {
+    return p != nullptr && sc_ == 1 && lp > 0 && hw > 1 && (reinterpret_cast<uintptr_t>(p) & 15) == 0 &&
+           (sn_ * sizeof(T)) % 16 == 0 && (sp_ * sizeof(T)) % 16 == 0;
+  };
+  if (splits > 1 || (vec_ok(ty, syc, syn, syp) || !y) && (vec_ok(tg, sgc, sgn, sgp) || !g) && hw > 1 && lp > 0) {
+    SSO_CHECK_ARG((!y || vec_ok(ty, syc, syn, syp)) && (!g || vec_ok(tg, sgc, sgn, sgp)),
+                  "bn_plane_sums: splits > 1 needs channels-contiguous, 16-byte aligned planes");
+    dim3 grid((unsigned)splits, (unsigned)n);
+    if (y) {
+      bn_plane_sums_vec<T, true><<<grid, 256, 0, st>>>(ty, (int)c, (int)hw, syn, syp, lp, splits, scale, shift, sx);
+      SSO_LAUNCH_OK("bn_plane_sums_vec");
+    }
+    if (g) {
+      bn_plane_sums_vec<T, false><<<grid, 256, 0, st>>>(tg, (int)c, (int)hw, sgn, sgp, lp, splits, nullptr, nullptr, sg);
+      SSO_LAUNCH_OK("bn_plane_sums_vec");
+    }
+    return 0;
+  }
   if (syc == 1 && sgc == 1 && hw > 1) {
     dim3 grid((unsigned)ceil_div64(c, 32), (unsigned)n);
     bn_plane_sums_ccontig<T><<<grid, 256, 0, st>>>(ty, tg, (int)n, (int)c, (int)hw, syn, syc, syp, sgn, sgc,
@@ -246,32 +341,38 @@ int sso_ema_update(const float* data, float* ema, int64_t count, float beta, int
   return sso_axpby(data, ema, count, beta, 1.f - beta, stream);
 }
 
+int sso_bn_plane_splits(int dtype, int64_t n, int64_t c, int64_t hw, int64_t stride_c) {
+  if (stride_c != 1) return 1;
+  return bn_vec_splits(n, c, hw, dtype == SSO_F32 ? 4 : 8);
+}
+
 int sso_bn_plane_sums(const void* y, const void* g, int dtype, int64_t n, int64_t c, int64_t hw,
                       int64_t syn, int64_t syc, int64_t syp, int64_t sgn, int64_t sgc, int64_t sgp,
-                      const float* scale, const float* shift, float* sx, float* sg, void* stream) {
+                      const float* scale, const float* shift, float* sx, float* sg, int splits, void* stream) {
   SSO_CHECK_ARG((y && sx) || (g && sg), "bn_plane_sums: nothing to do");
   SSO_CHECK_ARG(!y || sx, "bn_plane_sums: y without sx");
   SSO_CHECK_ARG(!g || sg, "bn_plane_sums: g without sg");
-  SSO_CHECK_ARG(n > 0 && c > 0 && hw > 0 && n * c < (int64_t)1 << 26, "bn_plane_sums: bad shape");
+  SSO_CHECK_ARG(n > 0 && c > 0 && hw > 0 && n * c < (int64_t)1 << 26 && splits >= 1, "bn_plane_sums: bad shape");
   if (!y) { syn = sgn; syc = sgc; syp = sgp; }
   if (!g) { sgn = syn; sgc = syc; sgp = syp; }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (dtype) {
     case SSO_F32:
-      return bn_sums_typed<float>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, st);
+      return bn_sums_typed<float>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, splits, st);
     case SSO_BF16:
-      return bn_sums_typed<__nv_bfloat16>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, st);
+      return bn_sums_typed<__nv_bfloat16>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, splits, st);
     case SSO_F16:
-      return bn_sums_typed<__half>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, st);
+      return bn_sums_typed<__half>(y, g, n, c, hw, syn, syc, syp, sgn, sgc, sgp, scale, shift, sx, sg, splits, st);
   }
   return fail(-1, "bn_plane_sums: unknown dtype %d", dtype);
 }
 
 int sso_bn_diag_finish(const float* sx, const float* sg, const float* sample_weight, int64_t n, int64_t c,
-                       float alpha, float beta, float* w_out, float* b_out, void* stream) {
-  SSO_CHECK_ARG(sx && sg && w_out && n > 0 && c > 0, "bn_diag_finish: bad argument");
+                       int splits_x, int splits_g, float alpha, float beta, float* w_out, float* b_out,
+                       void* stream) {
+  SSO_CHECK_ARG(sx && sg && w_out && n > 0 && c > 0 && splits_x >= 1 && splits_g >= 1, "bn_diag_finish: bad argument");
   bn_finish_kernel<<<(unsigned)ceil_div64(c, 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      sx, sg, sample_weight, (int)n, (int)c, alpha, beta, w_out, b_out);
+      sx, sg, sample_weight, (int)n, (int)c, splits_x, splits_g, alpha, beta, w_out, b_out);
   SSO_LAUNCH_OK("bn_finish_kernel");
   return 0;
 }

@@ -64,8 +64,9 @@ SIGNATURES = {
                                 c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
     'sso_factor_syrk_noalloc': (c_i32, [c_vp, c_i32, c_i64, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32, c_f32,
                                         c_vp, c_i64, c_i32, c_vp]),
-    'sso_bn_plane_sums': (c_i32, [c_vp, c_vp, c_i32] + [c_i64] * 9 + [c_vp] * 5),
-    'sso_bn_diag_finish': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_f32, c_f32, c_vp, c_vp, c_vp]),
+    'sso_bn_plane_splits': (c_i32, [c_i32, c_i64, c_i64, c_i64, c_i64]),
+    'sso_bn_plane_sums': (c_i32, [c_vp, c_vp, c_i32] + [c_i64] * 9 + [c_vp] * 4 + [c_i32, c_vp]),
+    'sso_bn_diag_finish': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_i32, c_f32, c_f32, c_vp, c_vp, c_vp]),
     'sso_ema_update': (c_i32, [c_vp, c_vp, c_i64, c_f32, c_i32, c_vp]),
     'sso_axpby': (c_i32, [c_vp, c_vp, c_i64, c_f32, c_f32, c_vp]),
     'sso_diag_inv_precondition': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_f32, c_i32, c_i32, c_vp]),
@@ -215,6 +216,54 @@ def factor_rows(x: torch.Tensor, append_ones: bool, row_weight: Optional[torch.T
         2.0 * rows * d * d, x.numel() * x.element_size() + 4 * d * d)
 
 
+class FactorOp:
+    """A factor-construction call with everything that does not change between steps (geometry,
+    strides, scratch size, output slot) resolved once; the hooks run it ~100 times per step, so
+    the per-call Python work is kept to pointer look-ups and one foreign call."""
+
+    __slots__ = ('fn', 'mid', 'out_ptr', 'ldo', 'nbytes', 'device', 'impl', 'flops', 'bytes')
+
+    def __init__(self, x: torch.Tensor, kernel_size, stride, padding, dilation, append_ones: bool,
+                 out: torch.Tensor, impl: int = IMPL_AUTO):
+        _require_cuda(x, 'factor input')
+        if x.dim() == 2:        # plain matrix [rows, cols]
+            n, c, h, w = x.shape[0], x.shape[1], 1, 1
+            sn, sc, sh, sw = x.stride(0), x.stride(1), 0, 0
+        else:
+            n, c, h, w = x.shape
+            sn, sc, sh, sw = x.stride()
+        kh, kw = kernel_size
+        ho = (h + 2 * padding[0] - dilation[0] * (kh - 1) - 1) // stride[0] + 1
+        wo = (w + 2 * padding[1] - dilation[1] * (kw - 1) - 1) // stride[1] + 1
+        d = c * kh * kw + (1 if append_ones else 0)
+        assert out.shape == (d, d) and out.dtype == torch.float32 and out.stride(1) == 1, (out.shape, d)
+        rows = n * ho * wo
+        L = lib()
+        self.fn = L.sso_factor_syrk_im2col
+        self.mid = (_dtype_code(x), n, c, h, w, sn, sc, sh, sw, kh, kw, stride[0], stride[1],
+                    padding[0], padding[1], dilation[0], dilation[1], int(append_ones))
+        self.out_ptr, self.ldo = out.data_ptr(), out.stride(0)
+        self.nbytes = L.sso_factor_workspace_bytes(rows, d, impl)
+        self.device, self.impl = x.device, impl
+        self.flops = 2.0 * rows * d * d
+        self.bytes = x.numel() * x.element_size() + 4 * d * d
+
+    def run(self, x: torch.Tensor, weight: Optional[torch.Tensor], alpha: float, beta: float):
+        ws = workspace(self.device, self.nbytes)
+        if FACTOR_TIMING is not None:
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+        rc = self.fn(x.data_ptr(), *self.mid, None if weight is None else weight.data_ptr(), alpha, beta,
+                     self.out_ptr, self.ldo, None if ws is None else ws.data_ptr(),
+                     0 if ws is None else ws.numel(), self.impl, torch.cuda.current_stream().cuda_stream)
+        if rc < 0:
+            _check(rc)
+        if FACTOR_TIMING is not None:
+            b.record()
+            FACTOR_TIMING.append((a, b, self.flops, self.bytes))
+
+
 def _plane_strides(t: torch.Tensor):
     """(n, c, hw) element strides of a [n,c] or [n,c,h,w] tensor whose (h,w) plane is
     addressable with one stride; returns None if it is not."""
@@ -227,31 +276,40 @@ def _plane_strides(t: torch.Tensor):
     return None
 
 
-def bn_plane_sums(y: Optional[torch.Tensor], g: Optional[torch.Tensor], scale, shift,
-                  sx: Optional[torch.Tensor], sg: Optional[torch.Tensor]):
-    ref = y if y is not None else g
-    _require_cuda(ref, 'batch-norm tensor')
-    n, c = ref.shape[0], ref.shape[1]
-    hw = ref.numel() // (n * c)
-    sy = (0, 0, 0)
-    if y is not None:
-        sy = _plane_strides(y)
-        if sy is None:
-            y = y.contiguous()
-            sy = _plane_strides(y)
-    sgs = (0, 0, 0)
-    if g is not None:
-        sgs = _plane_strides(g)
-        if sgs is None:
-            g = g.contiguous()
-            sgs = _plane_strides(g)
-    _check(lib().sso_bn_plane_sums(_ptr(y), _ptr(g), _dtype_code(ref), n, c, hw, *sy, *sgs,
-                                   _ptr(scale), _ptr(shift), _ptr(sx), _ptr(sg), _stream()))
+def bn_plane_layout(t: torch.Tensor):
+    """(tensor to pass, (n, c, hw) element strides, split count) for a [n,c] / [n,c,h,w] tensor."""
+    st = _plane_strides(t)
+    if st is None:
+        t = t.contiguous()
+        st = _plane_strides(t)
+    n, c = t.shape[0], t.shape[1]
+    hw = t.numel() // (n * c)
+    splits = lib().sso_bn_plane_splits(_dtype_code(t), n, c, hw, st[1]) if hw > 1 else 1
+    ok = (st[1] == 1 and t.data_ptr() % 16 == 0 and (st[0] * t.element_size()) % 16 == 0
+          and (st[2] * t.element_size()) % 16 == 0)
+    return t, st, (splits if ok else 1)
 
 
-def bn_diag_finish(sx, sg, sample_weight, n, c, alpha, beta, w_out, b_out):
-    _check(lib().sso_bn_diag_finish(sx.data_ptr(), sg.data_ptr(), _ptr(sample_weight), n, c, alpha,
-                                    beta, w_out.data_ptr(), _ptr(b_out), _stream()))
+def bn_plane_sums(t: torch.Tensor, is_output: bool, scale, shift, out: torch.Tensor, layout=None) -> int:
+    """out[n, splits, c] <- per-plane sums of squares of t (normalised with scale/shift when it
+    is the layer output); returns the split count that was used."""
+    _require_cuda(t, 'batch-norm tensor')
+    t, st, splits = layout if layout is not None else bn_plane_layout(t)
+    n, c = t.shape[0], t.shape[1]
+    hw = t.numel() // (n * c)
+    assert out.numel() >= n * splits * c
+    if is_output:
+        _check(lib().sso_bn_plane_sums(t.data_ptr(), None, _dtype_code(t), n, c, hw, *st, 0, 0, 0,
+                                       _ptr(scale), _ptr(shift), out.data_ptr(), None, splits, _stream()))
+    else:
+        _check(lib().sso_bn_plane_sums(None, t.data_ptr(), _dtype_code(t), n, c, hw, 0, 0, 0, *st,
+                                       None, None, None, out.data_ptr(), splits, _stream()))
+    return splits
+
+
+def bn_diag_finish(sx, sg, sample_weight, n, c, splits_x, splits_g, alpha, beta, w_out, b_out):
+    _check(lib().sso_bn_diag_finish(sx.data_ptr(), sg.data_ptr(), _ptr(sample_weight), n, c, splits_x,
+                                    splits_g, alpha, beta, w_out.data_ptr(), _ptr(b_out), _stream()))
 
 
 def ema_update(data: torch.Tensor, ema: torch.Tensor, beta: float, first: bool):

@@ -46,6 +46,7 @@ class Curvature(object):
         self._pool = None
         self._have = set()          # which of data / ema / inv / std hold values
         self._generic = {}          # storage for curvature shapes the pool does not manage
+        self._is_norm = isinstance(module, _NORM_TYPES)
         module.register_forward_hook(self.forward_postprocess)
 
     # ---- identity ---------------------------------------------------------------
@@ -123,10 +124,10 @@ class Curvature(object):
     def forward_postprocess(self, module, input, output):
         assert self._module is module
         x = input[0].detach()
-        setattr(module, 'data_input', x)
-        setattr(module, 'data_output', output)
-        self.update_in_forward(x if not isinstance(module, _NORM_TYPES) else output.detach())
-        if torch.is_grad_enabled() and isinstance(output, torch.Tensor) and output.requires_grad:
+        module.data_input = x
+        module.data_output = output
+        self.update_in_forward(output.detach() if self._is_norm else x)
+        if output.requires_grad and torch.is_grad_enabled():
             output.register_hook(self._backward_hook)
 
     def _backward_hook(self, grad_output):
@@ -134,7 +135,7 @@ class Curvature(object):
 
     def backward_postprocess(self, module, grad_input, grad_output):
         g = grad_output[0].detach()
-        setattr(module, 'grad_output', g)
+        module.grad_output = g
         # the n^2 rescale that undoes the mean reduction of the loss
         # (torchsso/curv/curvature.py:151-155) is folded into the kernels' alpha
         self.update_in_backward(g)

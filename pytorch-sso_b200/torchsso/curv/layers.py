@@ -80,8 +80,27 @@ class _KronFactors(KronCurvature):
     def _factor_G(self, g, weight, alpha_scale, beta, out):
         raise NotImplementedError
 
+    def _op(self, x, geometry, append_ones, out):
+        """Prepared factor call for this input layout (built on first sight of a shape/stride/dtype)."""
+        ops = self.__dict__.setdefault('_ops', {})
+        key = (x.shape, x.stride(), x.dtype, out.data_ptr())
+        op = ops.get(key)
+        if op is None:
+            if len(ops) > 16:
+                ops.clear()
+            op = nat.FactorOp(x, *geometry, append_ones, out)
+            ops[key] = op
+        return op
+
+    def _data_views(self):
+        v = self.__dict__.get('_dv')
+        if v is None or v[0] is not self._pool:
+            v = (self._pool if self._pool is not None else self.pool, self._views('data'))
+            self.__dict__['_dv'] = v
+        return v[1]
+
     def update_in_forward(self, x):
-        self._factor_A(x, self._views('data')[0])
+        self._factor_A(x, self._data_views()[0])
 
     def update_in_backward(self, g):
         fisher = isinstance(self, Fisher)
@@ -93,7 +112,7 @@ class _KronFactors(KronCurvature):
         n = g.shape[0]
         beta = 1.0 if (fisher and self._g_passes > 0) else 0.0
         w, ws = _weights(self, n, g.device)
-        self._factor_G(g, w, ws * float(n) * float(n), beta, self._views('data')[1])
+        self._factor_G(g, w, ws * float(n) * float(n), beta, self._data_views()[1])
         if fisher:
             self._g_passes += 1
         self._have.add('data')
@@ -107,13 +126,15 @@ class KronCovLinear(_KronFactors):
         da = f_in + 1 if self.bias else f_in
         return (da, da), (f_out, f_out)
 
+    _PLAIN = ((1, 1), (1, 1), (0, 0), (1, 1))
+
     def _factor_A(self, x, out):
-        x2 = x.reshape(-1, x.shape[-1])
-        nat.factor_rows(x2, self.bias, None, 1.0 / x2.shape[0], 0.0, out)
+        x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+        self._op(x2, self._PLAIN, self.bias, out).run(x2, None, 1.0 / x2.shape[0], 0.0)
 
     def _factor_G(self, g, weight, scale, beta, out):
-        g2 = g.reshape(-1, g.shape[-1])
-        nat.factor_rows(g2, False, weight, scale / g2.shape[0], beta, out)
+        g2 = g if g.dim() == 2 else g.reshape(-1, g.shape[-1])
+        self._op(g2, self._PLAIN, False, out).run(g2, weight, scale / g2.shape[0], beta)
 
 
 class KronCovConv2d(_KronFactors):
@@ -129,12 +150,39 @@ class KronCovConv2d(_KronFactors):
         m = self._module
         if m.groups != 1 or isinstance(m.padding, str):
             raise NotImplementedError('grouped / string-padded convolutions have no Kronecker curvature here')
-        nat.factor_im2col(x, m.kernel_size, m.stride, m.padding, m.dilation, self.bias, None,
-                          1.0 / x.shape[0], 0.0, out)
+        n, c = x.shape[0], x.shape[1]
+        vec = 4 if x.dtype == torch.float32 else 8
+        if x.stride(1) == 1 and c % vec != 0 and c < 64:
+            # Channels-last input whose channel count is not a whole number of 16-byte chunks (the
+            # 3-channel stem): zero-pad the channels so the tensor-core kernel applies, then keep
+            # the rows / columns of the real channels.  Columns are ordered (c, kh, kw), so the
+            # padding channels are a trailing block (followed by the ones column when there is a bias).
+            cp = (c + vec - 1) // vec * vec
+            kk = m.kernel_size[0] * m.kernel_size[1]
+            xp = torch.empty((n, cp, x.shape[2], x.shape[3]), dtype=x.dtype, device=x.device,
+                             memory_format=torch.channels_last)
+            xp[:, c:].zero_()
+            xp[:, :c] = x
+            dp = cp * kk + (1 if self.bias else 0)
+            if getattr(self, '_pad_buf', None) is None or self._pad_buf.shape[0] != dp:
+                self._pad_buf = torch.empty((dp, dp), dtype=torch.float32, device=x.device)
+            self._op(xp, (m.kernel_size, m.stride, m.padding, m.dilation), self.bias,
+                     self._pad_buf).run(xp, None, 1.0 / n, 0.0)
+            d = c * kk
+            out[:d, :d].copy_(self._pad_buf[:d, :d])
+            if self.bias:
+                out[:d, d].copy_(self._pad_buf[:d, dp - 1])
+                out[d, :d].copy_(self._pad_buf[dp - 1, :d])
+                out[d, d].copy_(self._pad_buf[dp - 1, dp - 1])
+            return
+        geometry = (m.kernel_size, m.stride, m.padding, m.dilation)
+        self._op(x, geometry, self.bias, out).run(x, None, 1.0 / n, 0.0)
+
+    _PLAIN = ((1, 1), (1, 1), (0, 0), (1, 1))
 
     def _factor_G(self, g, weight, scale, beta, out):
         n, c, h, w = g.shape
-        nat.factor_im2col(g, (1, 1), (1, 1), (0, 0), (1, 1), False, weight, scale / (n * h * w), beta, out)
+        self._op(g, self._PLAIN, False, out).run(g, weight, scale / (n * h * w), beta)
 
 
 class KronFisherLinear(KronCovLinear, Fisher):
@@ -172,20 +220,37 @@ class _DiagBatchNorm(DiagCurvature):
         super(_DiagBatchNorm, self).__init__(*args, **kwargs)
         self._sx = None
         self._sg = None
+        self._splits_x = 1
         self._passes = 0
 
-    def _plane(self, n, c, device):
-        if self._sx is None or self._sx.numel() != n * c:
-            self._sx = torch.empty(n * c, dtype=torch.float32, device=device)
-            self._sg = torch.empty(n * c, dtype=torch.float32, device=device)
-        return self._sx, self._sg
+    @staticmethod
+    def _buffer(buf, numel, device):
+        if buf is None or buf.numel() < numel or buf.device != device:
+            buf = torch.empty(numel, dtype=torch.float32, device=device)
+        return buf
+
+    def _layout(self, t):
+        """(strides, splits) of the plane-sum kernel for this tensor layout, cached."""
+        cache = self.__dict__.setdefault('_layouts', {})
+        key = (t.shape, t.stride(), t.dtype, t.data_ptr() % 16)
+        ent = cache.get(key)
+        if ent is None:
+            if len(cache) > 16:
+                cache.clear()
+            t2, st, splits = nat.bn_plane_layout(t)
+            ent = (st, splits, t2 is t)
+            cache[key] = ent
+        if not ent[2]:
+            t = t.contiguous()
+        return (t, ent[0], ent[1])
 
     def update_in_forward(self, out):
         bn = self._module
         if bn.weight is None:
             raise NotImplementedError('affine=False normalisation has no parameters to precondition')
-        sx, _ = self._plane(out.shape[0], out.shape[1], out.device)
-        nat.bn_plane_sums(out, None, bn.weight.detach(), bn.bias.detach(), sx, None)
+        layout = self._layout(out)
+        self._sx = self._buffer(self._sx, out.shape[0] * layout[2] * out.shape[1], out.device)
+        self._splits_x = nat.bn_plane_sums(layout[0], True, bn.weight.detach(), bn.bias.detach(), self._sx, layout)
 
     def update_in_backward(self, g):
         fisher = isinstance(self, Fisher)
@@ -194,12 +259,17 @@ class _DiagBatchNorm(DiagCurvature):
             self._have.add('data')
             return
         n, c = g.shape[0], g.shape[1]
-        sx, sg = self._plane(n, c, g.device)
-        nat.bn_plane_sums(None, g, None, None, None, sg)
+        layout = self._layout(g)
+        self._sg = self._buffer(self._sg, n * layout[2] * c, g.device)
+        splits_g = nat.bn_plane_sums(layout[0], False, None, None, self._sg, layout)
         beta = 1.0 if (fisher and self._passes > 0) else 0.0
-        views = self._views('data')
+        views = self.__dict__.get('_bnv')
+        if views is None or views[0] is not self._pool:
+            views = (self._pool if self._pool is not None else self.pool, self._views('data'))
+            self.__dict__['_bnv'] = views
+        views = views[1]
         w, ws = _weights(self, n, g.device)
-        nat.bn_diag_finish(sx, sg, w, n, c, ws * float(n) * float(n), beta,
+        nat.bn_diag_finish(self._sx, self._sg, w, n, c, self._splits_x, splits_g, ws * float(n) * float(n), beta,
                            views[0], views[1] if len(views) > 1 else None)
         if fisher:
             self._passes += 1

@@ -213,7 +213,8 @@ def test_factor_rejects_bad_arguments(nat):
 
 
 # ------------------------------------------------------------------------------------ batch norm
-@pytest.mark.parametrize('shape', [(6, 5, 4, 4), (4, 70, 7, 7), (8, 33), (3, 64, 1, 1)])
+@pytest.mark.parametrize('shape', [(6, 5, 4, 4), (4, 70, 7, 7), (8, 33), (3, 64, 1, 1), (4, 64, 56, 56),
+                                   (2, 2048, 7, 7), (3, 24, 20, 20)])
 @pytest.mark.parametrize('channels_last', [False, True])
 @pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
 def test_bn_diag_matches_oracle(nat, shape, channels_last, dtype):
@@ -232,13 +233,13 @@ def test_bn_diag_matches_oracle(nat, shape, channels_last, dtype):
     if channels_last:
         yd = yd.contiguous(memory_format=torch.channels_last)
         gd = gd.contiguous(memory_format=torch.channels_last)
-    sx = torch.empty(n * c, device='cuda')
-    sg = torch.empty(n * c, device='cuda')
-    nat.bn_plane_sums(yd, None, dev(gamma), dev(beta), sx, None)
-    nat.bn_plane_sums(None, gd, None, None, None, sg)
+    sx = torch.full((n * c * 64,), float('nan'), device='cuda')
+    sg = torch.full((n * c * 64,), float('nan'), device='cuda')
+    kx = nat.bn_plane_sums(yd, True, dev(gamma), dev(beta), sx)
+    kg = nat.bn_plane_sums(gd, False, None, None, sg)
     w_out = torch.empty(c, device='cuda')
     b_out = torch.empty(c, device='cuda')
-    nat.bn_diag_finish(sx, sg, dev(p), n, c, 1.0, 0.0, w_out, b_out)
+    nat.bn_diag_finish(sx, sg, dev(p), n, c, kx, kg, 1.0, 0.0, w_out, b_out)
     assert rel(w_out, ref[0]) < 2e-5
     assert rel(b_out, ref[1]) < 2e-5
 

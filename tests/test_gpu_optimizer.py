@@ -210,3 +210,18 @@ def test_constructor_validation_matches_reference(torchsso_mod):
         torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON, {'ema_decay': 2.0})
     with pytest.raises(AssertionError, match='Failed to lookup Curvature class'):
         torchsso.optim.SecondOrderOptimizer(model, 'Nope', KRON, {})
+
+
+def test_conv_stem_with_three_channels_channels_last(torchsso_mod):
+    """3-channel channels_last input (image stem): channels are zero-padded to a 16-byte chunk for the
+    tensor-core kernel and the padding rows / columns dropped again; with and without bias."""
+    import torch.nn as nn
+    from oracle import kfac_oracle as ko
+    torchsso = torchsso_mod
+    for bias in (False, True):
+        conv = nn.Conv2d(3, 8, 7, stride=2, padding=3, bias=bias).cuda().to(memory_format=torch.channels_last)
+        curv = torchsso.KronCovConv2d(conv, ema_decay=1.0, damping=1e-3)
+        x = cases.make_normal((4, 3, 20, 20), 17).cuda().contiguous(memory_format=torch.channels_last)
+        conv(x).square().mean().backward()
+        ref = ko.conv_factor_A(x.cpu().double(), (7, 7), (2, 2), (3, 3), (1, 1), bias)
+        assert rel(curv.data[0], ref) < 1e-5
