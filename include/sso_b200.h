@@ -31,14 +31,18 @@ extern "C" {
 #define SSO_VERSION 100
 
 enum { SSO_F32 = 0, SSO_BF16 = 1, SSO_F16 = 2 };
-/* factor kernel implementations: AUTO picks tcgen05 when the shape is supported */
-enum { SSO_IMPL_AUTO = 0, SSO_IMPL_SIMT = 1, SSO_IMPL_TCGEN05 = 2 };
+/* factor kernel implementations.  AUTO picks, in this order, the TMA-fed tcgen05 kernel (16-bit
+ * channels-contiguous inputs with a multiple of 64 channels, no ones column, no weights), the
+ * tcgen05 kernel with a register/cp.async gather (channels-contiguous inputs, 16-bit or fp32 as
+ * 3xTF32), the fp32 SIMT kernel (anything). */
+enum { SSO_IMPL_AUTO = 0, SSO_IMPL_SIMT = 1, SSO_IMPL_TCGEN05 = 2, SSO_IMPL_TMA = 3 };
 
 int sso_version(void);
 const char* sso_last_error(void);
 /* kernels launched by this library since it was loaded (bookkeeping for benchmarks) */
 uint64_t sso_launch_count(void);
-/* process-wide switches: "tc_auto" (0/1: may SSO_IMPL_AUTO choose the tcgen05 factor kernel),
+/* process-wide switches: "tc_auto" / "tma_auto" (0/1: may SSO_IMPL_AUTO choose the tcgen05 kernels /
+ * the TMA-fed one),
  * "tc_flush" (stages of tensor-core accumulation between drains into fp32 registers) */
 int sso_configure(const char* key, int value);
 

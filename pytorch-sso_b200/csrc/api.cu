@@ -18,7 +18,11 @@ size_t factor_tc_workspace_bytes(int64_t rows, int64_t d);
 bool factor_tc_supported(const FactorParams& p, int dtype);
 int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
 void factor_tc_set_flush(int stages);
-static int g_tc_auto = 1;   // whether SSO_IMPL_AUTO may pick the tcgen05 kernel
+int factor_tc_flush_setting();
+bool factor_tma_supported(const FactorParams& p, int dtype);
+int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
+static int g_tc_auto = 1;    // whether SSO_IMPL_AUTO may pick the tcgen05 kernels
+static int g_tma_auto = 1;   // whether SSO_IMPL_AUTO may pick the TMA-fed tcgen05 kernel
 }  // namespace sso
 
 using namespace sso;
@@ -33,6 +37,7 @@ int sso_configure(const char* key, int value) {
   SSO_CHECK_ARG(key != nullptr, "configure: null key");
   const std::string k(key);
   if (k == "tc_auto") { g_tc_auto = value != 0; return 0; }
+  if (k == "tma_auto") { g_tma_auto = value != 0; return 0; }
   if (k == "tc_flush") { factor_tc_set_flush(value); return 0; }
   return fail(-1, "configure: unknown key %s", key);
 }
@@ -41,7 +46,7 @@ size_t sso_factor_workspace_bytes(int64_t rows, int64_t d, int impl) {
   const size_t a = factor_simt_workspace_bytes(rows, d);
   const size_t b = factor_tc_workspace_bytes(rows, d);
   if (impl == SSO_IMPL_SIMT) return a;
-  if (impl == SSO_IMPL_TCGEN05) return b;
+  if (impl == SSO_IMPL_TCGEN05 || impl == SSO_IMPL_TMA) return b;
   return a > b ? a : b;
 }
 
@@ -72,6 +77,12 @@ int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64
   p.d = (int)d; p.dcols = (int)dcols;
   p.alpha = alpha; p.beta = beta;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (impl == SSO_IMPL_TMA) {
+    SSO_CHECK_ARG(factor_tma_supported(p, dtype), "factor: shape not supported by the TMA-fed tcgen05 path");
+    return factor_tma_launch(p, dtype, workspace, workspace_bytes, factor_tc_flush_setting(), st);
+  }
+  if (impl == SSO_IMPL_AUTO && g_tc_auto && g_tma_auto && factor_tma_supported(p, dtype))
+    return factor_tma_launch(p, dtype, workspace, workspace_bytes, factor_tc_flush_setting(), st);
   if (impl == SSO_IMPL_TCGEN05) {
     SSO_CHECK_ARG(factor_tc_supported(p, dtype), "factor: shape not supported by the tcgen05 path");
     return factor_tc_launch(p, dtype, workspace, workspace_bytes, st);

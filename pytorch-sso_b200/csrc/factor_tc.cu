@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 #include "factor_params.cuh"
+#include "tc_common.cuh"
 
 namespace sso {
 namespace tc {
@@ -36,7 +37,6 @@ constexpr int MMA_WARP = EPI_WARPS;
 constexpr int THREADS = 32 * (EPI_WARPS + 1 + LOAD_WARPS);
 constexpr int LOAD_THREADS = 32 * LOAD_WARPS;
 constexpr uint32_t TMEM_COLS = 256;    // two 128-column accumulators
-constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s
 
 template <typename T>
 struct Cfg;
@@ -68,98 +68,6 @@ struct Cfg<__half> {
   static constexpr uint32_t FMT = 0, MAJOR = 1;  // f16, MN-major
   static constexpr uint32_t LBO = 128, SBO = 1040, OPB = 16 * 1040, KSTEP = 2 * 128;
 };
-
-// ---- PTX wrappers ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false on timeout (code is recorded once).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > WAIT_CYCLES) {
-      if (status) atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-template <bool TF32>
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  if (TF32)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-        "r"(idesc), "r"(accumulate)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
-        "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// shared-memory matrix descriptor, no swizzle, descriptor version 1 (sm_100)
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
-         ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46);
-}
-// instruction descriptor: D fp32, A/B format `fmt`, both operands of major-ness `major`
-// (0 K-major, 1 MN-major), M = N = 128
-__device__ __forceinline__ uint32_t instr_desc(uint32_t fmt, uint32_t major) {
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | (major << 15) | (major << 16) | ((uint32_t)(TILE >> 3) << 17) |
-         ((uint32_t)(TILE >> 4) << 24);
-}
-__device__ __forceinline__ uint32_t rna_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
-}
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS, 1) factor_tc_kernel(const FactorParams p, int flush) {
@@ -574,6 +482,14 @@ int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspac
   }
   return fail(-1, "unknown dtype %d", dtype);
 }
+
+int factor_tc_run_reduce(const FactorParams& p, int tiles, cudaStream_t st) {
+  tc::factor_tc_reduce<<<dim3(tiles, 128 * 128 / (256 * 4)), 256, 0, st>>>(p);
+  SSO_LAUNCH_OK("factor_tc_reduce");
+  return 0;
+}
+
+int factor_tc_flush_setting() { return g_flush_stages & 0xFFFF; }
 
 void factor_tc_set_flush(int stages) { g_flush_stages = stages < 0 ? 0 : stages; }  // see kernel for bits 16/17
 

@@ -1,0 +1,344 @@
+// Kronecker-factor construction with TMA-fed operands: the im2col gather IS the TMA tile load.
+//
+// For 16-bit channels-contiguous inputs (channels_last activations / row-major matrices) whose
+// channel count is a multiple of 64, an operand block "64 channels of kernel position (ky,kx) for
+// a rectangle of output pixels" is exactly one 4-D tiled TMA box of the NHWC tensor:
+//     box = {64 channels, wo pixels, bh rows, bn images}, start = {c0, kx*dil - pad, oy0*stride +
+//     ky*dil - pad, n0}, element strides {1, stride_w, stride_h, 1}; padding is the out-of-bounds
+//     zero fill.  With the 128-byte swizzle the box lands in shared memory as rows of 128 bytes, which
+//     is the canonical MN-major SWIZZLE_128B operand layout of tcgen05.mma, so no thread touches
+//     the data: one producer thread issues up to four box loads per stage and the MMA warp
+//     consumes them.
+// One CTA = one lower-triangle 128x128 tile x one split of the stages; 8 accumulate warps (drain
+// TMEM every few stages into fp32 registers), 1 MMA warp, 1 producer warp.  Partial tiles go to
+// the same workspace layout as the gather kernel and are finished by the same reduction.
+// No multicast, no peer memory.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "factor_params.cuh"
+#include "tc_common.cuh"
+
+namespace sso {
+
+int factor_tc_run_reduce(const FactorParams& p, int tiles, cudaStream_t st);
+
+namespace tma {
+
+using namespace tc;
+
+constexpr int TILE = 128;
+constexpr int EPI_WARPS = 8;
+constexpr int MMA_WARP = 8;
+constexpr int PROD_WARP = 9;
+constexpr int THREADS = 320;
+constexpr int STAGES = 3;
+constexpr int KPAD_MAX = 128;
+constexpr uint32_t BLOCK_BYTES_MAX = KPAD_MAX * 128;       // one 64-column block of one stage
+constexpr uint32_t STAGE_BYTES = 4 * BLOCK_BYTES_MAX;      // A0 A1 B0 B1
+constexpr uint32_t TMEM_COLS = 256;
+
+struct Geom {
+  int bw, bh, bn;        // box in output pixels: width (= wo), rows, images
+  int kstage, kpad;      // rows per stage, padded to a multiple of 16
+  int ystages;           // stages per image group along the output height
+  int total_stages;
+  int stages_per_split;
+  int flush;
+  uint32_t fmt;          // 1 bf16, 0 fp16
+};
+
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CUtensorMap tmap) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int bi, bj;
+  tri_decode(blockIdx.x, bi, bj);
+  const bool share = (bi == bj);
+  const int split = blockIdx.y;
+  const int s_begin = split * g.stages_per_split;
+  const int s_end = min(g.total_stages, s_begin + g.stages_per_split);
+  const int nstages = max(0, s_end - s_begin);
+  const int flush = g.flush;
+  const int nchunks = ceil_div(nstages, flush);
+  int* status = p.status;
+
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto accfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto accempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accfull_bar(b), 1);
+      mbar_init(accempty_bar(b), EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // zero the operand buffers once: padding rows (kstage..kpad) and blocks past the matrix edge
+  // are never written by TMA and must read as zeros
+  for (uint32_t o = tid * 16u; o < STAGES * STAGE_BYTES; o += THREADS * 16u)
+    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(smem0 + o), "r"(0u) : "memory");
+  fence_async_smem();
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
+
+  if (warp < EPI_WARPS) {
+    // ------------------------------------------------------------------ accumulate warps
+    const int q = warp & 3, half = warp >> 2;
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+      const int b = c & 1;
+      if (!mbar_wait(accfull_bar(b), (c >> 1) & 1, status, 3)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TILE + half * 64);
+      uint32_t v0[32], v1[32];
+      tmem_ld32(taddr, v0);
+      tmem_ld32(taddr + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accempty_bar(b));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        acc[i] += __uint_as_float(v0[i]);
+        acc[32 + i] += __uint_as_float(v1[i]);
+      }
+    }
+    float* dst = p.partial + ((int64_t)blockIdx.x * p.splits + split) * (TILE * TILE) +
+                 (q * 32 + lane) * TILE + half * 64;
+#pragma unroll
+    for (int i = 0; i < 64; i += 4)
+      *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(g.fmt, 1u);
+      const int nk = g.kpad / 16;
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int slot = s % STAGES, c = s / flush, b = c & 1;
+        const bool first_of_chunk = (s % flush) == 0;
+        if (first_of_chunk && c >= 2) ok = mbar_wait(accempty_bar(b), ((c >> 1) - 1) & 1, status, 2);
+        if (!ok) break;
+        ok = mbar_wait(full_bar(slot), (s / STAGES) & 1, status, 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a0 = smem0 + slot * STAGE_BYTES;
+        const uint32_t b0 = share ? a0 : a0 + 2 * BLOCK_BYTES_MAX;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TILE);
+        for (int ks = 0; ks < nk; ++ks) {
+          // K = 16 rows = two 8-row swizzle atoms of 1024 bytes; the next 64-column block of the
+          // operand starts blk_bytes further on
+          const uint64_t ad = smem_desc_sw128(a0 + ks * 2048u, blk_bytes, 1024u);
+          const uint64_t bd = smem_desc_sw128(b0 + ks * 2048u, blk_bytes, 1024u);
+          umma<false>(d_tmem, ad, bd, idesc, (first_of_chunk && ks == 0) ? 0u : 1u);
+        }
+        umma_commit(empty_bar(slot));
+        if ((s % flush) == flush - 1 || s == nstages - 1) umma_commit(accfull_bar(b));
+      }
+    }
+  } else if (warp == PROD_WARP) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // the (up to) four 64-column blocks of this tile: A0 A1 (rows of the tile), B0 B1 (columns)
+      int bc0[4], bx[4], by[4];
+      bool bvalid[4];
+      int nvalid = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int op = e >> 1;
+        const int j0 = (op == 0 ? bi : bj) * TILE + (e & 1) * 64;
+        bvalid[e] = (j0 < p.dcols) && !(share && op == 1);
+        const int pos = j0 / p.c;
+        const int ky = pos / p.kw, kx = pos - ky * p.kw;
+        bc0[e] = j0 - pos * p.c;
+        bx[e] = kx * p.dil_w - p.pad_w;
+        by[e] = ky * p.dil_h - p.pad_h;
+        nvalid += bvalid[e] ? 1 : 0;
+      }
+      const uint32_t box_bytes = (uint32_t)g.kstage * 128u;
+      const uint64_t tmap_ptr = reinterpret_cast<uint64_t>(&tmap);
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int slot = s % STAGES;
+        if (s >= STAGES) ok = mbar_wait(empty_bar(slot), ((s / STAGES) - 1) & 1, status, 4);
+        if (!ok) break;
+        const int sg = s_begin + s;
+        const int n0 = (sg / g.ystages) * g.bn;
+        const int oy0 = (sg % g.ystages) * g.bh;
+        const uint32_t fb = full_bar(slot);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(box_bytes * nvalid) : "memory");
+        const uint32_t sb = smem0 + slot * STAGE_BYTES;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (!bvalid[e]) continue;
+          const uint32_t dst = sb + (e >> 1) * 2 * BLOCK_BYTES_MAX + (e & 1) * blk_bytes;
+          asm volatile(
+              "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+              ::"r"(dst), "l"(tmap_ptr), "r"(bc0[e]), "r"(bx[e]), "r"(oy0 * p.stride_h + by[e]), "r"(n0), "r"(fb)
+              : "memory");
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+static int round16(int v) { return (v + 15) / 16 * 16; }
+
+// Output-pixel box of one stage: full output rows, as many as fit in 128 pixels, or whole images
+// when an image has at most 128 pixels; chosen to minimise zero-padded rows.
+static bool choose_box(const FactorParams& p, Geom& g) {
+  const int wo = p.wo, ho = p.ho, hw = wo * ho;
+  if (wo > 128 || wo * p.stride_w > 256) return false;
+  g.bw = wo;
+  if (hw <= KPAD_MAX) {
+    int best = 1;
+    double best_cost = 1e30;
+    for (int bn = 1; bn * hw <= KPAD_MAX && bn <= 256; ++bn) {
+      const double cost = (double)round16(bn * hw) / bn;
+      if (cost <= best_cost + 1e-9) { best_cost = cost; best = bn; }   // ties: the larger box
+    }
+    g.bn = best; g.bh = ho; g.ystages = 1;
+  } else {
+    int best = 1;
+    double best_cost = 1e30;
+    for (int bh = 1; bh * wo <= KPAD_MAX && bh <= ho; ++bh) {
+      if (bh * p.stride_h > 256) break;
+      const double cost = (double)ceil_div(ho, bh) * round16(bh * wo);
+      if (cost <= best_cost + 1e-9) { best_cost = cost; best = bh; }   // ties: the larger box
+    }
+    g.bn = 1; g.bh = best; g.ystages = ceil_div(ho, best);
+  }
+  if (g.bh * p.stride_h > 256) return false;
+  g.kstage = g.bw * g.bh * g.bn;
+  g.kpad = round16(g.kstage);
+  g.total_stages = ceil_div(p.n, g.bn) * g.ystages;
+  return g.kpad <= KPAD_MAX;
+}
+
+static void choose_splits(int total_stages, int tiles, int& splits, int& stages_per_split) {
+  const int kSMs = 148;
+  const int most = std::max(1, total_stages / 4);
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 64 && s <= most; ++s) {
+    const int64_t ctas = (int64_t)tiles * s;
+    const double eff = (double)ctas / (double)(kSMs * ceil_div64(ctas, kSMs));
+    if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
+  }
+  stages_per_split = ceil_div(total_stages, best);
+  splits = ceil_div(total_stages, stages_per_split);
+}
+
+}  // namespace tma
+
+bool factor_tma_supported(const FactorParams& p, int dtype) {
+  if (dtype != SSO_BF16 && dtype != SSO_F16) return false;
+  if (p.sc != 1 || p.c % 64 != 0 || p.weight != nullptr || p.d != p.dcols) return false;
+  if ((reinterpret_cast<uintptr_t>(p.x) & 15) != 0) return false;
+  if (p.stride_h > 8 || p.stride_w > 8) return false;
+  if ((p.sn * 2) % 16 != 0 || (p.h > 1 && (p.sh * 2) % 16 != 0) || (p.w > 1 && (p.sw * 2) % 16 != 0)) return false;
+  tma::Geom g;
+  if (!tma::choose_box(p, g)) return false;
+  return tma::encode_fn() != nullptr;
+}
+
+int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush,
+                      cudaStream_t st) {
+  using namespace tma;
+  Geom g{};
+  SSO_CHECK_ARG(choose_box(p, g), "factor (tma): unsupported geometry");
+  const int nb = ceil_div(p.d, 128);
+  const int tiles = nb * (nb + 1) / 2;
+  choose_splits(g.total_stages, tiles, p.splits, g.stages_per_split);
+  // fit the partial tiles into the scratch the caller sized with sso_factor_workspace_bytes
+  SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= 256 + (size_t)tiles * 65536,
+                "factor workspace too small for the tensor-core path");
+  const int max_splits = (int)((workspace_bytes - 256) / ((size_t)tiles * 65536));
+  if (p.splits > max_splits) {
+    g.stages_per_split = ceil_div(g.total_stages, max_splits);
+    p.splits = ceil_div(g.total_stages, g.stages_per_split);
+  }
+  p.rows_per_split = 0;
+  g.flush = flush > 0 ? flush : 4;
+  g.fmt = (dtype == SSO_BF16) ? 1u : 0u;
+  p.status = reinterpret_cast<int*>(workspace);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+  SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), st));
+  p.perm_c = (p.kh * p.kw > 1) ? p.c : 0;
+  p.perm_kk = p.kh * p.kw;
+
+  // NHWC view of the input: dims {C, W, H, N}
+  CUtensorMap tmap;
+  const cuuint64_t gdim[4] = {(cuuint64_t)p.c, (cuuint64_t)p.w, (cuuint64_t)p.h, (cuuint64_t)p.n};
+  const cuuint64_t sw_b = (cuuint64_t)(p.w > 1 ? p.sw : p.c) * 2, sh_b = (cuuint64_t)(p.h > 1 ? p.sh : p.sn) * 2;
+  const cuuint64_t gstr[3] = {sw_b, sh_b, (cuuint64_t)p.sn * 2};
+  const cuuint32_t box[4] = {64u, (cuuint32_t)(g.bw * p.stride_w), (cuuint32_t)(g.bh * p.stride_h), (cuuint32_t)g.bn};
+  const cuuint32_t estr[4] = {1u, (cuuint32_t)p.stride_w, (cuuint32_t)p.stride_h, 1u};
+  const CUresult cr = encode_fn()(&tmap, dtype == SSO_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                  4, const_cast<void*>(p.x), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  factor_tma_kernel<<<dim3(tiles, p.splits), THREADS, smem, st>>>(p, g, tmap);
+  SSO_LAUNCH_OK("factor_tma_kernel");
+  return factor_tc_run_reduce(p, tiles, st);
+}
+
+}  // namespace sso

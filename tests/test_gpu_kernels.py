@@ -169,6 +169,51 @@ def test_factor_tcgen05_rows_matches_oracle(nat, rows, cols, bias, dtype):
     assert torch.equal(out, again)                                                  # deterministic
 
 
+# TMA-fed tensor-core path: 16-bit channels-contiguous inputs with a multiple of 64 channels
+TMA_CONVS = [
+    # n, c, h, w, k, stride, pad, dil
+    (2, 64, 6, 6, (1, 1), (1, 1), (0, 0), (1, 1)),
+    (2, 64, 6, 6, (3, 3), (1, 1), (1, 1), (1, 1)),
+    (3, 128, 9, 7, (3, 3), (1, 1), (1, 1), (1, 1)),
+    (4, 64, 14, 14, (3, 3), (2, 2), (1, 1), (1, 1)),
+    (4, 64, 14, 14, (1, 1), (2, 2), (0, 0), (1, 1)),
+    (2, 192, 20, 20, (3, 3), (1, 1), (1, 1), (1, 1)),       # d = 1728: ragged last tile
+    (2, 64, 12, 12, (5, 3), (1, 1), (2, 1), (1, 2)),        # rectangular kernel, dilation
+    (5, 64, 7, 7, (3, 3), (1, 1), (1, 1), (1, 1)),          # whole images per box, ragged image count
+    (6, 64, 30, 30, (3, 3), (1, 1), (1, 1), (1, 1)),        # 5400 rows: several splits
+]
+
+
+@pytest.mark.parametrize('cfg', TMA_CONVS)
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
+def test_factor_tma_conv_matches_oracle(nat, cfg, dtype):
+    n, c, h, w, k, s, p, d = cfg
+    x = cases.make_normal((n, c, h, w), 191 + c + h).to(dtype)
+    ref = ko.conv_factor_A(x.double(), k, s, p, d, False)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    out = torch.full(tuple(ref.shape), float('nan'), device='cuda')
+    nat.factor_im2col(xd, k, s, p, d, False, None, 1.0 / n, 0.0, out, nat.IMPL_TMA)
+    assert rel(out, ref) < FACTOR_TOL
+    assert torch.equal(out, out.t())
+    again = torch.empty_like(out)
+    nat.factor_im2col(xd, k, s, p, d, False, None, 1.0 / n, 0.0, again, nat.IMPL_TMA)
+    assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize('rows,cols', [(300, 64), (1000, 2048), (100352, 64), (77, 128)])
+def test_factor_tma_rows_matches_oracle(nat, rows, cols):
+    x = cases.make_normal((rows, cols), 5 + rows).clamp_min(-0.5).bfloat16()
+    out = torch.full((cols, cols), float('nan'), device='cuda')
+    nat.factor_rows(dev(x), False, None, 1.0 / rows, 0.0, out, nat.IMPL_TMA)
+    assert rel(out, ko.linear_factor_A(x.double(), False)) < FACTOR_TOL
+    # not eligible: ones column, fp32, channel count not a multiple of 64
+    with pytest.raises(RuntimeError):
+        nat.factor_rows(dev(x), True, None, 1.0 / rows, 0.0, torch.empty((cols + 1, cols + 1), device='cuda'),
+                        nat.IMPL_TMA)
+    with pytest.raises(RuntimeError):
+        nat.factor_rows(dev(x).float(), False, None, 1.0 / rows, 0.0, out, nat.IMPL_TMA)
+
+
 def test_factor_tcgen05_weighted_fp32_and_dispatch(nat):
     rows, cols = 300, 96
     g = cases.make_normal((rows, cols), 3)
