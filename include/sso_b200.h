@@ -42,7 +42,7 @@ const char* sso_last_error(void);
 /* kernels launched by this library since it was loaded (bookkeeping for benchmarks) */
 uint64_t sso_launch_count(void);
 /* process-wide switches: "tc_auto" / "tma_auto" (0/1: may SSO_IMPL_AUTO choose the tcgen05 kernels /
- * the TMA-fed one),
+ * the TMA-fed one), "engine_tc" (0/1: 128-wide tile phases of the engine on tcgen05 3xTF32 or fp32 FFMA),
  * "tc_flush" (stages of tensor-core accumulation between drains into fp32 registers) */
 int sso_configure(const char* key, int value);
 
@@ -181,7 +181,8 @@ typedef struct {
   float* C2;          /* optional transposed copy of the tile (mirror), NULL if unused */
   int32_t lda, ldb, ldc, ldc2;
   int32_t m, n, k;
-  uint32_t flags;     /* bit0: A transposed, bit1: B transposed */
+  uint32_t flags;     /* bit0: A transposed, bit1: B transposed, bit2: symmetric square tile (only
+                         its lower half is computed and it is mirrored inside the tile) */
   float alpha, beta;
 } sso_tile_task;
 
@@ -257,6 +258,9 @@ int64_t sso_sample_plan_create(int n_layers, const int64_t* dA, const int64_t* d
 int sso_sample_plan_run(int64_t plan, float std_scale, void* stream);
 
 int sso_plan_destroy(int64_t plan);
+/* 0, or the code of a bounded device-side wait that gave up in a tensor-core tile task of this
+ * plan (synchronises; for diagnostics) */
+int sso_plan_status(int64_t plan);
 
 /* Plan introspection (host side; used to check the task program without a GPU). */
 int sso_plan_num_phases(int64_t plan);

@@ -21,6 +21,7 @@ void factor_tc_set_flush(int stages);
 int factor_tc_flush_setting();
 bool factor_tma_supported(const FactorParams& p, int dtype);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
+extern int g_engine_tc;
 static int g_tc_auto = 1;    // whether SSO_IMPL_AUTO may pick the tcgen05 kernels
 static int g_tma_auto = 1;   // whether SSO_IMPL_AUTO may pick the TMA-fed tcgen05 kernel
 }  // namespace sso
@@ -38,6 +39,7 @@ int sso_configure(const char* key, int value) {
   const std::string k(key);
   if (k == "tc_auto") { g_tc_auto = value != 0; return 0; }
   if (k == "tma_auto") { g_tma_auto = value != 0; return 0; }
+  if (k == "engine_tc") { g_engine_tc = value != 0; return 0; }
   if (k == "tc_flush") { factor_tc_set_flush(value); return 0; }
   return fail(-1, "configure: unknown key %s", key);
 }

@@ -183,24 +183,42 @@ __global__ void __launch_bounds__(256) bn_plane_sums_vec(const T* __restrict__ t
   }
 }
 
-__global__ void bn_finish_kernel(const float* __restrict__ sx, const float* __restrict__ sg,
-                                 const float* __restrict__ weight, int n, int c, int splits_x, int splits_g,
-                                 float alpha, float beta, float* __restrict__ w_out, float* __restrict__ b_out) {
-  const int ic = blockIdx.x * blockDim.x + threadIdx.x;
-  if (ic >= c) return;
+// block = 32 channels x 8 image lanes; each thread sums the split partials of its images with
+// independent accumulators, the 8 lanes are combined in shared memory (fixed order: deterministic)
+__global__ void __launch_bounds__(256) bn_finish_kernel(const float* __restrict__ sx, const float* __restrict__ sg,
+                                                        const float* __restrict__ weight, int n, int c,
+                                                        int splits_x, int splits_g, float alpha, float beta,
+                                                        float* __restrict__ w_out, float* __restrict__ b_out) {
+  __shared__ float rw[8][33], rb[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int ic = blockIdx.x * 32 + tx;
   float aw = 0.f, ab = 0.f;
-  for (int in = 0; in < n; ++in) {
-    const float p = weight ? weight[in] : 1.f;
-    float xs = 0.f, gs = 0.f;
-    for (int q = 0; q < splits_x; ++q) xs += sx[((int64_t)in * splits_x + q) * c + ic];
-    for (int q = 0; q < splits_g; ++q) gs += sg[((int64_t)in * splits_g + q) * c + ic];
-    const float gsum = p * gs;
-    aw = fmaf(xs, gsum, aw);
-    ab += gsum;
+  if (ic < c) {
+    for (int in = ty; in < n; in += 8) {
+      const float* px = sx + (int64_t)in * splits_x * c + ic;
+      const float* pg = sg + (int64_t)in * splits_g * c + ic;
+      float x0 = 0.f, x1 = 0.f, g0 = 0.f, g1 = 0.f;
+      int q = 0;
+      for (; q + 1 < splits_x; q += 2) { x0 += px[(int64_t)q * c]; x1 += px[(int64_t)(q + 1) * c]; }
+      if (q < splits_x) x0 += px[(int64_t)q * c];
+      for (q = 0; q + 1 < splits_g; q += 2) { g0 += pg[(int64_t)q * c]; g1 += pg[(int64_t)(q + 1) * c]; }
+      if (q < splits_g) g0 += pg[(int64_t)q * c];
+      const float gsum = (weight ? weight[in] : 1.f) * (g0 + g1);
+      aw = fmaf(x0 + x1, gsum, aw);
+      ab += gsum;
+    }
   }
-  const float s = alpha / (float)n;
-  w_out[ic] = (beta == 0.f) ? s * aw : fmaf(beta, w_out[ic], s * aw);
-  if (b_out) b_out[ic] = (beta == 0.f) ? s * ab : fmaf(beta, b_out[ic], s * ab);
+  rw[ty][tx] = aw;
+  rb[ty][tx] = ab;
+  __syncthreads();
+  if (ty == 0 && ic < c) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { tw += rw[i][tx]; tb += rb[i][tx]; }
+    const float s = alpha / (float)n;
+    w_out[ic] = (beta == 0.f) ? s * tw : fmaf(beta, w_out[ic], s * tw);
+    if (b_out) b_out[ic] = (beta == 0.f) ? s * tb : fmaf(beta, b_out[ic], s * tb);
+  }
 }
 
 // pixel-range splits of the vectorised kernel for a [n, c, hw] tensor (1 when it is not used)
@@ -214,7 +232,7 @@ static int bn_vec_splits(int64_t n, int64_t c, int64_t hw, int vec) {
   const int lp = bn_vec_lanes(c, vec);
   if (lp == 0 || hw <= 1) return 1;
   const int npp = 256 / lp;
-  int64_t s = ceil_div64(3 * kSMs, n);                       // about three waves of blocks
+  int64_t s = ceil_div64(3 * kSMs / 2, n);                   // about one and a half waves of blocks
   const int64_t most = std::max<int64_t>(1, hw / (4 * npp)); // at least four pixels per lane
   if (s > most) s = most;
   return (int)std::max<int64_t>(1, s);
@@ -371,7 +389,7 @@ int sso_bn_diag_finish(const float* sx, const float* sg, const float* sample_wei
                        int splits_x, int splits_g, float alpha, float beta, float* w_out, float* b_out,
                        void* stream) {
   SSO_CHECK_ARG(sx && sg && w_out && n > 0 && c > 0 && splits_x >= 1 && splits_g >= 1, "bn_diag_finish: bad argument");
-  bn_finish_kernel<<<(unsigned)ceil_div64(c, 128), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  bn_finish_kernel<<<(unsigned)ceil_div64(c, 32), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       sx, sg, sample_weight, (int)n, (int)c, splits_x, splits_g, alpha, beta, w_out, b_out);
   SSO_LAUNCH_OK("bn_finish_kernel");
   return 0;

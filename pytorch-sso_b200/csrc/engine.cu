@@ -21,6 +21,9 @@
 
 namespace sso {
 
+int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
+int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
+
 constexpr int NB = 64;  // algorithmic block size of the factorisations
 
 // ------------------------------------------------------------------------------------------
@@ -125,11 +128,13 @@ __global__ void __launch_bounds__(256) tile_task_kernel(const sso_tile_task* __r
     for (int j = 0; j < MT; ++j) {
       const int c = TileCore<MT>::col_of(tx, j);
       if (c >= t.n) continue;
+      if ((t.flags & 4u) && c > r) continue;   // symmetric tile: lower half computed, mirrored below
       float* o = t.C + (int64_t)r * t.ldc + c;
       float v = t.alpha * acc[i][j];
       if (t.beta != 0.f) v = fmaf(t.beta, *o, v);
       *o = v;
       if (t.C2) t.C2[(int64_t)c * t.ldc2 + r] = v;
+      if ((t.flags & 4u) && c < r) t.C[(int64_t)c * t.ldc + r] = v;
     }
   }
 }
@@ -137,63 +142,109 @@ __global__ void __launch_bounds__(256) tile_task_kernel(const sso_tile_task* __r
 // ------------------------------------------------------------------------------------------
 // diagonal block: Cholesky of a (<=64)x(<=64) SPD block and the inverse of its factor
 // ------------------------------------------------------------------------------------------
+// The 64x64 block lives in registers: thread (ty, tx) of a 16x16 grid owns the 4x4 sub-block at
+// rows 4ty.., columns 4tx...  Both the right-looking Cholesky and the right-looking triangular
+// inverse then cost one __syncthreads per column: the owners of column j publish it (unscaled,
+// pivot included) in a double-buffered shared vector, everybody applies the rank-1 update to its
+// registers.  Padding rows/columns (block smaller than 64) behave as an identity block.
 __global__ void __launch_bounds__(256) diag_block_kernel(const DiagRec* __restrict__ recs,
                                                          int* __restrict__ info) {
-  __shared__ float S[NB][NB + 1];
-  __shared__ float Inv[NB][NB + 1];
-  __shared__ float diag_inv[NB];
+  __shared__ float Ls[NB][NB + 1];      // finished factor, column by column
+  __shared__ float colbuf[2][NB];
+  __shared__ float rowbuf[2][NB];
+  __shared__ float dinv[NB];
   const DiagRec rec = recs[blockIdx.x];
   const int tid = threadIdx.x, n = rec.size;
-  for (int e = tid; e < NB * NB; e += 256) {
-    const int r = e / NB, c = e % NB;
-    float v = (r == c) ? 1.f : 0.f;  // identity padding keeps the tail harmless
-    if (r < n && c < n) v = (c <= r) ? rec.L[(int64_t)r * rec.ld_l + c] : 0.f;
-    S[r][c] = v;
+  const int ty = tid >> 4, tx = tid & 15, r0 = ty * 4, c0 = tx * 4;
+  float a[4][4], x[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = r0 + i, c = c0 + j;
+      float v = (r == c) ? 1.f : 0.f;
+      if (r < n && c < n) v = (c <= r) ? rec.L[(int64_t)r * rec.ld_l + c] : 0.f;
+      a[i][j] = v;
+      x[i][j] = (r == c) ? 1.f : 0.f;
+    }
+  // ---- Cholesky
+  for (int j = 0; j < NB; ++j) {
+    const int jb = j >> 2, jj = j & 3;
+    if (tx == jb) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (q == jj && r0 + i >= j) colbuf[j & 1][r0 + i] = a[i][q];
+    }
+    __syncthreads();
+    float pv = colbuf[j & 1][j];
+    if (!(pv > 0.f)) {   // non-positive or NaN pivot: record once, continue with 1
+      if (tid == 0 && info && j < n) atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + j + 1);
+      pv = 1.f;
+    }
+    const float inv = 1.f / pv, rs = rsqrtf(pv);
+    float cr[4], cc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      cr[i] = colbuf[j & 1][r0 + i];
+      cc[i] = colbuf[j & 1][c0 + i];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = r0 + i, c = c0 + q;
+        if (r > j && c > j && c <= r) a[i][q] -= cr[i] * cc[q] * inv;
+        if (c == j && r >= j) {          // finish column j of the factor
+          const float l = (r == j) ? sqrtf(pv) : a[i][q] * rs;
+          a[i][q] = l;
+          Ls[r][j] = l;
+        }
+      }
+    if (tid == 0) dinv[j] = rs;
   }
   __syncthreads();
-  // right-looking column Cholesky on the lower triangle
-  for (int j = 0; j < n; ++j) {
-    if (tid == 0) {
-      float pv = S[j][j];
-      if (!(pv > 0.f)) {  // non-positive or NaN pivot: record once, keep going with 1
-        if (info) atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + j + 1);
-        pv = 1.f;
-      }
-      const float s = sqrtf(pv);
-      S[j][j] = s;
-      diag_inv[j] = 1.f / s;
+  // ---- inverse of the factor: X starts as I; for k: row k of X /= L_kk, rows r > k -= L_rk * row k
+  for (int k = 0; k < NB; ++k) {
+    const int kb = k >> 2, kk = k & 3;
+    if (ty == kb) {
+      const float d = dinv[k];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          if (i == kk) {
+            x[i][q] *= d;
+            rowbuf[k & 1][c0 + q] = x[i][q];
+          }
     }
     __syncthreads();
-    const float dj = diag_inv[j];
-    for (int r = j + 1 + tid; r < n; r += 256) S[r][j] *= dj;
-    __syncthreads();
-    // trailing update of the lower triangle: S[r][c] -= S[r][j]*S[c][j], j < c <= r < n
-    const int rem = n - j - 1;
-    for (int e = tid; e < rem * rem; e += 256) {
-      const int r = j + 1 + e / rem, c = j + 1 + e % rem;
-      if (c <= r) S[r][c] -= S[r][j] * S[c][j];
-    }
-    __syncthreads();
-  }
-  // inverse of the lower-triangular factor, one column per thread (forward substitution)
-  if (tid < NB) {
-    const int c = tid;
-    for (int r = 0; r < NB; ++r) Inv[r][c] = 0.f;
-    if (c < n) {
-      Inv[c][c] = diag_inv[c];
-      for (int r = c + 1; r < n; ++r) {
-        float s = 0.f;
-        for (int k = c; k < r; ++k) s = fmaf(S[r][k], Inv[k][c], s);
-        Inv[r][c] = -s * diag_inv[r];
+    if (c0 <= k) {
+      float xr[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) xr[q] = rowbuf[k & 1][c0 + q];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = r0 + i;
+        if (r > k) {
+          const float l = Ls[r][k];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) x[i][q] -= l * xr[q];
+        }
       }
     }
   }
-  __syncthreads();
-  for (int e = tid; e < n * n; e += 256) {
-    const int r = e / n, c = e % n;
-    rec.L[(int64_t)r * rec.ld_l + c] = (c <= r) ? S[r][c] : 0.f;
-    rec.Linv[(int64_t)r * rec.ld_inv + c] = (c <= r) ? Inv[r][c] : 0.f;
-  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = r0 + i, c = c0 + q;
+      if (r < n && c < n) {
+        rec.L[(int64_t)r * rec.ld_l + c] = (c <= r) ? a[i][q] : 0.f;
+        rec.Linv[(int64_t)r * rec.ld_inv + c] = (c <= r) ? x[i][q] : 0.f;
+      }
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -264,6 +315,7 @@ struct Plan {
   MatRec* d_mats = nullptr;
   float* d_traces = nullptr;
   float* d_shift = nullptr;
+  int* d_status = nullptr;   // set by a tensor-core tile task whose wait gave up
   int first_scaled_task = -1, n_scaled_tasks = 0;  // sample plan: tasks whose alpha is std_scale
   bool host_only = false;
 };
@@ -291,12 +343,13 @@ struct Builder {
   explicit Builder(Plan& plan, std::vector<sso_phase>* ph) : p(plan), phases(ph) {}
   int task_begin() const { return (int)p.tasks.size(); }
   void gemm(const float* A, int lda, bool ta, const float* B, int ldb, bool tb, float* C, int ldc,
-            int m, int n, int k, float alpha, float beta, float* C2 = nullptr, int ldc2 = 0) {
+            int m, int n, int k, float alpha, float beta, float* C2 = nullptr, int ldc2 = 0,
+            bool symmetric = false) {
     sso_tile_task t;
     t.A = A; t.B = B; t.C = C; t.C2 = C2;
     t.lda = lda; t.ldb = ldb; t.ldc = ldc; t.ldc2 = ldc2;
     t.m = m; t.n = n; t.k = k;
-    t.flags = (ta ? 1u : 0u) | (tb ? 2u : 0u);
+    t.flags = (ta ? 1u : 0u) | (tb ? 2u : 0u) | (symmetric ? 4u : 0u);
     t.alpha = alpha; t.beta = beta;
     p.tasks.push_back(t);
   }
@@ -366,7 +419,7 @@ static void emit_lauum(Builder& b, const std::vector<Mat>& ms) {
           // rows k >= i*tile of Li contribute: A = Li[k, i-cols]^T, B = Li[k, j-cols]
           const float* A = m.Li + (int64_t)i * tile * m.d + (int64_t)i * tile;
           const float* B = m.Li + (int64_t)i * tile * m.d + (int64_t)j * tile;
-          b.gemm(A, m.d, true, B, m.d, false, C, m.d, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.d);
+          b.gemm(A, m.d, true, B, m.d, false, C, m.d, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.d, i == j);
         }
     }
     b.end_phase(pass == 0 ? 0 : 1, first, b.task_begin() - first);
@@ -386,7 +439,7 @@ static void emit_copy(Builder& b, const float* src, float* dst, int d, int mat, 
 static size_t plan_table_bytes(size_t tasks, size_t diags, size_t copies, size_t mats) {
   return align_up(tasks * sizeof(sso_tile_task)) + align_up(diags * sizeof(DiagRec)) +
          align_up(copies * sizeof(CopyRec)) + align_up(mats * sizeof(MatRec)) +
-         2 * align_up(mats * sizeof(float));
+         2 * align_up(mats * sizeof(float)) + 256;
 }
 
 static int upload(Plan& p, void* dev_mem, size_t dev_bytes) {
@@ -399,7 +452,9 @@ static int upload(Plan& p, void* dev_mem, size_t dev_bytes) {
   p.d_copies = reinterpret_cast<CopyRec*>(q); q += align_up(p.copies.size() * sizeof(CopyRec));
   p.d_mats = reinterpret_cast<MatRec*>(q); q += align_up(p.mats.size() * sizeof(MatRec));
   p.d_traces = reinterpret_cast<float*>(q); q += align_up(p.mats.size() * sizeof(float));
-  p.d_shift = reinterpret_cast<float*>(q);
+  p.d_shift = reinterpret_cast<float*>(q); q += align_up(p.mats.size() * sizeof(float));
+  p.d_status = reinterpret_cast<int*>(q);
+  SSO_CUDA_OK(cudaMemset(p.d_status, 0, 256));
   if (!p.tasks.empty())
     SSO_CUDA_OK(cudaMemcpy(p.d_tasks, p.tasks.data(), p.tasks.size() * sizeof(sso_tile_task), cudaMemcpyHostToDevice));
   if (!p.diags.empty())
@@ -415,7 +470,14 @@ static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* 
   for (const sso_phase& ph : phases) {
     switch (ph.kind) {
       case 0: tile_task_kernel<4><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first); break;
-      case 1: tile_task_kernel<8><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first); break;
+      case 1:
+        if (g_engine_tc) {
+          const int rc = launch_tile_tasks_tc(p.d_tasks + ph.first, ph.count, p.d_status, st);
+          if (rc) return rc;
+          continue;
+        }
+        tile_task_kernel<8><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first);
+        break;
       case 2: diag_block_kernel<<<ph.count, 256, 0, st>>>(p.d_diags + ph.first, info); break;
       case 3: copy_kernel<<<ph.count, 256, 0, st>>>(p.d_copies + ph.first, p.d_shift); break;
       default: return fail(-1, "bad phase kind %d", ph.kind);
@@ -783,6 +845,14 @@ int sso_plan_copy_copy_recs(int64_t plan, sso_copy_rec* out, int capacity) {
   const int n = std::min(capacity, (int)p->copies.size());
   std::copy(p->copies.begin(), p->copies.begin() + n, out);
   return n;
+}
+
+int sso_plan_status(int64_t plan) {
+  Plan* p = find_plan(plan);
+  SSO_CHECK_ARG(p != nullptr && !p->host_only && p->d_status != nullptr, "unknown or host-only plan");
+  int v = 0;
+  SSO_CUDA_OK(cudaMemcpy(&v, p->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  return v;
 }
 
 int sso_run_tile_tasks(const sso_tile_task* tasks_dev, int count, int tile, void* stream) {

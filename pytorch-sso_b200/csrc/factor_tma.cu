@@ -253,6 +253,9 @@ static bool choose_box(const FactorParams& p, Geom& g) {
     double best_cost = 1e30;
     for (int bh = 1; bh * wo <= KPAD_MAX && bh <= ho; ++bh) {
       if (bh * p.stride_h > 256) break;
+      // the box must not reach past the last output row: with a kernel offset or padding the
+      // input rows of such phantom pixels can lie inside the image and would be counted
+      if (ho % bh != 0) continue;
       const double cost = (double)ceil_div(ho, bh) * round16(bh * wo);
       if (cost <= best_cost + 1e-9) { best_cost = cost; best = bh; }   // ties: the larger box
     }

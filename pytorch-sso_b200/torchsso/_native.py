@@ -83,6 +83,7 @@ SIGNATURES = {
     'sso_sample_plan_create': (c_i64, [c_i32] + [c_vp] * 9 + [c_sz, c_i32]),
     'sso_sample_plan_run': (c_i32, [c_i64, c_f32, c_vp]),
     'sso_plan_destroy': (c_i32, [c_i64]),
+    'sso_plan_status': (c_i32, [c_i64]),
     'sso_plan_num_phases': (c_i32, [c_i64]),
     'sso_plan_get_phase': (c_i32, [c_i64, c_i32, c_vp]),
     'sso_plan_num_tasks': (c_i32, [c_i64]),

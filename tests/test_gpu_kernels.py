@@ -181,6 +181,8 @@ TMA_CONVS = [
     (2, 64, 12, 12, (5, 3), (1, 1), (2, 1), (1, 2)),        # rectangular kernel, dilation
     (5, 64, 7, 7, (3, 3), (1, 1), (1, 1), (1, 1)),          # whole images per box, ragged image count
     (6, 64, 30, 30, (3, 3), (1, 1), (1, 1), (1, 1)),        # 5400 rows: several splits
+    (3, 64, 14, 14, (3, 3), (1, 1), (1, 1), (1, 1)),        # 196 pixels per image: box rows must divide 14
+    (2, 64, 13, 13, (3, 3), (1, 1), (1, 1), (1, 1)),        # prime height: one output row per box
 ]
 
 

@@ -53,6 +53,8 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
                 val = alpha * (A.astype(np.float64) @ B.astype(np.float64))
                 if t.beta != 0:
                     val = val + t.beta * Cv
+                if t.flags & 4:
+                    val = np.tril(val) + np.tril(val, -1).T
                 results.append((t, val.astype(np.float32)))
             # tasks of one phase are independent: apply all writes after all reads
             for t, val in results:
