@@ -96,7 +96,7 @@ def synthetic_batch(batch, num_classes, seed, device='cpu', pin=False):
     x = torch.randn((batch, 3, 224, 224), generator=g)
     y = torch.randint(0, num_classes, (batch,), generator=g)
     if pin:
-        x, y = x.pin_memory(), y.pin_memory()
+        x, y = x.contiguous(memory_format=torch.channels_last).pin_memory(), y.pin_memory()
     return x.to(device), y.to(device)
 
 
@@ -245,9 +245,23 @@ def run_gpu_arm(args):
     x_pin, y_pin = pinned[0]
     state = {'step': 0}
 
+    # The closure reads its batch from fixed device tensors so that it can be captured once into a
+    # CUDA graph (forward, sampling backward, loss backward and all curvature kernels of the hooks)
+    # and replayed; every step first copies its batch into them.
+    x_static = torch.empty_like(resident[0][0])
+    y_static = torch.empty_like(resident[0][1])
+    x_static.copy_(resident[0][0]); y_static.copy_(resident[0][1])
+    closure = fisher_closure(torchsso, opt, model, x_static, y_static)
+    eager_closure = closure
+    if args.graph:
+        opt.update_inv = True
+        opt.step(closure=closure)            # eager first step: builds pools, plans, scratch
+        closure = torchsso.utils.GraphedClosure(opt, closure)
+        state['step'] = 1
+
     def one_step(x, y):
-        # Fisher closure with the forward under autocast
-        closure = fisher_closure(torchsso, opt, model, x, y)
+        x_static.copy_(x, non_blocking=True)
+        y_static.copy_(y, non_blocking=True)
         opt.update_inv = (state['step'] % INV_INTERVAL == 0)
         loss, _ = opt.step(closure=closure)
         state['step'] += 1
@@ -262,14 +276,12 @@ def run_gpu_arm(args):
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = nat.launch_count()
+        r0 = closure.replays if args.graph else 0
         ev0.record()
         last = None
         for i in range(nsteps):
             if e2e:
-                xp, yp = pinned[i % NB]
-                x = xp.to(dev, non_blocking=True).contiguous(memory_format=torch.channels_last)
-                y = yp.to(dev, non_blocking=True)
-                last = one_step(x, y).item()
+                last = one_step(*pinned[i % NB]).item()      # host -> device copy inside one_step
             else:
                 last = one_step(*resident[i % NB])
         ev1.record()
@@ -279,23 +291,35 @@ def run_gpu_arm(args):
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        return ms, nat.launch_count() - l0, last
+        launches = nat.launch_count() - l0
+        if args.graph:      # kernels inside the replayed graph are not seen by the host-side counter
+            launches += (closure.replays - r0) * closure.library_kernels_per_replay
+        return ms, launches, float(last)
 
     # warm-up (also builds plans and cuDNN algorithm choices); first step inverts
     for i in range(max(args.warmup, 3)):
         one_step(*resident[i % NB])
     # align the inverse schedule so that every timed window of K steps sees K/10 inverses
     state['step'] = 1
-    nat.FACTOR_TIMING = []
     with ClockSampler(local_rank) as clocks:
         ms, launches, last_loss = timed(args.steps, e2e=False)
+    torch.cuda.synchronize()
+    state['step'] = 1
+    ms_e2e, _, last_e2e = timed(args.steps, e2e=True)
+    # Per-kernel timing of the dominant kernel (factor construction): CUDA events around every
+    # factor launch, on the launching stream, over a few more steps of the same workload issued
+    # eagerly (a replayed graph has no host-side call to bracket).
+    nat.FACTOR_TIMING = []
+    probe_steps = 3
+    for i in range(probe_steps):
+        x_static.copy_(resident[i % NB][0]); y_static.copy_(resident[i % NB][1])
+        opt.update_inv = False
+        opt.step(closure=eager_closure)
     torch.cuda.synchronize()
     ft = nat.FACTOR_TIMING
     nat.FACTOR_TIMING = None
     f_ms = sum(a.elapsed_time(b) for a, b, _, _ in ft)
     f_flops = sum(f for _, _, f, _ in ft)
-    state['step'] = 1
-    ms_e2e, _, last_e2e = timed(args.steps, e2e=True)
 
     if rank != 0:
         if world > 1:
@@ -312,6 +336,7 @@ def run_gpu_arm(args):
         'config': {'workload': 'resnet50_kfac_b32', 'batch_per_gpu': B, 'global_batch': B * world,
                    'image': '3x224x224', 'curvature': 'Fisher MC(1): Kron conv/linear + diag BN',
                    'factors_every': 1, 'inverse_every': INV_INTERVAL,
+                   'closure': 'CUDA graph replay' if args.graph else 'eager',
                    'parallelism': 'dp%d, factors reduce-scattered to owners' % world if world > 1 else 'single',
                    'l2_policy': 'per-step inputs (%.0f MB activations + 615 MB factor pools) exceed the 126 MB L2'
                                 % (B * 3 * 224 * 224 * 2 / 1e6),
@@ -325,7 +350,7 @@ def run_gpu_arm(args):
                      'achieved': achieved_tf, 'peak': tf_peak, 'unit': 'TFLOP/s',
                      'frac': achieved_tf / tf_peak if tf_peak else None, 'traffic': None,
                      'peak_source': peak_src + ' (bf16 dense, sustained)',
-                     'launches': len(ft), 'total_ms': f_ms,
+                     'launches': len(ft), 'total_ms': f_ms, 'measured_over_steps': probe_steps,
                      'flops_rule': '2*rows*d^2 per factor (what the reference einsum performs)'},
     }
     if world == 1 and not args.no_cpu_baseline:
@@ -357,6 +382,8 @@ def main():
     ap.add_argument('--batch', type=int, default=32, help='images per GPU')
     ap.add_argument('--cpu-batch', type=int, default=4, help='batch of the bounded CPU sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-graph', dest='graph', action='store_false',
+                    help='issue the closure eagerly instead of replaying a captured CUDA graph')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference_arm(args)

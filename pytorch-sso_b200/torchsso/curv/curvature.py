@@ -124,8 +124,10 @@ class Curvature(object):
     def forward_postprocess(self, module, input, output):
         assert self._module is module
         x = input[0].detach()
-        module.data_input = x
-        module.data_output = output
+        d = module.__dict__          # plain attributes; nn.Module.__setattr__ is slow on this hot path
+        d['data_input'] = x
+        d['data_output'] = output.detach()   # detached: keeping the graph alive between steps would
+                                             # pin last step's activations and autograd nodes
         self.update_in_forward(output.detach() if self._is_norm else x)
         if output.requires_grad and torch.is_grad_enabled():
             output.register_hook(self._backward_hook)
@@ -135,7 +137,7 @@ class Curvature(object):
 
     def backward_postprocess(self, module, grad_input, grad_output):
         g = grad_output[0].detach()
-        module.grad_output = g
+        module.__dict__['grad_output'] = g
         # the n^2 rescale that undoes the mean reduction of the loss
         # (torchsso/curv/curvature.py:151-155) is folded into the kernels' alpha
         self.update_in_backward(g)

@@ -15,7 +15,9 @@ _APPROX_TYPE_MC = 'mc'
 def sample_targets(prob: torch.Tensor, num_mc: int) -> torch.Tensor:
     """[num_mc, n] class indices drawn from the model's predictive distribution.
     A module-level function so that a parity harness can substitute a deterministic draw."""
-    return torch.distributions.Categorical(prob).sample((num_mc,))
+    # same draw as torch.distributions.Categorical(prob).sample((num_mc,)) without the argument
+    # validation, which synchronises with the host (and so cannot be captured in a CUDA graph)
+    return torch.multinomial(prob, num_mc, replacement=True).t()
 
 
 def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num_mc=1):

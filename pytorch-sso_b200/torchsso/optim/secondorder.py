@@ -345,6 +345,12 @@ class SecondOrderOptimizer(Optimizer):
 
     def update_preprocess(self, group, target='params', grad_type='raw'):
         assert grad_type in ['raw', 'preconditioned'], 'Invalid grad type: {}.'.format(grad_type)
+        raw = grad_type == 'raw'
+        if not ((raw and group['l2_reg'] != 0) or (not raw and group['weight_decay'] != 0) or
+                (group['momentum'] != 0 and group['momentum_type'] == grad_type) or
+                (group['grad_ema_decay'] != 1 and group['grad_ema_type'] == grad_type) or
+                (not raw and group['bias_correction']) or (group['lars'] and group['lars_type'] == grad_type)):
+            return      # nothing to apply for this group at this stage
         params = [p for p in group[target] if p.grad is not None]
         if not params:
             return

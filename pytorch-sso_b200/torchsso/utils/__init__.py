@@ -2,3 +2,4 @@ from torchsso.utils.logger import Logger  # noqa: F401
 from torchsso.utils.linalg import inv, cholesky  # noqa: F401
 from torchsso.utils.accumulator import TensorAccumulator  # noqa: F401
 from torchsso.utils.communicator import KFACCommunicator, create_communicator, assign_owners  # noqa: F401
+from torchsso.utils.graphs import GraphedClosure  # noqa: F401

@@ -225,3 +225,44 @@ def test_conv_stem_with_three_channels_channels_last(torchsso_mod):
         conv(x).square().mean().backward()
         ref = ko.conv_factor_A(x.cpu().double(), (7, 7), (2, 2), (3, 3), (1, 1), bias)
         assert rel(curv.data[0], ref) < 1e-5
+
+
+def test_graphed_closure_equals_eager(torchsso_mod):
+    """Replaying the closure from a CUDA graph (hooks' curvature kernels included) must give the
+    same parameters as issuing it eagerly."""
+    torchsso = torchsso_mod
+
+    def run(graphed):
+        model = cases.make_model('tiny_convnet', seed=1).cuda()
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON, {'ema_decay': 0.95, 'damping': 1e-3}, lr=1e-2)
+        xs = torch.empty((6, 3, 8, 8), device='cuda')
+        ys = torch.empty((6,), dtype=torch.int64, device='cuda')
+
+        def closure():
+            opt.zero_grad()
+            o = model(xs)
+            loss = F.cross_entropy(o, ys)
+            loss.backward()
+            return loss, o
+        x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100)
+        xs.copy_(x); ys.copy_(y)
+        step_closure = closure
+        if graphed:
+            # batch-norm running statistics advance during warm-up and capture: snapshot / restore
+            state = {k: v.clone() for k, v in model.state_dict().items()}
+            step_closure = torchsso.utils.GraphedClosure(opt, closure)
+            model.load_state_dict(state)
+            assert step_closure.library_kernels_per_replay > 0
+        losses = []
+        for t in range(3):
+            x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100 + t)
+            xs.copy_(x); ys.copy_(y)
+            loss, _ = opt.step(closure=step_closure)
+            losses.append(loss.item())
+        return losses, [p.detach().clone() for p in model.parameters()]
+
+    l0, p0 = run(False)
+    l1, p1 = run(True)
+    assert max(abs(a - b) for a, b in zip(l0, l1)) < 1e-5
+    for a, b in zip(p0, p1):
+        assert rel(b, a.cpu().numpy()) < 1e-5
