@@ -354,7 +354,7 @@ def run_gpu_arm(args):
                      'flops_rule': '2*rows*d^2 per factor (what the reference einsum performs)'},
     }
     if world == 1 and not args.no_cpu_baseline:
-        val, cores, sample, _ = cpu_port_images_per_sec(args.cpu_batch, 1)
+        val, cores, sample, _ = cpu_port_images_per_sec(args.cpu_batch, 2)
         line['cpu_baseline'] = {'value': val, 'unit': 'images/sec', 'cores': cores, 'kind': 'port',
                                 'sample': sample}
     print(json.dumps(line), flush=True)
@@ -380,7 +380,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--batch', type=int, default=32, help='images per GPU')
-    ap.add_argument('--cpu-batch', type=int, default=4, help='batch of the bounded CPU sample')
+    ap.add_argument('--cpu-batch', type=int, default=16, help='batch of the bounded CPU sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-graph', dest='graph', action='store_false',
                     help='issue the closure eagerly instead of replaying a captured CUDA graph')

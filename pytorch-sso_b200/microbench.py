@@ -1,0 +1,230 @@
+"""Operator-level microbenchmarks of libsso_b200 (one JSON line per case).
+
+    python pytorch-sso_b200/microbench.py factor   [--dtype bf16|fp32] [--case I] [--iters K]
+    python pytorch-sso_b200/microbench.py rows     [--case I]      fp32 X^T X, d in 64..4608
+    python pytorch-sso_b200/microbench.py inverse  [--case I]      damped SPD inverse, d in 64..4608
+    python pytorch-sso_b200/microbench.py precond  [--case I]      G^-1 dW A^-1
+    python pytorch-sso_b200/microbench.py stream                   EMA / axpby / BN plane sums
+    torchrun ... pytorch-sso_b200/microbench.py collective         factor exchange sweep (N > 1)
+
+Inputs are seeded N(0,1) tensors created on the device; every case moves more bytes than the
+L2 holds or is timed over launches on rotating buffers, and times are CUDA-event times on
+the launching stream after warm-up.  ``--case I`` runs a single case (what a profiler capture
+wants); without it the whole suite runs.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import torch  # noqa: E402
+
+from torchsso import _native as nat  # noqa: E402
+
+# (c, h, w, k, stride, pad) of the distinct ResNet-50 convolutions' A factors at 224x224 input
+R50_CONVS = [
+    (64, 56, 56, 1, 1, 0), (64, 56, 56, 3, 1, 1), (256, 56, 56, 1, 1, 0), (128, 56, 56, 3, 2, 1),
+    (128, 28, 28, 3, 1, 1), (512, 28, 28, 1, 1, 0), (256, 28, 28, 3, 2, 1), (256, 14, 14, 3, 1, 1),
+    (1024, 14, 14, 1, 1, 0), (512, 14, 14, 3, 2, 1), (512, 7, 7, 3, 1, 1), (2048, 7, 7, 1, 1, 0),
+]
+DIMS = [64, 256, 576, 1152, 2304, 4608]
+# (d_A, d_G) of representative ResNet-50 layers
+R50_PAIRS = [(576, 64), (256, 64), (1152, 128), (2304, 256), (1024, 256), (4608, 512), (2048, 512), (2049, 1000)]
+
+
+def timeit(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), '..', 'MEASURED_PEAKS.json')
+    try:
+        p = json.load(open(path))
+        return float(p['hbm_gbs']), float(p['bf16_tflops'])
+    except Exception:
+        return 6650.0, 1590.0
+
+
+def select(cases, idx):
+    return list(enumerate(cases)) if idx is None else [(idx, cases[idx])]
+
+
+def suite_factor(args):
+    dt = {'bf16': torch.bfloat16, 'fp16': torch.float16, 'fp32': torch.float32}[args.dtype]
+    n = args.batch
+    _, tf_peak = peaks()
+    for i, (c, h, w, k, s, p) in select(R50_CONVS, args.case):
+        g = torch.Generator(device='cuda').manual_seed(i)
+        xs = [torch.randn((n, c, h, w), device='cuda', generator=g).to(dt).contiguous(
+            memory_format=torch.channels_last) for _ in range(args.rotate)]
+        d = c * k * k
+        out = torch.empty((d, d), device='cuda')
+        ho, wo = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+        rows = n * ho * wo
+        state = {'i': 0}
+
+        def run():
+            x = xs[state['i'] % len(xs)]
+            state['i'] += 1
+            nat.factor_im2col(x, (k, k), (s, s), (p, p), (1, 1), False, None, 1.0 / n, 0.0, out, args.impl)
+        ms = timeit(run, args.iters)
+        tf = 2.0 * rows * d * d / ms / 1e9
+        emit(suite='factor', case=i, dtype=args.dtype, conv=dict(n=n, c=c, h=h, w=w, k=k, stride=s, pad=p),
+             rows=rows, d=d, ms=round(ms, 4), tflops=round(tf, 1), frac_of_measured_bf16=round(tf / tf_peak, 3),
+             input_gbs=round(xs[0].numel() * xs[0].element_size() / ms / 1e6, 1))
+
+
+def suite_rows(args):
+    _, tf_peak = peaks()
+    for i, d in select(DIMS, args.case):
+        rows = args.rows if args.rows else max(8192, min(802816, (1 << 31) // (4 * d)))
+        g = torch.Generator(device='cuda').manual_seed(i)
+        x = torch.randn((rows, d), device='cuda', generator=g)
+        out = torch.empty((d, d), device='cuda')
+        ms = timeit(lambda: nat.factor_rows(x, False, None, 1.0 / rows, 0.0, out, args.impl), args.iters)
+        tf = 2.0 * rows * d * d / ms / 1e9
+        emit(suite='rows', case=i, dtype='fp32 (3xTF32)', rows=rows, d=d, ms=round(ms, 4), tflops=round(tf, 1),
+             tensor_tflops=round(3 * tf, 1), frac_of_measured_bf16=round(3 * tf / tf_peak, 3),
+             input_gbs=round(4.0 * rows * d / ms / 1e6, 1))
+
+
+def spd(d, seed):
+    g = torch.Generator(device='cuda').manual_seed(seed)
+    x = torch.randn((4 * d, d), device='cuda', generator=g)
+    return (x.t() @ x) / x.shape[0]
+
+
+def suite_inverse(args):
+    for i, d in select(DIMS, args.case):
+        A, G = spd(d, 2 * i), spd(d, 2 * i + 1)
+        src = [A, G]
+        dst = [torch.empty_like(m) for m in src]
+        work = [torch.empty_like(m) for m in src]
+        plan = nat.kron_plan([d, d], src, dst, work, None, [1, 0], [0, 1], torch.device('cuda'))
+        damp = torch.full((2,), math.sqrt(1e-3), device='cuda')
+        info = torch.zeros(4, dtype=torch.int32, device='cuda')
+        ms = timeit(lambda: nat.kron_plan_run(plan, damp, info, True, False), args.iters)
+        assert int(info.abs().sum()) == 0
+        eye = torch.eye(d, device='cuda')
+        r = math.sqrt(1e-3)
+        pi = math.sqrt((A.trace() / d / (G.trace() / d)).item())
+        resid = ((A + r * pi * eye) @ dst[0] - eye).norm().item() / math.sqrt(d)
+        emit(suite='inverse', case=i, d=d, matrices=2, ms=round(ms, 4),
+             gflops=round(2 * d ** 3 / ms / 1e6, 1), residual=float('%.3g' % resid))
+
+
+def suite_precond(args):
+    for i, (da, dg) in select(R50_PAIRS, args.case):
+        Ai, Gi = spd(da, 50 + i), spd(dg, 80 + i)
+        g = torch.Generator(device='cuda').manual_seed(i)
+        gw = torch.randn((dg, da), device='cuda', generator=g) * 0.1
+        tmp = torch.empty(dg * da, device='cuda')
+        plan = nat.precond_plan([da], [dg], [Ai], [Gi], [gw], [None], [tmp], torch.device('cuda'))
+        ms = timeit(lambda: nat.precond_plan_run(plan), args.iters)
+        fl = 2.0 * dg * da * (da + dg)
+        emit(suite='precond', case=i, dA=da, dG=dg, ms=round(ms, 4), tflops=round(fl / ms / 1e9, 2))
+
+
+def suite_stream(args):
+    hbm, _ = peaks()
+    n = 1 << 27                                # 512 MiB per fp32 array
+    a = torch.randn(n, device='cuda')
+    b = torch.randn(n, device='cuda')
+    ms = timeit(lambda: nat.ema_update(a, b, 0.95, False), args.iters)
+    emit(suite='stream', kernel='ema_update', bytes=12 * n, ms=round(ms, 4), gbs=round(12.0 * n / ms / 1e6, 1),
+         frac_of_measured_hbm=round(12.0 * n / ms / 1e6 / hbm, 3))
+    ms = timeit(lambda: nat.axpby(a, b, 0.5, 0.5), args.iters)
+    emit(suite='stream', kernel='axpby', bytes=12 * n, ms=round(ms, 4), gbs=round(12.0 * n / ms / 1e6, 1),
+         frac_of_measured_hbm=round(12.0 * n / ms / 1e6 / hbm, 3))
+    x = torch.randn((128, 256, 56, 56), device='cuda').to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    layout = nat.bn_plane_layout(x)
+    out = torch.empty((layout[2] * 128 * 256,), device='cuda')
+    ms = timeit(lambda: nat.bn_plane_sums(x, False, None, None, out, layout), args.iters)
+    nb = x.numel() * 2
+    emit(suite='stream', kernel='bn_plane_sums', bytes=nb, ms=round(ms, 4), gbs=round(nb / ms / 1e6, 1),
+         frac_of_measured_hbm=round(nb / ms / 1e6 / hbm, 3))
+
+
+def suite_collective(args):
+    """Reduce-scatter of the tri-packed ResNet-50 factors to owner ranks and all-gather of the
+    parameter-sized updates, as the distributed optimizer issues them (padded equal segments)."""
+    import torch.distributed as dist
+    from torchsso.utils.communicator import assign_owners
+    rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
+    torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', 0)))
+    dist.init_process_group('nccl', device_id=torch.device('cuda', torch.cuda.current_device()))
+    layers = []
+    for (c, h, w, k, s, p), reps, oc in zip(R50_CONVS, [1, 3, 2, 1, 3, 3, 1, 5, 5, 1, 2, 2],
+                                            [64, 64, 64, 128, 128, 128, 256, 256, 256, 512, 512, 512]):
+        layers += [(c * k * k, oc)] * reps
+    layers.append((2049, 1000))
+    owners = assign_owners([a ** 3 + g ** 3 for a, g in layers], world)
+    tri = lambda d: d * (d + 1) // 2
+    seg = max(sum(tri(layers[i][0]) + tri(layers[i][1]) + layers[i][0] * layers[i][1] for i in own)
+              for own in owners)
+    seg = (seg + 255) // 256 * 256
+    send = torch.randn(seg * world, device='cuda')
+    recv = torch.empty(seg, device='cuda')
+    pseg = max(sum(layers[i][0] * layers[i][1] for i in own) for own in owners)
+    pseg = (pseg + 255) // 256 * 256
+    psend = torch.randn(pseg, device='cuda')
+    precv = torch.empty(pseg * world, device='cuda')
+
+    def timed(fn):
+        dist.barrier()
+        ms = torch.tensor([timeit(fn, args.iters)], device='cuda')
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+    ms_rs = timed(lambda: dist.reduce_scatter_tensor(recv, send, op=dist.ReduceOp.SUM))
+    ms_ag = timed(lambda: dist.all_gather_into_tensor(precv, psend))
+    if rank == 0:
+        f = (world - 1) / world
+        emit(suite='collective', op='reduce_scatter(factors+grads)', world=world, bytes=4 * seg * world,
+             ms=round(ms_rs, 4), bus_gbs=round(4.0 * seg * world * f / ms_rs / 1e6, 1), nominal_gbs=900)
+        emit(suite='collective', op='all_gather(updates)', world=world, bytes=4 * pseg * world,
+             ms=round(ms_ag, 4), bus_gbs=round(4.0 * pseg * world * f / ms_ag / 1e6, 1), nominal_gbs=900)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+SUITES = {'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
+          'stream': suite_stream, 'collective': suite_collective}
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument('suite', choices=sorted(SUITES))
+    ap.add_argument('--case', type=int, default=None)
+    ap.add_argument('--iters', type=int, default=10)
+    ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp16', 'fp32'])
+    ap.add_argument('--batch', type=int, default=32)
+    ap.add_argument('--rows', type=int, default=0)
+    ap.add_argument('--rotate', type=int, default=4, help='input buffers rotated between launches')
+    ap.add_argument('--impl', type=int, default=nat.IMPL_AUTO, help='0 auto, 1 SIMT, 2 tcgen05 gather, 3 TMA')
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit('microbench needs a CUDA device: there is no CPU path')
+    nat.lib()
+    SUITES[args.suite](args)
+
+
+if __name__ == '__main__':
+    main()
