@@ -210,7 +210,7 @@ typedef struct {
 } sso_copy_rec;
 
 typedef struct {
-  int32_t kind;       /* 0 gemm64, 1 gemm128, 2 diag-block factor, 3 copy */
+  int32_t kind;       /* 0 gemm64, 1 gemm128, 2 diag-block factor, 3 copy, 4 gemm128 whose operands are both read along k */
   int32_t first;      /* first record of this phase in its table */
   int32_t count;      /* number of records (= CTAs) */
   int32_t reserved;

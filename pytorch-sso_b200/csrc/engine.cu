@@ -22,6 +22,7 @@
 namespace sso {
 
 int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
+int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
 int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
 
 constexpr int NB = 64;  // algorithmic block size of the factorisations
@@ -353,11 +354,27 @@ struct Builder {
     t.alpha = alpha; t.beta = beta;
     p.tasks.push_back(t);
   }
-  void end_phase(int kind, int first, int count) {
+  // A 128-wide task qualifies for the cp.async kernel when both operands are read along k in
+  // 16-byte aligned rows.
+  static bool k_contiguous(const sso_tile_task& t) {
+    auto al = [](const void* p, int ld) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && ld % 4 == 0; };
+    return (t.flags & 3u) == 2u && al(t.A, t.lda) && al(t.B, t.ldb);
+  }
+  void push_phase(int kind, int first, int count) {
     if (count <= 0) return;
     sso_phase ph;
     ph.kind = kind; ph.first = first; ph.count = count; ph.reserved = 0;
     phases->push_back(ph);
+  }
+  void end_phase(int kind, int first, int count) {
+    if (count <= 0) return;
+    if (kind != 1) return push_phase(kind, first, count);
+    // the tasks of a phase are independent: run the k-contiguous ones (kind 4) and the rest
+    // (kind 1) as two launches
+    auto mid = std::stable_partition(p.tasks.begin() + first, p.tasks.begin() + first + count, k_contiguous);
+    const int nfast = (int)(mid - (p.tasks.begin() + first));
+    push_phase(4, first, nfast);
+    push_phase(1, first + nfast, count - nfast);
   }
 };
 
@@ -372,33 +389,51 @@ static inline int bsz(const Mat& m, int b) { return std::min(NB, m.d - b * NB); 
 static inline float* blk(float* base, int d, int bi, int bj) { return base + (int64_t)bi * NB * d + (int64_t)bj * NB; }
 
 // Cholesky of every matrix in `ms` (in place in W, block inverses into Li's diagonal blocks).
+// Left-looking over panels of two blocks (128 columns): a panel first receives the update of
+// all finished columns in one phase of 128x128 tasks with a long K (tensor cores), then its
+// two block columns are factorised with 64-wide tasks.  The upper triangle of W is scratch.
 static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot) {
-  int max_nb = 0;
-  for (auto& m : ms) max_nb = std::max(max_nb, m.nb);
-  for (int j = 0; j < max_nb; ++j) {
-    int first = (int)b.p.diags.size();
-    for (auto& m : ms)
-      if (j < m.nb) {
-        DiagRec r;
-        r.L = blk(m.W, m.d, j, j); r.Linv = blk(m.Li, m.d, j, j);
-        r.ld_l = m.d; r.ld_inv = m.d; r.size = bsz(m, j); r.mat = m.mat_index; r.row0 = j * NB;
-        r.info_slot = info_slot;
-        b.p.diags.push_back(r);
+  constexpr int PB = 2 * NB;
+  int max_np = 0;
+  for (auto& m : ms) max_np = std::max(max_np, (m.d + PB - 1) / PB);
+  auto blk2 = [](float* base, int d, int pi, int pj) { return base + (int64_t)pi * PB * d + (int64_t)pj * PB; };
+  for (int p = 0; p < max_np; ++p) {
+    int first = b.task_begin();
+    if (p > 0)
+      for (auto& m : ms) {
+        const int np = (m.d + PB - 1) / PB;
+        for (int i = p; i < np; ++i)
+          b.gemm(blk2(m.W, m.d, i, 0), m.d, false, blk2(m.W, m.d, p, 0), m.d, true, blk2(m.W, m.d, i, p), m.d,
+                 std::min(PB, m.d - i * PB), std::min(PB, m.d - p * PB), p * PB, -1.f, 1.f);
       }
-    b.end_phase(2, first, (int)b.p.diags.size() - first);
-    first = b.task_begin();
-    for (auto& m : ms)
-      for (int i = j + 1; i < m.nb; ++i)
-        b.gemm(blk(m.W, m.d, i, j), m.d, false, blk(m.Li, m.d, j, j), m.d, true,
-               blk(m.W, m.d, i, j), m.d, bsz(m, i), NB, NB, 1.f, 0.f);
-    b.end_phase(0, first, b.task_begin() - first);
-    first = b.task_begin();
-    for (auto& m : ms)
-      for (int i = j + 1; i < m.nb; ++i)
-        for (int k = j + 1; k <= i; ++k)
-          b.gemm(blk(m.W, m.d, i, j), m.d, false, blk(m.W, m.d, k, j), m.d, true,
-                 blk(m.W, m.d, i, k), m.d, bsz(m, i), bsz(m, k), NB, -1.f, 1.f);
-    b.end_phase(0, first, b.task_begin() - first);
+    b.end_phase(1, first, b.task_begin() - first);
+    for (int half = 0; half < 2; ++half) {
+      const int j = 2 * p + half;
+      if (half == 1) {   // second block column of the panel: update by the first
+        first = b.task_begin();
+        for (auto& m : ms)
+          for (int i = j; i < m.nb; ++i)
+            b.gemm(blk(m.W, m.d, i, j - 1), m.d, false, blk(m.W, m.d, j, j - 1), m.d, true,
+                   blk(m.W, m.d, i, j), m.d, bsz(m, i), bsz(m, j), NB, -1.f, 1.f);
+        b.end_phase(0, first, b.task_begin() - first);
+      }
+      first = (int)b.p.diags.size();
+      for (auto& m : ms)
+        if (j < m.nb) {
+          DiagRec r;
+          r.L = blk(m.W, m.d, j, j); r.Linv = blk(m.Li, m.d, j, j);
+          r.ld_l = m.d; r.ld_inv = m.d; r.size = bsz(m, j); r.mat = m.mat_index; r.row0 = j * NB;
+          r.info_slot = info_slot;
+          b.p.diags.push_back(r);
+        }
+      b.end_phase(2, first, (int)b.p.diags.size() - first);
+      first = b.task_begin();
+      for (auto& m : ms)
+        for (int i = j + 1; i < m.nb; ++i)
+          b.gemm(blk(m.W, m.d, i, j), m.d, false, blk(m.Li, m.d, j, j), m.d, true,
+                 blk(m.W, m.d, i, j), m.d, bsz(m, i), NB, NB, 1.f, 0.f);
+      b.end_phase(0, first, b.task_begin() - first);
+    }
   }
 }
 
@@ -478,6 +513,14 @@ static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* 
         }
         tile_task_kernel<8><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first);
         break;
+      case 4:
+        if (g_engine_tc) {
+          const int rc = launch_tile_tasks_kc(p.d_tasks + ph.first, ph.count, p.d_status, st);
+          if (rc) return rc;
+          continue;
+        }
+        tile_task_kernel<8><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first);
+        break;
       case 2: diag_block_kernel<<<ph.count, 256, 0, st>>>(p.d_diags + ph.first, info); break;
       case 3: copy_kernel<<<ph.count, 256, 0, st>>>(p.d_copies + ph.first, p.d_shift); break;
       default: return fail(-1, "bad phase kind %d", ph.kind);
@@ -523,30 +566,34 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
     int max_nb = 0;
     for (auto& m : ms) max_nb = std::max(max_nb, m.nb);
     for (int s = 1; s < max_nb; s *= 2) {
+      // from s = 2 on every range boundary is a multiple of two blocks: 128x128 tasks (the
+      // zero blocks just above the diagonal of Li make the wider K ranges harmless)
+      const int w = s == 1 ? 1 : 2;
+      const int T = w * NB;
       first = b.task_begin();
       for (auto& m : ms)
         for (int lo = 0; lo + s < m.nb; lo += 2 * s) {
           const int mid = lo + s, hi = std::min(lo + 2 * s, m.nb);
-          for (int i = mid; i < hi; ++i)
-            for (int j = lo; j < mid; ++j)
+          for (int i = mid; i < hi; i += w)
+            for (int j = lo; j < mid; j += w)
               // Y(i,j)^T = sum_{k in [j,mid)} Inv11(k,j)^T * L(i,k)^T  -> W block (j,i)
               b.gemm(blk(m.Li, m.d, j, j), m.d, true, blk(m.W, m.d, i, j), m.d, true,
-                     blk(m.W, m.d, j, i), m.d, NB, bsz(m, i), (mid - j) * NB, 1.f, 0.f);
+                     blk(m.W, m.d, j, i), m.d, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
         }
-      b.end_phase(0, first, b.task_begin() - first);
+      b.end_phase(w == 1 ? 0 : 1, first, b.task_begin() - first);
       first = b.task_begin();
       for (auto& m : ms)
         for (int lo = 0; lo + s < m.nb; lo += 2 * s) {
           const int mid = lo + s, hi = std::min(lo + 2 * s, m.nb);
-          for (int i = mid; i < hi; ++i)
-            for (int j = lo; j < mid; ++j) {
-              const int kk = std::min((i - mid + 1) * NB, m.d - mid * NB);
+          for (int i = mid; i < hi; i += w)
+            for (int j = lo; j < mid; j += w) {
+              const int kk = std::min((i + w - mid) * NB, m.d - mid * NB);
               // Inv21(i,j) = - sum_k Inv22(i,k) * Y(k,j),  Y(k,j) stored at W(j,k) transposed
               b.gemm(blk(m.Li, m.d, i, mid), m.d, false, blk(m.W, m.d, j, mid), m.d, true,
-                     blk(m.Li, m.d, i, j), m.d, bsz(m, i), NB, kk, -1.f, 0.f);
+                     blk(m.Li, m.d, i, j), m.d, std::min(T, m.d - i * NB), T, kk, -1.f, 0.f);
             }
         }
-      b.end_phase(0, first, b.task_begin() - first);
+      b.end_phase(w == 1 ? 0 : 1, first, b.task_begin() - first);
     }
     for (auto& m : ms) m.T = m.W;  // L is dead now; the inverse overwrites it
     emit_lauum(b, ms);
@@ -638,36 +685,43 @@ static Plan* build_precond(int n, const int64_t* dA, const int64_t* dG, float* c
   Plan* p = new Plan();
   Builder b(*p, &p->run_phases);
   constexpr int T = 128;
-  // T = G_inv * [gw | gb]     (columns of the weight block, then the bias column)
+  // Both factors are symmetric, which lets every operand be read along its contiguous
+  // direction (the fast path of the tensor-core tasks):
+  //   tmp = U^T = A_inv[:, :wc] * gw^T (+ A_inv[:, wc] * gb^T),   [gw | gb] = G_inv * U.
   int first = b.task_begin();
   for (int l = 0; l < n; ++l) {
     const int a = (int)dA[l], g = (int)dG[l];
     const bool bias = gb && gb[l];
     const int wcols = bias ? a - 1 : a;
-    for (int i = 0; i < g; i += T)
-      for (int j = 0; j < wcols; j += T)
-        b.gemm(G_inv[l] + (int64_t)i * g, g, false, gw[l] + j, wcols, false,
-               tmp[l] + (int64_t)i * a + j, a, std::min(T, g - i), std::min(T, wcols - j), g, 1.f, 0.f);
-    if (bias)
-      for (int i = 0; i < g; i += T)
-        b.gemm(G_inv[l] + (int64_t)i * g, g, false, gb[l], 1, false,
-               tmp[l] + (int64_t)i * a + wcols, a, std::min(T, g - i), 1, g, 1.f, 0.f);
+    for (int i = 0; i < a; i += T)
+      for (int j = 0; j < g; j += T)
+        b.gemm(A_inv[l] + (int64_t)i * a, a, false, gw[l] + (int64_t)j * wcols, wcols, true,
+               tmp[l] + (int64_t)i * g + j, g, std::min(T, a - i), std::min(T, g - j), wcols, 1.f, 0.f);
   }
   b.end_phase(1, first, b.task_begin() - first);
-  // [gw | gb] = T * A_inv
+  first = b.task_begin();
+  for (int l = 0; l < n; ++l) {
+    const int a = (int)dA[l], g = (int)dG[l];
+    if (!(gb && gb[l])) continue;
+    for (int i = 0; i < a; i += NB)
+      for (int j = 0; j < g; j += NB)
+        b.gemm(A_inv[l] + (int64_t)i * a + (a - 1), a, false, gb[l] + j, g, false,
+               tmp[l] + (int64_t)i * g + j, g, std::min(NB, a - i), std::min(NB, g - j), 1, 1.f, 1.f);
+  }
+  b.end_phase(0, first, b.task_begin() - first);
   first = b.task_begin();
   for (int l = 0; l < n; ++l) {
     const int a = (int)dA[l], g = (int)dG[l];
     const bool bias = gb && gb[l];
     const int wcols = bias ? a - 1 : a;
-    for (int i = 0; i < g; i += T)
+    for (int i = 0; i < g; i += T) {
       for (int j = 0; j < wcols; j += T)
-        b.gemm(tmp[l] + (int64_t)i * a, a, false, A_inv[l] + j, a, false,
-               gw[l] + (int64_t)i * wcols + j, wcols, std::min(T, g - i), std::min(T, wcols - j), a, 1.f, 0.f);
-    if (bias)
-      for (int i = 0; i < g; i += T)
-        b.gemm(tmp[l] + (int64_t)i * a, a, false, A_inv[l] + wcols, a, false,
-               gb[l] + i, 1, std::min(T, g - i), 1, a, 1.f, 0.f);
+        b.gemm(G_inv[l] + (int64_t)i * g, g, false, tmp[l] + (int64_t)j * g, g, true,
+               gw[l] + (int64_t)i * wcols + j, wcols, std::min(T, g - i), std::min(T, wcols - j), g, 1.f, 0.f);
+      if (bias)
+        b.gemm(G_inv[l] + (int64_t)i * g, g, false, tmp[l] + (int64_t)wcols * g, g, true,
+               gb[l] + i, 1, std::min(T, g - i), 1, g, 1.f, 0.f);
+    }
   }
   b.end_phase(1, first, b.task_begin() - first);
   return p;
@@ -677,7 +731,7 @@ size_t sso_precond_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t
   size_t tasks = 0;
   for (int l = 0; l < n_layers; ++l) {
     const size_t ti = (dG[l] + 127) / 128, tj = (dA[l] + 127) / 128 + 1;
-    tasks += 2 * ti * tj;
+    tasks += 2 * ti * tj + ((dG[l] + 63) / 64) * ((dA[l] + 63) / 64);
   }
   return plan_table_bytes(tasks, 0, 0, 0);
 }

@@ -4,12 +4,16 @@
 // stages, because the tensor core's own accumulation truncates).
 //
 // One CTA per task, 17 warps: 8 accumulate warps, 1 MMA warp, 8 load warps.  Both operands end up
-// K-major in shared memory (canonical no-swizzle layout, core matrix = 8 rows x 16 bytes):
+// K-major in shared memory in the canonical SWIZZLE_128B layout: one operand row = 32 k = 128
+// bytes, eight rows = one 1024-byte atom, the 16-byte chunk index XOR-ed with (row & 7).  Core
+// matrices are then aligned to 128-byte lines, which the tensor core needs to read shared memory
+// at full rate (padded no-swizzle layouts halve it), and the swizzle keeps the stores free of
+// bank conflicts:
 //   * operand contiguous along k in global memory (A not transposed, B transposed): a thread loads
-//     16 bytes = 4 consecutive k of one row and stores them as they are; 8 lanes = one 128-byte line;
-//     LBO = 144, SBO = 1152 rotate the 8 k-chunks of a row over the banks;
+//     16 bytes = 4 consecutive k of one row and stores them as one chunk; 8 lanes = one row;
 //   * operand contiguous along its row/column index (A transposed, B not transposed): a thread loads
-//     4 consecutive indices of one k and scatters them with scalar stores; LBO = 128, SBO = 1040.
+//     4 consecutive indices of one k and scatters them with scalar stores; a warp covers 16 k x 8
+//     indices so that its 32 stores fall into 32 different banks.
 // Unaligned bases / leading dimensions (odd matrix sizes) fall back to element loads.
 // Every wait is bounded; a timeout sets *status and the task writes nothing.
 #include "common.cuh"
@@ -23,15 +27,21 @@ using namespace tc;
 constexpr int TILE = 128, KS = 32, STAGES = 3;
 constexpr int EPI_WARPS = 8, MMA_WARP = 8, LOAD_WARPS = 8;
 constexpr int THREADS = 32 * (EPI_WARPS + 1 + LOAD_WARPS);
-constexpr uint32_t OPB = 16 * 1152;                 // bytes of one operand part (hi or lo) of one stage
+constexpr uint32_t OPB = TILE * 128;                // bytes of one operand part (hi or lo) of one stage
 constexpr uint32_t STAGE_BYTES = 4 * OPB;           // A_hi A_lo B_hi B_lo
 constexpr uint32_t TMEM_COLS = 256;
 constexpr int FLUSH = 2;
+constexpr int CT_LD = TILE + 1;           // row pitch of the output tile staged in shared memory
 
-struct Layout {
-  uint32_t lbo, sbo;
-};
-__device__ __forceinline__ Layout layout_of(bool kcontig) { return kcontig ? Layout{144u, 1152u} : Layout{128u, 1040u}; }
+__device__ __forceinline__ uint64_t smem_desc_sw128_kmajor(uint32_t saddr) {
+  // start address, LBO unused for a K-major operand one swizzle atom wide, SBO = 1024 (eight
+  // rows), descriptor version 1, layout type 2 = SWIZZLE_128B
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// byte offset of element (row r, k) inside one operand part
+__device__ __forceinline__ uint32_t sw_off(int r, int k) {
+  return (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u + (uint32_t)(((k >> 2) ^ (r & 7)) << 4) + (uint32_t)(k & 3) * 4u;
+}
 
 __device__ __forceinline__ void split_store4(uint32_t addr, float4 v) {
   const uint32_t h0 = rna_tf32(v.x), h1 = rna_tf32(v.y), h2 = rna_tf32(v.z), h3 = rna_tf32(v.w);
@@ -62,19 +72,120 @@ __device__ __forceinline__ float4 load4(const float* __restrict__ P, int64_t ld,
   return v;
 }
 
+// Stage-invariant addressing of one operand for one load thread (lt = 0..255).
+//   k-contiguous operand: chunk j is row (lt>>3) + 32j, k = (lt&7)*4 .. +3;
+//   other operand: with w = lt>>5, kq = lt&15, rc = (lt>>4)&1, chunk j is k = (j&1)*16 + kq and the
+//   four indices 4c .. 4c+3, c = 4w + 2(j>>1) + rc.
+struct OpLoad {
+  const float* p0;      // chunk j of stage s is at p0 + joff(j) + s*step
+  int64_t ja, step;     // k-contiguous: joff = j*ja;  other: joff = (j&1)*ja + (j>>1)*8
+  uint32_t so0;         // k-contiguous: chunk j is stored at so0 + j*4096
+  uint32_t okmask;
+  bool fast;
+};
+__device__ __forceinline__ OpLoad make_op(const float* P, int ld, bool kc, int lim, int lt, bool vec) {
+  OpLoad o;
+  o.okmask = 0u;
+  o.fast = vec;
+  o.step = kc ? (int64_t)KS : (int64_t)KS * ld;
+  if (kc) {
+    const int q = lt >> 3, l8 = lt & 7;
+    o.p0 = P + (int64_t)q * ld + l8 * 4;
+    o.ja = (int64_t)32 * ld;
+    o.so0 = sw_off(q, l8 * 4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (q + 32 * j < lim) o.okmask |= 1u << j;
+  } else {
+    const int w = lt >> 5, kq = lt & 15, rc = (lt >> 4) & 1;
+    o.p0 = P + (int64_t)kq * ld + (4 * w + rc) * 4;
+    o.ja = (int64_t)16 * ld;
+    o.so0 = 0u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = (4 * w + 2 * (j >> 1) + rc) * 4;
+      if (idx + 3 < lim) o.okmask |= 1u << j;
+      else if (idx < lim) o.fast = false;    // a chunk straddling the edge needs the checked loads
+    }
+  }
+  return o;
+}
+
+// Role of the 8 accumulate warps: drain the TMEM accumulator chunk by chunk into fp32 registers,
+// then write the tile.  accfull0 / accempty0 are the shared addresses of barrier pairs (b = 0, 1
+// at +8 bytes).  `ct` is shared memory that is free once the last commit has fired.
+__device__ __forceinline__ void accumulate_and_store(const sso_tile_task& t, uint32_t tmem_base, uint32_t accfull0,
+                                                     uint32_t accempty0, int nchunks, int* status, float* ct,
+                                                     int warp, int lane, int dbg) {
+  auto accfull_bar = [&](int b) { return accfull0 + 8u * b; };
+  auto accempty_bar = [&](int b) { return accempty0 + 8u * b; };
+  const int q = warp & 3, half = warp >> 2;
+  float acc[64];
+#pragma unroll
+  for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+  bool ok = true;
+  for (int c = 0; c < nchunks; ++c) {
+    const int b = c & 1;
+    if (!mbar_wait(accfull_bar(b), (c >> 1) & 1, status, 13)) { ok = false; break; }
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TILE + half * 64);
+    uint32_t v0[32], v1[32];
+    tmem_ld32(taddr, v0);
+    tmem_ld32(taddr + 32, v1);
+    tmem_ld_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(accempty_bar(b));
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      acc[i] += __uint_as_float(v0[i]);
+      acc[32 + i] += __uint_as_float(v1[i]);
+    }
+  }
+  // The operand buffers are free now (the last commit has fired, so every MMA has read them):
+  // stage the tile there, row r at r*129 floats, and write C (and its mirror) with whole
+  // warps per row so that global accesses are coalesced.
+  const int r = q * 32 + lane;
+  if (ok) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) ct[r * CT_LD + half * 64 + i] = t.alpha * acc[i];
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+  if (ok) {
+    const bool sym = (t.flags & 4u) != 0;
+    for (int rr = warp; rr < t.m; rr += EPI_WARPS) {
+      float* crow = t.C + (int64_t)rr * t.ldc;
+      for (int c = lane; c < t.n; c += 32) {
+        // symmetric tile: only the lower half was computed to be used; mirror it
+        float v = (sym && c > rr) ? ct[c * CT_LD + rr] : ct[rr * CT_LD + c];
+        if (t.beta != 0.f) v = fmaf(t.beta, crow[c], v);
+        crow[c] = v;
+      }
+    }
+  }
+  // the mirror of an updated tile (beta != 0) reads back what other warps have just written
+  if (t.C2 && t.beta != 0.f) asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+  if (ok && t.C2) {
+    for (int c = warp; c < t.n; c += EPI_WARPS) {
+      float* orow = t.C2 + (int64_t)c * t.ldc2;
+      for (int rr = lane; rr < t.m; rr += 32)
+        orow[rr] = (t.beta != 0.f) ? t.C[(int64_t)rr * t.ldc + c] : ct[rr * CT_LD + c];
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1) tile_task_tc_kernel(const sso_tile_task* __restrict__ tasks, int* status) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_slot;
   const sso_tile_task t = tasks[blockIdx.x];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool ta = t.flags & 1u, tb = t.flags & 2u;
   const bool a_kc = !ta, b_kc = tb;
-  const Layout la = layout_of(a_kc), lb = layout_of(b_kc);
   const int nstages = ceil_div(t.k, KS);
   const int nchunks = ceil_div(nstages, FLUSH);
 
-  const uint32_t smem0 = (smem_u32(smem_raw) + 127u) & ~127u;
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
@@ -99,44 +210,8 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tc_kernel(const sso_tile
 
   if (warp < EPI_WARPS) {
     // ------------------------------------------------------------------ accumulate + epilogue
-    const int q = warp & 3, half = warp >> 2;
-    float acc[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    bool ok = true;
-    for (int c = 0; c < nchunks; ++c) {
-      const int b = c & 1;
-      if (!mbar_wait(accfull_bar(b), (c >> 1) & 1, status, 13)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TILE + half * 64);
-      uint32_t v0[32], v1[32];
-      tmem_ld32(taddr, v0);
-      tmem_ld32(taddr + 32, v1);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(accempty_bar(b));
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        acc[i] += __uint_as_float(v0[i]);
-        acc[32 + i] += __uint_as_float(v1[i]);
-      }
-    }
-    const int r = q * 32 + lane;
-    if (ok && r < t.m) {
-      float* crow = t.C + (int64_t)r * t.ldc;
-#pragma unroll 4
-      for (int i = 0; i < 64; ++i) {
-        const int c = half * 64 + i;
-        if (c >= t.n) break;
-        if ((t.flags & 4u) && c > r) break;      // symmetric tile: lower half computed, mirrored below
-        float v = t.alpha * acc[i];
-        if (t.beta != 0.f) v = fmaf(t.beta, crow[c], v);
-        crow[c] = v;
-        if (t.C2) t.C2[(int64_t)c * t.ldc2 + r] = v;
-        if ((t.flags & 4u) && c < r) t.C[(int64_t)c * t.ldc + r] = v;
-      }
-    }
+    float* ct = reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw)));
+    accumulate_and_store(t, tmem_base, accfull_bar(0), accempty_bar(0), nchunks, status, ct, warp, lane);
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -155,8 +230,9 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tc_kernel(const sso_tile
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * TILE);
 #pragma unroll
         for (int ks = 0; ks < KS / 8; ++ks) {
-          const uint64_t adh = smem_desc(ah + ks * 2 * la.lbo, la.lbo, la.sbo), adl = smem_desc(al + ks * 2 * la.lbo, la.lbo, la.sbo);
-          const uint64_t bdh = smem_desc(bh + ks * 2 * lb.lbo, lb.lbo, lb.sbo), bdl = smem_desc(bl + ks * 2 * lb.lbo, lb.lbo, lb.sbo);
+          // one k-slice = 8 tf32 = 32 bytes further along the 128-byte rows
+          const uint64_t adh = smem_desc_sw128_kmajor(ah + ks * 32u), adl = smem_desc_sw128_kmajor(al + ks * 32u);
+          const uint64_t bdh = smem_desc_sw128_kmajor(bh + ks * 32u), bdl = smem_desc_sw128_kmajor(bl + ks * 32u);
           umma<true>(d_tmem, adl, bdh, idesc, (first_of_chunk && ks == 0) ? 0u : 1u);
           umma<true>(d_tmem, adh, bdl, idesc, 1u);
           umma<true>(d_tmem, adh, bdh, idesc, 1u);
@@ -168,63 +244,220 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tc_kernel(const sso_tile
   } else {
     // ------------------------------------------------------------------ load warps
     const int lt = tid - 32 * (MMA_WARP + 1);
-    const int l8 = lt & 7, q = lt >> 3;               // q: 0..31
+    const int l8 = lt & 7, q = lt >> 3;               // k-contiguous mapping
+    const int w = lt >> 5, kq = lt & 15, rc = (lt >> 4) & 1;   // mapping of the other kind
     const bool a_vec = ((reinterpret_cast<uintptr_t>(t.A) & 15) == 0) && (t.lda % 4 == 0);
     const bool b_vec = ((reinterpret_cast<uintptr_t>(t.B) & 15) == 0) && (t.ldb % 4 == 0);
-    bool ok = true;
-    for (int s = 0; s < nstages && ok; ++s) {
-      const int slot = s % STAGES, k0 = s * KS;
-      float4 va[4], vb[4];
-      // operand A: rows i of op(A), contraction index k
+    // Addresses that do not change from stage to stage are computed once.  Interior stages of
+    // aligned operands then cost one 16-byte load per chunk; edges and unaligned operands take
+    // the checked element loads.
+    const OpLoad oa = make_op(t.A, t.lda, a_kc, t.m, lt, a_vec);
+    const OpLoad ob = make_op(t.B, t.ldb, b_kc, t.n, lt, b_vec);
+    auto load_op = [&](const OpLoad& o, const float* P, int ld, bool kc, int lim, bool vec, int s, float4 (&v)[4]) {
+      const int k0 = s * KS;
+      if (k0 + KS <= t.k && o.fast) {
+        const float* base = o.p0 + (int64_t)s * o.step;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (a_kc) {        // A[i*lda + k]: row i = q + 32j, k-chunk l8
-          const int i = q + 32 * j;
-          va[j] = load4(t.A, t.lda, i, k0 + l8 * 4, i < t.m, t.k, a_vec);
-        } else {           // A[k*lda + i]: k = k0 + q, index chunk l8 + 8j
-          const int k = k0 + q;
-          va[j] = load4(t.A, t.lda, k, (l8 + 8 * j) * 4, k < t.k, t.m, a_vec);
+        for (int j = 0; j < 4; ++j) {
+          const int64_t joff = kc ? j * o.ja : (j & 1) * o.ja + (j >> 1) * 8;
+          v[j] = ((o.okmask >> j) & 1u) ? __ldg(reinterpret_cast<const float4*>(base + joff))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        if (b_kc) {        // B[jcol*ldb + k]
-          const int jc = q + 32 * j;
-          vb[j] = load4(t.B, t.ldb, jc, k0 + l8 * 4, jc < t.n, t.k, b_vec);
-        } else {           // B[k*ldb + jcol]
-          const int k = k0 + q;
-          vb[j] = load4(t.B, t.ldb, k, (l8 + 8 * j) * 4, k < t.k, t.n, b_vec);
-        }
-      }
-      if (s >= STAGES) ok = mbar_wait(empty_bar(slot), ((s / STAGES) - 1) & 1, status, 14);
-      if (!ok) break;
-      const uint32_t sb = smem0 + slot * STAGE_BYTES;
+      } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (a_kc) {
-          const int i = q + 32 * j;
-          split_store4(sb + (i >> 3) * la.sbo + l8 * la.lbo + (i & 7) * 16, va[j]);
-        } else {
-          const float f[4] = {va[j].x, va[j].y, va[j].z, va[j].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = (l8 + 8 * j) * 4 + e;
-            split_store1(sb + (col >> 3) * la.sbo + (q >> 2) * la.lbo + (col & 7) * 16 + (q & 3) * 4, f[e]);
-          }
-        }
-        if (b_kc) {
-          const int jc = q + 32 * j;
-          split_store4(sb + 2 * OPB + (jc >> 3) * lb.sbo + l8 * lb.lbo + (jc & 7) * 16, vb[j]);
-        } else {
-          const float f[4] = {vb[j].x, vb[j].y, vb[j].z, vb[j].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = (l8 + 8 * j) * 4 + e;
-            split_store1(sb + 2 * OPB + (col >> 3) * lb.sbo + (q >> 2) * lb.lbo + (col & 7) * 16 + (q & 3) * 4, f[e]);
+        for (int j = 0; j < 4; ++j) {
+          if (kc) {          // P[i*ld + k]
+            const int i = q + 32 * j;
+            v[j] = load4(P, ld, i, k0 + l8 * 4, i < lim, t.k, vec);
+          } else {           // P[k*ld + index]
+            const int k = k0 + (j & 1) * 16 + kq;
+            v[j] = load4(P, ld, k, (4 * w + 2 * (j >> 1) + rc) * 4, k < t.k, lim, vec);
           }
         }
       }
+    };
+    auto store_op = [&](const OpLoad& o, bool kc, uint32_t base, const float4 (&v)[4]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (kc) {
+          split_store4(base + o.so0 + j * 4096u, v[j]);
+        } else {
+          const int k = (j & 1) * 16 + kq, r0 = (4 * w + 2 * (j >> 1) + rc) * 4;
+          split_store1(base + sw_off(r0, k), v[j].x);
+          split_store1(base + sw_off(r0 + 1, k), v[j].y);
+          split_store1(base + sw_off(r0 + 2, k), v[j].z);
+          split_store1(base + sw_off(r0 + 3, k), v[j].w);
+        }
+      }
+    };
+    auto load_stage = [&](int s, float4 (&va)[4], float4 (&vb)[4]) {
+      load_op(oa, t.A, t.lda, a_kc, t.m, a_vec, s, va);
+      load_op(ob, t.B, t.ldb, b_kc, t.n, b_vec, s, vb);
+    };
+    auto store_stage = [&](int s, const float4 (&va)[4], const float4 (&vb)[4]) -> bool {
+      const int slot = s % STAGES;
+      if (s >= STAGES && !mbar_wait(empty_bar(slot), ((s / STAGES) - 1) & 1, status, 14)) return false;
+      const uint32_t sa = smem0 + slot * STAGE_BYTES;
+      store_op(oa, a_kc, sa, va);
+      store_op(ob, b_kc, sa + 2 * OPB, vb);
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_bar(slot));
+      return true;
+    };
+    // the global loads of stage s+1 are in flight while stage s is split and stored
+    float4 a0[4], b0[4], a1[4], b1[4];
+    if (nstages > 0) load_stage(0, a0, b0);
+    for (int s = 0; s < nstages; s += 2) {
+      if (s + 1 < nstages) load_stage(s + 1, a1, b1);
+      if (!store_stage(s, a0, b0) || s + 1 >= nstages) break;
+      if (s + 2 < nstages) load_stage(s + 2, a0, b0);
+      if (!store_stage(s + 1, a1, b1)) break;
     }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Fast variant for tasks whose operands are both contiguous along k (A not transposed, B
+// transposed) with 16-byte aligned rows: the fp32 tiles travel global -> shared with cp.async
+// into a ring of RAW_SLOTS raw stages, so several stages of loads are in flight without holding
+// registers; the load warps then split each of their own chunks in place (hi overwrites the raw
+// value, lo goes to a ring of LO_SLOTS stages) and hand the stage to the MMA warp.
+// ------------------------------------------------------------------------------------------
+constexpr int RAW_SLOTS = 5, LO_SLOTS = 2, PREFETCH = 3;
+constexpr uint32_t PART = 2 * OPB;                       // A and B of one stage, one flavour (raw/hi or lo)
+constexpr uint32_t KC_SMEM = (RAW_SLOTS + LO_SLOTS) * PART;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1) tile_task_kc_kernel(const sso_tile_task* __restrict__ tasks, int* status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[RAW_SLOTS + 2 * LO_SLOTS + 4];
+  __shared__ uint32_t tmem_base_slot;
+  const sso_tile_task t = tasks[blockIdx.x];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nstages = ceil_div(t.k, KS);
+  const int nchunks = ceil_div(nstages, FLUSH);
+
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t lo0 = smem0 + RAW_SLOTS * PART;
+  const uint32_t bar0 = smem_u32(bars);
+  auto rawfree_bar = [&](int s) { return bar0 + 8u * s; };
+  auto full_bar = [&](int s) { return bar0 + 8u * (RAW_SLOTS + s); };
+  auto lofree_bar = [&](int s) { return bar0 + 8u * (RAW_SLOTS + LO_SLOTS + s); };
+  const uint32_t accfull0 = bar0 + 8u * (RAW_SLOTS + 2 * LO_SLOTS), accempty0 = accfull0 + 16u;
+  if (tid == 0) {
+    for (int s = 0; s < RAW_SLOTS; ++s) mbar_init(rawfree_bar(s), 1);
+    for (int s = 0; s < LO_SLOTS; ++s) {
+      mbar_init(full_bar(s), LOAD_WARPS);
+      mbar_init(lofree_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accfull0 + 8u * b, 1);
+      mbar_init(accempty0 + 8u * b, EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp < EPI_WARPS) {
+    float* ct = reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw)));
+    accumulate_and_store(t, tmem_base, accfull0, accempty0, nchunks, status, ct, warp, lane);
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(2u, 0u);   // tf32, K-major
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS, c = s / FLUSH, b = c & 1;
+        const bool first_of_chunk = (s % FLUSH) == 0;
+        if (first_of_chunk && c >= 2) ok = mbar_wait(accempty0 + 8u * b, ((c >> 1) - 1) & 1, status, 22);
+        if (!ok) break;
+        ok = mbar_wait(full_bar(ls), (s / LO_SLOTS) & 1, status, 21);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ah = smem0 + rs * PART, bh = ah + OPB, al = lo0 + ls * PART, bl = al + OPB;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TILE);
+#pragma unroll
+        for (int ks = 0; ks < KS / 8; ++ks) {
+          const uint64_t adh = smem_desc_sw128_kmajor(ah + ks * 32u), adl = smem_desc_sw128_kmajor(al + ks * 32u);
+          const uint64_t bdh = smem_desc_sw128_kmajor(bh + ks * 32u), bdl = smem_desc_sw128_kmajor(bl + ks * 32u);
+          umma<true>(d_tmem, adl, bdh, idesc, (first_of_chunk && ks == 0) ? 0u : 1u);
+          umma<true>(d_tmem, adh, bdl, idesc, 1u);
+          umma<true>(d_tmem, adh, bdh, idesc, 1u);
+        }
+        umma_commit(rawfree_bar(rs));
+        umma_commit(lofree_bar(ls));
+        if ((s % FLUSH) == FLUSH - 1 || s == nstages - 1) umma_commit(accfull0 + 8u * b);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ load + split warps
+    const int lt = tid - 32 * (MMA_WARP + 1);
+    const int q = lt >> 3, l8 = lt & 7;
+    const uint32_t so0 = sw_off(q, l8 * 4);
+    const float* pa = t.A + (int64_t)q * t.lda + l8 * 4;
+    const float* pb = t.B + (int64_t)q * t.ldb + l8 * 4;
+    const int64_t ja = (int64_t)32 * t.lda, jb = (int64_t)32 * t.ldb;
+    uint32_t oka = 0u, okb = 0u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (q + 32 * j < t.m) oka |= 1u << j;
+      if (q + 32 * j < t.n) okb |= 1u << j;
+    }
+    bool ok = true;
+    auto issue = [&](int s) {       // cp.async of this thread's 8 chunks of stage s (zero fill past the edges)
+      const int rs = s % RAW_SLOTS;
+      if (s >= RAW_SLOTS && !mbar_wait(rawfree_bar(rs), ((s / RAW_SLOTS) - 1) & 1, status, 24)) { ok = false; return; }
+      const int kk = s * KS + l8 * 4;
+      const uint32_t nb = (uint32_t)min(16, max(0, (t.k - kk) * 4));
+      const uint32_t dst = smem0 + rs * PART + so0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        cp_async16(dst + j * 4096u, pa + j * ja + s * KS, ((oka >> j) & 1u) ? nb : 0u);
+        cp_async16(dst + OPB + j * 4096u, pb + j * jb + s * KS, ((okb >> j) & 1u) ? nb : 0u);
+      }
+    };
+    for (int s = 0; s < PREFETCH; ++s) {     // always PREFETCH groups, so that wait_group counts stages
+      if (s < nstages) issue(s);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int s = 0; s < nstages && ok; ++s) {
+      if (s + PREFETCH < nstages) issue(s + PREFETCH);
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      if (!ok) break;
+      asm volatile("cp.async.wait_group %0;" ::"n"(PREFETCH) : "memory");
+      const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS;
+      if (s >= LO_SLOTS && !mbar_wait(lofree_bar(ls), ((s / LO_SLOTS) - 1) & 1, status, 25)) break;
+      const uint32_t hi = smem0 + rs * PART + so0, lo = lo0 + ls * PART + so0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t off = (uint32_t)(j & 3) * 4096u + (uint32_t)(j >> 2) * OPB;
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(hi + off) : "memory");
+        const uint32_t h0 = rna_tf32(v.x), h1 = rna_tf32(v.y), h2 = rna_tf32(v.z), h3 = rna_tf32(v.w);
+        const uint32_t l0 = __float_as_uint(v.x - __uint_as_float(h0)), l1 = __float_as_uint(v.y - __uint_as_float(h1));
+        const uint32_t l2 = __float_as_uint(v.z - __uint_as_float(h2)), l3 = __float_as_uint(v.w - __uint_as_float(h3));
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(hi + off), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(lo + off), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar(ls));
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -237,8 +470,20 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tc_kernel(const sso_tile
 
 }  // namespace etc
 
+int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st) {
+  const size_t smem = (size_t)etc::KC_SMEM + 1024;
+  static bool configured = false;
+  if (!configured) {
+    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  etc::tile_task_kc_kernel<<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
+  SSO_LAUNCH_OK("tile_task_kc_kernel");
+  return 0;
+}
+
 int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st) {
-  const size_t smem = (size_t)etc::STAGES * etc::STAGE_BYTES + 128;
+  const size_t smem = (size_t)etc::STAGES * etc::STAGE_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
     SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

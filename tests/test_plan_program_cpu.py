@@ -41,7 +41,7 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
     copies, _ = plan.copy_recs()
     info = {}
     for kind, first, count in plan.phases():
-        if kind in (0, 1):
+        if kind in (0, 1, 4):
             tile = 64 if kind == 0 else 128
             results = []
             for t in [tasks[i] for i in range(first, first + count)]:
