@@ -116,7 +116,7 @@ __device__ __forceinline__ OpLoad make_op(const float* P, int ld, bool kc, int l
 // at +8 bytes).  `ct` is shared memory that is free once the last commit has fired.
 __device__ __forceinline__ void accumulate_and_store(const sso_tile_task& t, uint32_t tmem_base, uint32_t accfull0,
                                                      uint32_t accempty0, int nchunks, int* status, float* ct,
-                                                     int warp, int lane, int dbg) {
+                                                     int warp, int lane) {
   auto accfull_bar = [&](int b) { return accfull0 + 8u * b; };
   auto accempty_bar = [&](int b) { return accempty0 + 8u * b; };
   const int q = warp & 3, half = warp >> 2;
