@@ -256,6 +256,8 @@ def run_gpu_arm(args):
     if args.graph:
         opt.update_inv = True
         opt.step(closure=closure)            # eager first step: builds pools, plans, scratch
+        # the model has no in-place activations, so the hooks' kernels may run beside it
+        torchsso.utils.set_curvature_stream(args.side_stream)
         closure = torchsso.utils.GraphedClosure(opt, closure)
         state['step'] = 1
 
@@ -337,6 +339,7 @@ def run_gpu_arm(args):
                    'image': '3x224x224', 'curvature': 'Fisher MC(1): Kron conv/linear + diag BN',
                    'factors_every': 1, 'inverse_every': INV_INTERVAL,
                    'closure': 'CUDA graph replay' if args.graph else 'eager',
+                   'curvature_stream': bool(args.graph and args.side_stream),
                    'parallelism': 'dp%d, factors reduce-scattered to owners' % world if world > 1 else 'single',
                    'l2_policy': 'per-step inputs (%.0f MB activations + 615 MB factor pools) exceed the 126 MB L2'
                                 % (B * 3 * 224 * 224 * 2 / 1e6),
@@ -382,6 +385,8 @@ def main():
     ap.add_argument('--batch', type=int, default=32, help='images per GPU')
     ap.add_argument('--cpu-batch', type=int, default=16, help='batch of the bounded CPU sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-side-stream', dest='side_stream', action='store_false',
+                    help='launch the curvature kernels of the hooks on the main stream')
     ap.add_argument('--no-graph', dest='graph', action='store_false',
                     help='issue the closure eagerly instead of replaying a captured CUDA graph')
     args = ap.parse_args()

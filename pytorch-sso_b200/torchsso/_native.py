@@ -128,6 +128,56 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+# ---- optional side stream for the curvature kernels of the hooks -----------------------------
+# When enabled, the factor / BatchNorm kernels that the forward and backward hooks launch go to a
+# dedicated stream per device, so they overlap with the model's own kernels; whoever consumes
+# curvature data joins the stream first (join_curvature_stream).
+_curv_streams = {}
+_curv_enabled = False
+_curv_dirty = set()
+
+
+def set_curvature_stream(enabled: bool):
+    global _curv_enabled
+    if not enabled:
+        for dev in list(_curv_dirty):
+            join_curvature_stream(torch.device('cuda', dev))
+    _curv_enabled = bool(enabled)
+
+
+def curvature_stream_enabled() -> bool:
+    return _curv_enabled
+
+
+def run_on_curvature_stream(fn, tensor: torch.Tensor):
+    """fn(tensor) with its kernels on the side stream, ordered after everything already queued on
+    the current stream.  `tensor` is kept alive for the side stream (record_stream)."""
+    if not _curv_enabled or not tensor.is_cuda:
+        return fn(tensor)
+    idx = tensor.device.index if tensor.device.index is not None else torch.cuda.current_device()
+    side = _curv_streams.get(idx)
+    if side is None:
+        side = _curv_streams[idx] = torch.cuda.Stream(device=idx)
+    side.wait_stream(torch.cuda.current_stream(idx))
+    tensor.record_stream(side)
+    _curv_dirty.add(idx)
+    with torch.cuda.stream(side):
+        return fn(tensor)
+
+
+def join_curvature_stream(device=None):
+    """Make the current stream wait for the curvature kernels queued so far."""
+    if not _curv_dirty:
+        return
+    if device is None or device.index is None:
+        idx = torch.cuda.current_device()
+    else:
+        idx = device.index
+    if idx in _curv_dirty:
+        torch.cuda.current_stream(idx).wait_stream(_curv_streams[idx])
+        _curv_dirty.discard(idx)
+
+
 def _require_cuda(t: torch.Tensor, what: str):
     if not t.is_cuda:
         raise RuntimeError('%s must live on a CUDA device: the K-FAC kernels have no CPU path' % what)

@@ -100,6 +100,7 @@ class Curvature(object):
         raise NotImplementedError
 
     def _get(self, role):
+        nat.join_curvature_stream(None)
         if role in self._generic:
             return self._generic[role]
         return self._views(role) if role in self._have else None
@@ -128,7 +129,7 @@ class Curvature(object):
         d['data_input'] = x
         d['data_output'] = output.detach()   # detached: keeping the graph alive between steps would
                                              # pin last step's activations and autograd nodes
-        self.update_in_forward(output.detach() if self._is_norm else x)
+        nat.run_on_curvature_stream(self.update_in_forward, output.detach() if self._is_norm else x)
         if output.requires_grad and torch.is_grad_enabled():
             output.register_hook(self._backward_hook)
 
@@ -140,7 +141,7 @@ class Curvature(object):
         module.__dict__['grad_output'] = g
         # the n^2 rescale that undoes the mean reduction of the loss
         # (torchsso/curv/curvature.py:151-155) is folded into the kernels' alpha
-        self.update_in_backward(g)
+        nat.run_on_curvature_stream(self.update_in_backward, g)
 
     def update_in_forward(self, data_input):
         pass
@@ -163,6 +164,7 @@ class Curvature(object):
 
     # ---- data -> ema -> inv -> std ------------------------------------------------
     def step(self, update_std=False, update_inv=True):
+        nat.join_curvature_stream(None)
         self.update_ema()
         if update_inv:
             self.update_inv()

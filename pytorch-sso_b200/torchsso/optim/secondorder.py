@@ -231,6 +231,7 @@ class SecondOrderOptimizer(Optimizer):
         loss = None
         if closure is not None:
             loss = closure()
+            nat.join_curvature_stream(None)
             self._harvest_grads()
             if n > 1:
                 self._accumulate(1.0 / n)

@@ -10,6 +10,8 @@ from __future__ import annotations
 import math
 
 import torch
+
+from torchsso import _native as nat
 import torch.nn as nn
 import torch.nn.functional as F
 
@@ -185,6 +187,7 @@ class VIOptimizer(SecondOrderOptimizer):
         for _ in range(m):
             self.sample_params()
             loss, output = closure()
+            nat.join_curvature_stream(None)
             acc_loss.update(loss.detach(), scale=1 / m)
             acc_prob.update(_probabilities(output.detach()), scale=1 / n)
             self._harvest_grads()

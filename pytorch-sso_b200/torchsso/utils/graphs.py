@@ -29,16 +29,18 @@ class GraphedClosure:
         torch.cuda.synchronize()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        from torchsso import _native as nat
         with torch.cuda.stream(side):
             for _ in range(max(1, warmup)):
                 closure()
+                nat.join_curvature_stream(None)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        from torchsso import _native as nat
         self.graph = torch.cuda.CUDAGraph()
         before = nat.launch_count()
         with torch.cuda.graph(self.graph, stream=side):
             self.result = closure()
+            nat.join_curvature_stream(None)      # forked curvature kernels rejoin inside the capture
         #: kernels of libsso_b200 inside the graph, i.e. launched by every replay
         self.library_kernels_per_replay = nat.launch_count() - before
         self.replays = 0

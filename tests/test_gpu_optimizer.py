@@ -227,9 +227,11 @@ def test_conv_stem_with_three_channels_channels_last(torchsso_mod):
         assert rel(curv.data[0], ref) < 1e-5
 
 
-def test_graphed_closure_equals_eager(torchsso_mod):
-    """Replaying the closure from a CUDA graph (hooks' curvature kernels included) must give the
-    same parameters as issuing it eagerly."""
+@pytest.mark.parametrize('side_stream', [False, True])
+def test_graphed_closure_equals_eager(torchsso_mod, side_stream):
+    """Replaying the closure from a CUDA graph (hooks' curvature kernels included, on the main
+    stream or forked to the curvature side stream) must give the same parameters as issuing it
+    eagerly."""
     torchsso = torchsso_mod
 
     def run(graphed):
@@ -262,7 +264,14 @@ def test_graphed_closure_equals_eager(torchsso_mod):
         return losses, [p.detach().clone() for p in model.parameters()]
 
     l0, p0 = run(False)
-    l1, p1 = run(True)
+    torchsso.utils.set_curvature_stream(side_stream)
+    try:
+        l1, p1 = run(True)
+        if side_stream:          # eager launches through the side stream as well
+            l2, p2 = run(False)
+            assert max(abs(a - b) for a, b in zip(l0, l2)) < 1e-5
+    finally:
+        torchsso.utils.set_curvature_stream(False)
     assert max(abs(a - b) for a, b in zip(l0, l1)) < 1e-5
     for a, b in zip(p0, p1):
         assert rel(b, a.cpu().numpy()) < 1e-5
