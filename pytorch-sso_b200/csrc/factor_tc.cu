@@ -28,6 +28,7 @@
 #include "tc_common.cuh"
 
 namespace sso {
+int factor_tc_run_reduce(const FactorParams& p, int tiles, cudaStream_t st);
 namespace tc {
 
 constexpr int TILE = 128;
@@ -362,7 +363,95 @@ __global__ void __launch_bounds__(THREADS, 1) factor_tc_kernel(const FactorParam
 
 // Sum the splits (fixed order), permute internal (kh,kw,c) columns to (c,kh,kw), apply
 // alpha / beta, mirror.  A non-zero status (a wait gave up) poisons the result with NaN.
-__global__ void __launch_bounds__(256) factor_tc_reduce(const FactorParams p) {
+//
+// One CTA produces 32 output rows x one group of columns that is CONTIGUOUS in the output:
+// for permuted factors a block of up to 8 channels at all kernel positions (8*kk columns), else
+// 32 consecutive columns.  Inside the partial tiles such a group is kk runs of 8 consecutive
+// columns.  Elements on or below the diagonal are read from their own tile with the lanes along
+// the run; elements above it are read from the mirrored position with the lanes along the rows,
+// so global reads come in whole 32-byte sectors, writes in whole rows of the group, and both
+// halves of the symmetric result come from the same numbers (bitwise symmetric).  The block is
+// staged in shared memory.
+constexpr int RED_ROWS = 32, RED_CB = 8, RED_W = 32;
+
+// sum over the splits of element (r, c), r >= c, of the lower-triangle partial tiles; four
+// independent partial sums keep several loads in flight, combined in a fixed order
+__device__ __forceinline__ float reduce_fetch(const float* __restrict__ partial, int nsplit, int r, int c) {
+  const int bi = r >> 7, bj = c >> 7;
+  const float* src = partial + ((int64_t)(bi * (bi + 1) / 2 + bj) * nsplit) * (TILE * TILE) + (r & 127) * TILE + (c & 127);
+  constexpr int64_t S = TILE * TILE;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int sp = 0;
+  for (; sp + 4 <= nsplit; sp += 4) {
+    a0 += src[sp * S];
+    a1 += src[(sp + 1) * S];
+    a2 += src[(sp + 2) * S];
+    a3 += src[(sp + 3) * S];
+  }
+  for (; sp < nsplit; ++sp) a0 += src[sp * S];
+  return (a0 + a1) + (a2 + a3);
+}
+
+__global__ void __launch_bounds__(256) factor_tc_reduce(const FactorParams p, int perm_groups, int pitch) {
+  extern __shared__ float rs[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gi0 = blockIdx.x * RED_ROWS;
+  const int grp = blockIdx.y;
+  const int kk = p.perm_kk, C = p.perm_c, d = p.d;
+  int ext0, n_ext;
+  if (grp < perm_groups) {
+    const int c0 = grp * RED_CB, len = min(RED_CB, C - c0);
+    ext0 = c0 * kk;
+    n_ext = len * kk;
+    // below / on the diagonal: 4 rows x 8 columns per warp; above: 32 rows x 1 column per warp
+    const int rrA = warp * 4 + (lane >> 3), eA = lane & 7, giA = gi0 + rrA;
+    const int rrB = lane, eB = warp, giB = gi0 + rrB;
+    const bool okA = eA < len && giA < d, okB = eB < len && giB < d;
+#pragma unroll 3
+    for (int run = 0; run < kk; ++run) {
+      const int gjA = run * C + c0 + eA, gjB = run * C + c0 + eB;
+      float vA = 0.f, vB = 0.f;
+      const bool doA = okA && gjA <= giA, doB = okB && gjB > giB;
+      if (doA) vA = reduce_fetch(p.partial, p.splits, giA, gjA);
+      if (doB) vB = reduce_fetch(p.partial, p.splits, gjB, giB);
+      if (doA) rs[rrA * pitch + eA * kk + run] = vA;
+      if (doB) rs[rrB * pitch + eB * kk + run] = vB;
+    }
+  } else {
+    ext0 = (perm_groups > 0 ? p.dcols : 0) + (grp - perm_groups) * RED_W;
+    n_ext = min(RED_W, d - ext0);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int rrA = warp + 8 * k, giA = gi0 + rrA, gjA = ext0 + lane;
+      const int eB = warp + 8 * k, giB = gi0 + lane, gjB = ext0 + eB;
+      const bool doA = lane < n_ext && giA < d && gjA <= giA;
+      const bool doB = eB < n_ext && giB < d && gjB > giB;
+      float vA = 0.f, vB = 0.f;
+      if (doA) vA = reduce_fetch(p.partial, p.splits, giA, gjA);
+      if (doB) vB = reduce_fetch(p.partial, p.splits, gjB, giB);
+      if (doA) rs[rrA * pitch + lane] = vA;
+      if (doB) rs[lane * pitch + eB] = vB;
+    }
+  }
+  __syncthreads();
+  const bool bad = p.status && *p.status != 0;
+  for (int rr = warp; rr < RED_ROWS; rr += 8) {
+    const int gi = gi0 + rr;
+    if (gi >= d) break;
+    const int gr = (C > 0 && gi < p.dcols) ? (gi % C) * kk + gi / C : gi;
+    float* orow = p.out + (int64_t)gr * p.ldo + ext0;
+    for (int e = lane; e < n_ext; e += 32) {
+      float v = p.alpha * rs[rr * pitch + e];
+      if (bad) v = __int_as_float(0x7fc00000);
+      orow[e] = (p.beta == 0.f) ? v : fmaf(p.beta, orow[e], v);
+    }
+  }
+}
+
+// Tile-wise variant of the finishing kernel: one CTA sums 1024 elements of one partial tile with
+// 16-byte loads and scatters them (and their mirror) to the output.  It wins when many splits
+// make the partial tiles, not the output, the bulk of the traffic.
+__global__ void __launch_bounds__(256) factor_tc_reduce_tiles(const FactorParams p) {
   int bi, bj;
   tri_decode(blockIdx.x, bi, bj);
   const float* src = p.partial + (int64_t)blockIdx.x * p.splits * (TILE * TILE);
@@ -458,9 +547,7 @@ static int tc_launch_typed(FactorParams p, int tiles, cudaStream_t st) {
   tc::factor_tc_kernel<T><<<dim3(tiles, p.splits), tc::THREADS, smem, st>>>(
       p, g_flush_stages > 0 ? g_flush_stages : C::FLUSH);
   SSO_LAUNCH_OK("factor_tc_kernel");
-  tc::factor_tc_reduce<<<dim3(tiles, 128 * 128 / (256 * 4)), 256, 0, st>>>(p);
-  SSO_LAUNCH_OK("factor_tc_reduce");
-  return 0;
+  return factor_tc_run_reduce(p, tiles, st);
 }
 
 int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, cudaStream_t st) {
@@ -484,7 +571,27 @@ int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspac
 }
 
 int factor_tc_run_reduce(const FactorParams& p, int tiles, cudaStream_t st) {
-  tc::factor_tc_reduce<<<dim3(tiles, 128 * 128 / (256 * 4)), 256, 0, st>>>(p);
+  // few splits of a large permuted factor: the output dominates, write it in whole rows
+  if (!(p.perm_c > 0 && p.splits <= 3 && p.d >= 1024)) {
+    tc::factor_tc_reduce_tiles<<<dim3(tiles, 128 * 128 / (256 * 4)), 256, 0, st>>>(p);
+    SSO_LAUNCH_OK("factor_tc_reduce_tiles");
+    return 0;
+  }
+  int perm_groups = 0, width = tc::RED_W;
+  if (p.perm_c > 0) {
+    perm_groups = ceil_div(p.perm_c, tc::RED_CB);
+    width = std::max(tc::RED_CB * p.perm_kk, 1);
+  }
+  const int plain_groups = p.perm_c > 0 ? (p.d > p.dcols ? 1 : 0) : ceil_div(p.d, tc::RED_W);
+  const int pitch = width | 1;
+  const size_t smem = (size_t)tc::RED_ROWS * pitch * sizeof(float);
+  SSO_CHECK_ARG(smem <= 200 * 1024, "factor: kernel window too large for the finishing kernel");
+  static bool configured = false;
+  if (!configured) {
+    SSO_CUDA_OK(cudaFuncSetAttribute(tc::factor_tc_reduce, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    configured = true;
+  }
+  tc::factor_tc_reduce<<<dim3(ceil_div(p.d, tc::RED_ROWS), perm_groups + plain_groups), 256, smem, st>>>(p, perm_groups, pitch);
   SSO_LAUNCH_OK("factor_tc_reduce");
   return 0;
 }
