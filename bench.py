@@ -181,6 +181,43 @@ def cpu_port_images_per_sec(batch, steps, seed=0):
     return batch / per_step, cores, sample, per_step
 
 
+def sgd_images_per_sec(batch, dev, steps=20):
+    """Stock torch SGD (momentum 0.9) on the same ResNet-50, bf16 autocast, channels_last inputs,
+    the whole step replayed from a CUDA graph: the denominator of the "fraction of SGD" figure."""
+    model = ResNet50().to(dev)
+    opt = torch.optim.SGD(model.parameters(), lr=1e-3, momentum=0.9)
+    x, y = synthetic_batch(batch, 1000, 7)
+    x = x.to(dev).contiguous(memory_format=torch.channels_last)
+    y = y.to(dev)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast('cuda', dtype=torch.bfloat16):
+            loss = F.cross_entropy(model(x).float(), y)
+        loss.backward()
+        opt.step()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return batch * steps / (e0.elapsed_time(e1) / 1e3)
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
@@ -230,7 +267,9 @@ def run_gpu_arm(args):
     nat.lib()
     torch.backends.cudnn.benchmark = True
     torch.manual_seed(0)
-    model = ResNet50().to(dev).to(memory_format=torch.channels_last)
+    model = ResNet50().to(dev)
+    if args.weights == 'channels_last':
+        model = model.to(memory_format=torch.channels_last)
     kw = dict(lr=1e-3)
     if world > 1:
         opt = torchsso.optim.DistributedSecondOrderOptimizer(model, 'Fisher', KRON, CURV_KW, **kw)
@@ -311,9 +350,15 @@ def run_gpu_arm(args):
     # Per-kernel timing of the dominant kernel (factor construction): CUDA events around every
     # factor launch, on the launching stream, over a few more steps of the same workload issued
     # eagerly (a replayed graph has no host-side call to bracket).
+    # The probe launches the hooks' kernels on the main stream: beside the model's kernels (side
+    # stream) a factor kernel's elapsed time includes waiting for SMs, which says nothing about it.
+    torchsso.utils.set_curvature_stream(False)
     nat.FACTOR_TIMING = []
     probe_steps = 3
     for i in range(probe_steps):
+        # hold the stream back ~25 ms so that the host runs ahead and the step's kernels execute
+        # back to back, as they do inside the replayed graph, instead of each starting on an idle GPU
+        torch.cuda._sleep(int(5e7))
         x_static.copy_(resident[i % NB][0]); y_static.copy_(resident[i % NB][1])
         opt.update_inv = False
         opt.step(closure=eager_closure)
@@ -356,6 +401,12 @@ def run_gpu_arm(args):
                      'launches': len(ft), 'total_ms': f_ms, 'measured_over_steps': probe_steps,
                      'flops_rule': '2*rows*d^2 per factor (what the reference einsum performs)'},
     }
+    if world == 1 and not args.no_sgd_baseline:
+        del closure, eager_closure, opt
+        sgd = sgd_images_per_sec(B, dev)
+        line['sgd_baseline'] = {'value': sgd, 'unit': 'images/sec', 'frac_of_sgd': ips / sgd,
+                                'note': 'stock torch SGD+momentum, same model / batch / bf16 autocast, '
+                                        'CUDA-graph replay, measured in this run'}
     if world == 1 and not args.no_cpu_baseline:
         val, cores, sample, _ = cpu_port_images_per_sec(args.cpu_batch, 2)
         line['cpu_baseline'] = {'value': val, 'unit': 'images/sec', 'cores': cores, 'kind': 'port',
@@ -385,6 +436,9 @@ def main():
     ap.add_argument('--batch', type=int, default=32, help='images per GPU')
     ap.add_argument('--cpu-batch', type=int, default=16, help='batch of the bounded CPU sample')
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-sgd-baseline', action='store_true')
+    ap.add_argument('--weights', default='contiguous', choices=['channels_last', 'contiguous'],
+                    help='memory format of the convolution weights (activations are channels_last)')
     ap.add_argument('--no-side-stream', dest='side_stream', action='store_false',
                     help='launch the curvature kernels of the hooks on the main stream')
     ap.add_argument('--no-graph', dest='graph', action='store_false',

@@ -5,6 +5,7 @@
     python pytorch-sso_b200/microbench.py inverse  [--case I]      damped SPD inverse, d in 64..4608
     python pytorch-sso_b200/microbench.py precond  [--case I]      G^-1 dW A^-1
     python pytorch-sso_b200/microbench.py stream                   EMA / axpby / BN plane sums
+    python pytorch-sso_b200/microbench.py peaks                    cuBLAS bf16 / TF32 GEMM and copy, for reference
     torchrun ... pytorch-sso_b200/microbench.py collective         factor exchange sweep (N > 1)
 
 Inputs are seeded N(0,1) tensors created on the device; every case moves more bytes than the
@@ -163,6 +164,26 @@ def suite_stream(args):
          frac_of_measured_hbm=round(nb / ms / 1e6 / hbm, 3))
 
 
+def suite_peaks(args):
+    """Library peaks on this GPU, timed like the other suites: cuBLAS bf16 and TF32 GEMM (the
+    3xTF32 kernels spend three TF32 MMAs per product, so their ceiling is a third of the TF32
+    figure) and a device-to-device copy."""
+    n = 8192
+    for name, dt, tf32 in (('bf16', torch.bfloat16, False), ('tf32', torch.float32, True)):
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        a = torch.randn((n, n), device='cuda', dtype=dt)
+        b = torch.randn((n, n), device='cuda', dtype=dt)
+        c = torch.empty((n, n), device='cuda', dtype=dt)
+        ms = timeit(lambda: torch.matmul(a, b, out=c), args.iters)
+        emit(suite='peaks', kernel='cuBLAS %s gemm %d^3' % (name, n), ms=round(ms, 4),
+             tflops=round(2.0 * n ** 3 / ms / 1e9, 1))
+    torch.backends.cuda.matmul.allow_tf32 = False
+    x = torch.empty(1 << 28, device='cuda')
+    y = torch.empty(1 << 28, device='cuda')
+    ms = timeit(lambda: y.copy_(x), args.iters)
+    emit(suite='peaks', kernel='copy 1 GiB', ms=round(ms, 4), gbs=round(2.0 * 4 * (1 << 28) / ms / 1e6, 1))
+
+
 def suite_collective(args):
     """Reduce-scatter of the tri-packed ResNet-50 factors to owner ranks and all-gather of the
     parameter-sized updates, as the distributed optimizer issues them (padded equal segments)."""
@@ -205,7 +226,7 @@ def suite_collective(args):
     dist.destroy_process_group()
 
 
-SUITES = {'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
+SUITES = {'peaks': suite_peaks, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
           'stream': suite_stream, 'collective': suite_collective}
 
 
