@@ -20,6 +20,7 @@ int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspac
 void factor_tc_set_flush(int stages);
 int factor_tc_flush_setting();
 bool factor_tma_supported(const FactorParams& p, int dtype);
+void factor_tma_set_pair_min_d(int d);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
 extern int g_engine_tc;
 static int g_tc_auto = 1;    // whether SSO_IMPL_AUTO may pick the tcgen05 kernels
@@ -40,6 +41,7 @@ int sso_configure(const char* key, int value) {
   if (k == "tc_auto") { g_tc_auto = value != 0; return 0; }
   if (k == "tma_auto") { g_tma_auto = value != 0; return 0; }
   if (k == "engine_tc") { g_engine_tc = value != 0; return 0; }
+  if (k == "tma_pair_min_d") { factor_tma_set_pair_min_d(value); return 0; }
   if (k == "tc_flush") { factor_tc_set_flush(value); return 0; }
   return fail(-1, "configure: unknown key %s", key);
 }

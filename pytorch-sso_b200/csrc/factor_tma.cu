@@ -213,6 +213,226 @@ factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CU
   }
 }
 
+// ---- CTA-pair variant ----------------------------------------------------------------------------
+// Two CTAs of a cluster compute one 256x256 block of the result with tcgen05.mma.cta_group::2:
+// CTA r of the pair stages columns [256I + 128r, +128) of the A side and columns [256J + 128r, +128)
+// of the B side (its half of N) - the same four 64-column boxes per stage as the single-CTA
+// kernel - but each byte in shared memory now feeds twice the tensor work (M = 256, N = 256), which
+// is what the single-CTA kernel, bound by the L2 -> shared-memory feed, lacks.  The leader CTA
+// (rank 0) issues the MMAs; all TMA loads of both CTAs complete on the leader's "full" barrier;
+// tcgen05.commit with a cluster multicast releases the stage ("empty") and publishes the
+// accumulator ("accfull") in both CTAs; every accumulate warp of both CTAs arrives on the leader's
+// "accempty".  Each CTA keeps rows [128r, +128) x 256 columns of the block in its own TMEM
+// (2 x 256 columns) and writes them as two ordinary 128x128 partial tiles, so the finishing
+// kernels are shared with the other factor kernels.  No multicast loads, no peer-GPU memory.
+constexpr uint32_t TMEM_COLS2 = 512;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma2_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc),
+      "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at the same shared-memory offset in both CTAs of the pair once all MMAs
+// issued so far have completed
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
+}
+// instruction descriptor: D fp32, A/B 16-bit format `fmt`, both MN-major, M = 256 (pair), N = 256
+__device__ __forceinline__ uint32_t instr_desc_pair(uint32_t fmt) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(256 >> 3) << 17) |
+         ((uint32_t)(256 >> 4) << 24);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant__ CUtensorMap tmap) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  int bI, bJ;
+  tri_decode(blockIdx.x >> 1, bI, bJ);        // 256-wide block row / column of the pair
+  const bool share = (bI == bJ);
+  const int split = blockIdx.y;
+  const int s_begin = split * g.stages_per_split;
+  const int s_end = min(g.total_stages, s_begin + g.stages_per_split);
+  const int nstages = max(0, s_end - s_begin);
+  const int flush = g.flush;
+  const int nchunks = ceil_div(nstages, flush);
+  int* status = p.status;
+
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto accfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto accempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accfull_bar(b), 1);
+      mbar_init(accempty_bar(b), 2 * EPI_WARPS);   // the accumulate warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (uint32_t o = tid * 16u; o < STAGES * STAGE_BYTES; o += THREADS * 16u)
+    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(smem0 + o), "r"(0u) : "memory");
+  fence_async_smem();
+  if (warp == MMA_WARP) tmem_alloc2(smem_u32(&tmem_base_slot), TMEM_COLS2);
+  tc_fence_before();
+  cluster_sync_all();          // barriers of both CTAs are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
+
+  // valid 64-column blocks of a CTA of rank rr: A0 A1 (rows of the block), B0 B1 (its half of the columns)
+  auto block_col = [&](uint32_t rr, int e) { return ((e >> 1) == 0 ? bI : bJ) * 256 + (int)rr * TILE + (e & 1) * 64; };
+  auto block_valid = [&](uint32_t rr, int e) { return block_col(rr, e) < p.dcols && !(share && (e >> 1) == 1); };
+
+  if (warp < EPI_WARPS) {
+    // ------------------------------------------------------------------ accumulate warps
+    // warp = 4*half + q: TMEM lanes 32q.., columns [128*half, +128) = one 128x128 tile of the result
+    const int q = warp & 3, half = warp >> 2;
+    float acc[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+    const uint32_t leader_accempty0 = map_to_cta(accempty_bar(0), 0u);
+    for (int c = 0; c < nchunks; ++c) {
+      const int b = c & 1;
+      if (!mbar_wait(accfull_bar(b), (c >> 1) & 1, status, 33)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * 256 + half * 128);
+#pragma unroll
+      for (int part = 0; part < 4; ++part) {
+        uint32_t v[32];
+        tmem_ld32(taddr + part * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[part * 32 + i] += __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_accempty0 + 8u * b);
+    }
+    const int ti = 2 * bI + (int)rank, tj = 2 * bJ + half;
+    const int nb = ceil_div(p.d, TILE);
+    if (ti < nb && tj <= ti) {
+      float* dst = p.partial + ((int64_t)(ti * (ti + 1) / 2 + tj) * p.splits + split) * (TILE * TILE) +
+                   (q * 32 + lane) * TILE;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    }
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = instr_desc_pair(g.fmt);
+      const int nk = g.kpad / 16;
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int slot = s % STAGES, c = s / flush, b = c & 1;
+        const bool first_of_chunk = (s % flush) == 0;
+        if (first_of_chunk && c >= 2) ok = mbar_wait(accempty_bar(b), ((c >> 1) - 1) & 1, status, 32);
+        if (!ok) break;
+        ok = mbar_wait(full_bar(slot), (s / STAGES) & 1, status, 31);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a0 = smem0 + slot * STAGE_BYTES;
+        const uint32_t b0 = share ? a0 : a0 + 2 * BLOCK_BYTES_MAX;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * 256);
+        for (int ks = 0; ks < nk; ++ks) {
+          const uint64_t ad = smem_desc_sw128(a0 + ks * 2048u, blk_bytes, 1024u);
+          const uint64_t bd = smem_desc_sw128(b0 + ks * 2048u, blk_bytes, 1024u);
+          umma2_f16(d_tmem, ad, bd, idesc, (first_of_chunk && ks == 0) ? 0u : 1u);
+        }
+        umma2_commit_both(empty_bar(slot));
+        if ((s % flush) == flush - 1 || s == nstages - 1) umma2_commit_both(accfull_bar(b));
+      }
+    }
+  } else if (warp == PROD_WARP) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int bc0[4], bx[4], by[4];
+      bool bvalid[4];
+      int nvalid_pair = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j0 = block_col(rank, e);
+        bvalid[e] = block_valid(rank, e);
+        const int pos = j0 / p.c;
+        const int ky = pos / p.kw, kx = pos - ky * p.kw;
+        bc0[e] = j0 - pos * p.c;
+        bx[e] = kx * p.dil_w - p.pad_w;
+        by[e] = ky * p.dil_h - p.pad_h;
+        nvalid_pair += (block_valid(0u, e) ? 1 : 0) + (block_valid(1u, e) ? 1 : 0);
+      }
+      const uint32_t box_bytes = (uint32_t)g.kstage * 128u;
+      const uint64_t tmap_ptr = reinterpret_cast<uint64_t>(&tmap);
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int slot = s % STAGES;
+        if (s >= STAGES) ok = mbar_wait(empty_bar(slot), ((s / STAGES) - 1) & 1, status, 34);
+        if (!ok) break;
+        const int sg = s_begin + s;
+        const int n0 = (sg / g.ystages) * g.bn;
+        const int oy0 = (sg % g.ystages) * g.bh;
+        // the loads of both CTAs complete on the leader's barrier; the leader announces the bytes
+        const uint32_t fb = map_to_cta(full_bar(slot), 0u);
+        if (rank == 0)
+          asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(slot)), "r"(box_bytes * nvalid_pair) : "memory");
+        const uint32_t sb = smem0 + slot * STAGE_BYTES;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (!bvalid[e]) continue;
+          const uint32_t dst = sb + (e >> 1) * 2 * BLOCK_BYTES_MAX + (e & 1) * blk_bytes;
+          asm volatile(
+              "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+              ::"r"(dst), "l"(tmap_ptr), "r"(bc0[e]), "r"(bx[e]), "r"(oy0 * p.stride_h + by[e]), "r"(n0), "r"(fb)
+              : "memory");
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();          // neither CTA leaves while its peer may still read its shared memory
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, TMEM_COLS2);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -302,6 +522,9 @@ bool factor_tma_supported(const FactorParams& p, int dtype) {
   return tma::encode_fn() != nullptr;
 }
 
+static int g_pair_min_d = 512;  // factors at least this wide use the CTA-pair kernel; 0 = never
+void factor_tma_set_pair_min_d(int d) { g_pair_min_d = d < 0 ? 0 : d; }
+
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush,
                       cudaStream_t st) {
   using namespace tma;
@@ -309,7 +532,10 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   SSO_CHECK_ARG(choose_box(p, g), "factor (tma): unsupported geometry");
   const int nb = ceil_div(p.d, 128);
   const int tiles = nb * (nb + 1) / 2;
-  choose_splits(g.total_stages, tiles, p.splits, g.stages_per_split);
+  const bool pair = g_pair_min_d > 0 && p.d >= g_pair_min_d;
+  const int nb2 = ceil_div(p.d, 256);
+  const int pair_blocks = nb2 * (nb2 + 1) / 2;
+  choose_splits(g.total_stages, pair ? 2 * pair_blocks : tiles, p.splits, g.stages_per_split);
   // fit the partial tiles into the scratch the caller sized with sso_factor_workspace_bytes
   SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= 256 + (size_t)tiles * 65536,
                 "factor workspace too small for the tensor-core path");
@@ -345,6 +571,16 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   if (!configured) {
     SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
+  }
+  if (pair) {
+    static bool configured2 = false;
+    if (!configured2) {
+      SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured2 = true;
+    }
+    factor_tma_pair_kernel<<<dim3(2 * pair_blocks, p.splits), THREADS, smem, st>>>(p, g, tmap);
+    SSO_LAUNCH_OK("factor_tma_pair_kernel");
+    return factor_tc_run_reduce(p, tiles, st);
   }
   factor_tma_kernel<<<dim3(tiles, p.splits), THREADS, smem, st>>>(p, g, tmap);
   SSO_LAUNCH_OK("factor_tma_kernel");
