@@ -23,6 +23,9 @@ namespace sso {
 
 int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
 int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
+int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, int count, int* status_dev, cudaStream_t st);
+bool tma_encode_f32_rows(void* out, const float* base, int64_t rows, int64_t cols, int64_t ld);
+int g_engine_tma = 1;   // k-contiguous 128-wide tasks fetch their operands with TMA (tensor maps per task)
 int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
 
 constexpr int NB = 64;  // algorithmic block size of the factorisations
@@ -317,6 +320,8 @@ struct Plan {
   float* d_traces = nullptr;
   float* d_shift = nullptr;
   int* d_status = nullptr;   // set by a tensor-core tile task whose wait gave up
+  unsigned char* d_maps = nullptr;   // 256 bytes per task: tensor maps of A and B (k-contiguous tasks only)
+  bool have_maps = false;
   int first_scaled_task = -1, n_scaled_tasks = 0;  // sample plan: tasks whose alpha is std_scale
   bool host_only = false;
 };
@@ -472,7 +477,7 @@ static void emit_copy(Builder& b, const float* src, float* dst, int d, int mat, 
 }
 
 static size_t plan_table_bytes(size_t tasks, size_t diags, size_t copies, size_t mats) {
-  return align_up(tasks * sizeof(sso_tile_task)) + align_up(diags * sizeof(DiagRec)) +
+  return align_up(tasks * 256) + align_up(tasks * sizeof(sso_tile_task)) + align_up(diags * sizeof(DiagRec)) +
          align_up(copies * sizeof(CopyRec)) + align_up(mats * sizeof(MatRec)) +
          2 * align_up(mats * sizeof(float)) + 256;
 }
@@ -482,6 +487,8 @@ static int upload(Plan& p, void* dev_mem, size_t dev_bytes) {
   SSO_CHECK_ARG(dev_mem != nullptr && dev_bytes >= need, "plan device memory too small: need %zu, got %zu",
                 need, dev_bytes);
   char* q = reinterpret_cast<char*>(dev_mem);
+  q = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(q)));
+  p.d_maps = reinterpret_cast<unsigned char*>(q); q += align_up(p.tasks.size() * 256);
   p.d_tasks = reinterpret_cast<sso_tile_task*>(q); q += align_up(p.tasks.size() * sizeof(sso_tile_task));
   p.d_diags = reinterpret_cast<DiagRec*>(q); q += align_up(p.diags.size() * sizeof(DiagRec));
   p.d_copies = reinterpret_cast<CopyRec*>(q); q += align_up(p.copies.size() * sizeof(CopyRec));
@@ -492,6 +499,28 @@ static int upload(Plan& p, void* dev_mem, size_t dev_bytes) {
   SSO_CUDA_OK(cudaMemset(p.d_status, 0, 256));
   if (!p.tasks.empty())
     SSO_CUDA_OK(cudaMemcpy(p.d_tasks, p.tasks.data(), p.tasks.size() * sizeof(sso_tile_task), cudaMemcpyHostToDevice));
+  // tensor maps for the tasks of the k-contiguous phases (operand = rows of a row-major matrix)
+  p.have_maps = false;
+  if (g_engine_tma && !p.tasks.empty()) {
+    std::vector<unsigned char> maps(p.tasks.size() * 256, 0);
+    bool ok = true, any = false;
+    auto encode_phase = [&](const sso_phase& ph) {
+      if (ph.kind != 4) return;
+      for (int i = ph.first; i < ph.first + ph.count && ok; ++i) {
+        const sso_tile_task& t = p.tasks[i];
+        ok = tma_encode_f32_rows(&maps[(size_t)i * 256], t.A, t.m, t.k, t.lda) &&
+             tma_encode_f32_rows(&maps[(size_t)i * 256 + 128], t.B, t.n, t.k, t.ldb);
+        any = true;
+      }
+    };
+    for (auto& ph : p.inv_phases) encode_phase(ph);
+    for (auto& ph : p.std_phases) encode_phase(ph);
+    for (auto& ph : p.run_phases) encode_phase(ph);
+    if (ok && any) {
+      SSO_CUDA_OK(cudaMemcpy(p.d_maps, maps.data(), maps.size(), cudaMemcpyHostToDevice));
+      p.have_maps = true;
+    }
+  }
   if (!p.diags.empty())
     SSO_CUDA_OK(cudaMemcpy(p.d_diags, p.diags.data(), p.diags.size() * sizeof(DiagRec), cudaMemcpyHostToDevice));
   if (!p.copies.empty())
@@ -515,7 +544,9 @@ static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* 
         break;
       case 4:
         if (g_engine_tc) {
-          const int rc = launch_tile_tasks_kc(p.d_tasks + ph.first, ph.count, p.d_status, st);
+          const int rc = p.have_maps
+              ? launch_tile_tasks_tma(p.d_tasks + ph.first, p.d_maps + (size_t)ph.first * 256, ph.count, p.d_status, st)
+              : launch_tile_tasks_kc(p.d_tasks + ph.first, ph.count, p.d_status, st);
           if (rc) return rc;
           continue;
         }

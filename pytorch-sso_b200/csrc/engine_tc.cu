@@ -331,14 +331,14 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tc_kernel(const sso_tile
 // registers; the load warps then split each of their own chunks in place (hi overwrites the raw
 // value, lo goes to a ring of LO_SLOTS stages) and hand the stage to the MMA warp.
 // ------------------------------------------------------------------------------------------
-constexpr int RAW_SLOTS = 5, LO_SLOTS = 2, PREFETCH = 3;
 constexpr uint32_t PART = 2 * OPB;                       // A and B of one stage, one flavour (raw/hi or lo)
-constexpr uint32_t KC_SMEM = (RAW_SLOTS + LO_SLOTS) * PART;
+constexpr uint32_t KC_SMEM = 7 * PART;                   // RAW_SLOTS + LO_SLOTS = 7 in every variant
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 
+template <int RAW_SLOTS, int LO_SLOTS, int PREFETCH>
 __global__ void __launch_bounds__(THREADS, 1) tile_task_kc_kernel(const sso_tile_task* __restrict__ tasks, int* status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[RAW_SLOTS + 2 * LO_SLOTS + 4];
@@ -468,16 +468,165 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_kc_kernel(const sso_tile
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// TMA-fed variant of the k-contiguous kernel: the two operand boxes of a stage (128 rows x 32 k,
+// fp32) are fetched by one thread with cp.async.bulk.tensor into the raw ring (tensor maps made
+// on the host when the plan is built, two per task), so the loads no longer pass through the
+// load/store units.  The load warps only split: hi in place, lo into the second ring.
+// ------------------------------------------------------------------------------------------
+struct alignas(128) TaskMaps {
+  unsigned char a[128];
+  unsigned char b[128];
+};
+
+template <int RAW_SLOTS, int LO_SLOTS, int PREFETCH>
+__global__ void __launch_bounds__(THREADS, 1) tile_task_tma_kernel(const sso_tile_task* __restrict__ tasks,
+                                                                    const TaskMaps* __restrict__ maps, int* status) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * RAW_SLOTS + 2 * LO_SLOTS + 4];
+  __shared__ uint32_t tmem_base_slot;
+  const sso_tile_task t = tasks[blockIdx.x];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nstages = ceil_div(t.k, KS);
+  const int nchunks = ceil_div(nstages, FLUSH);
+
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t lo0 = smem0 + RAW_SLOTS * PART;
+  const uint32_t bar0 = smem_u32(bars);
+  auto rawfree_bar = [&](int s) { return bar0 + 8u * s; };
+  auto rawfull_bar = [&](int s) { return bar0 + 8u * (RAW_SLOTS + s); };
+  auto full_bar = [&](int s) { return bar0 + 8u * (2 * RAW_SLOTS + s); };
+  auto lofree_bar = [&](int s) { return bar0 + 8u * (2 * RAW_SLOTS + LO_SLOTS + s); };
+  const uint32_t accfull0 = bar0 + 8u * (2 * RAW_SLOTS + 2 * LO_SLOTS), accempty0 = accfull0 + 16u;
+  if (tid == 0) {
+    for (int s = 0; s < RAW_SLOTS; ++s) {
+      mbar_init(rawfree_bar(s), 1);
+      mbar_init(rawfull_bar(s), 1);
+    }
+    for (int s = 0; s < LO_SLOTS; ++s) {
+      mbar_init(full_bar(s), LOAD_WARPS);
+      mbar_init(lofree_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accfull0 + 8u * b, 1);
+      mbar_init(accempty0 + 8u * b, EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp < EPI_WARPS) {
+    float* ct = reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw)));
+    accumulate_and_store(t, tmem_base, accfull0, accempty0, nchunks, status, ct, warp, lane);
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(2u, 0u);   // tf32, K-major
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS, c = s / FLUSH, b = c & 1;
+        const bool first_of_chunk = (s % FLUSH) == 0;
+        if (first_of_chunk && c >= 2) ok = mbar_wait(accempty0 + 8u * b, ((c >> 1) - 1) & 1, status, 42);
+        if (!ok) break;
+        ok = mbar_wait(full_bar(ls), (s / LO_SLOTS) & 1, status, 41);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ah = smem0 + rs * PART, bh = ah + OPB, al = lo0 + ls * PART, bl = al + OPB;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TILE);
+#pragma unroll
+        for (int ks = 0; ks < KS / 8; ++ks) {
+          const uint64_t adh = smem_desc_sw128_kmajor(ah + ks * 32u), adl = smem_desc_sw128_kmajor(al + ks * 32u);
+          const uint64_t bdh = smem_desc_sw128_kmajor(bh + ks * 32u), bdl = smem_desc_sw128_kmajor(bl + ks * 32u);
+          umma<true>(d_tmem, adl, bdh, idesc, (first_of_chunk && ks == 0) ? 0u : 1u);
+          umma<true>(d_tmem, adh, bdl, idesc, 1u);
+          umma<true>(d_tmem, adh, bdh, idesc, 1u);
+        }
+        umma_commit(rawfree_bar(rs));
+        umma_commit(lofree_bar(ls));
+        if ((s % FLUSH) == FLUSH - 1 || s == nstages - 1) umma_commit(accfull0 + 8u * b);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ producer thread + split warps
+    const int lt = tid - 32 * (MMA_WARP + 1);
+    const int q = lt >> 3, l8 = lt & 7;
+    const uint32_t so0 = sw_off(q, l8 * 4);
+    const uint64_t map_a = reinterpret_cast<uint64_t>(maps[blockIdx.x].a), map_b = reinterpret_cast<uint64_t>(maps[blockIdx.x].b);
+    bool ok = true;
+    auto issue = [&](int s) {       // one thread: both boxes of stage s
+      const int rs = s % RAW_SLOTS;
+      if (s >= RAW_SLOTS && !mbar_wait(rawfree_bar(rs), ((s / RAW_SLOTS) - 1) & 1, status, 44)) { ok = false; return; }
+      const uint32_t fb = rawfull_bar(rs), dst = smem0 + rs * PART;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(PART) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(dst), "l"(map_a), "r"(s * KS), "r"(0), "r"(fb) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                   ::"r"(dst + OPB), "l"(map_b), "r"(s * KS), "r"(0), "r"(fb) : "memory");
+    };
+    if (lt == 0)
+      for (int s = 0; s < PREFETCH && s < nstages; ++s) issue(s);
+    for (int s = 0; s < nstages; ++s) {
+      if (lt == 0 && s + PREFETCH < nstages) issue(s + PREFETCH);
+      const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS;
+      if (!mbar_wait(rawfull_bar(rs), (s / RAW_SLOTS) & 1, status, 46)) break;
+      if (s >= LO_SLOTS && !mbar_wait(lofree_bar(ls), ((s / LO_SLOTS) - 1) & 1, status, 45)) break;
+      const uint32_t hi = smem0 + rs * PART + so0, lo = lo0 + ls * PART + so0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t off = (uint32_t)(j & 3) * 4096u + (uint32_t)(j >> 2) * OPB;
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(hi + off) : "memory");
+        const uint32_t h0 = rna_tf32(v.x), h1 = rna_tf32(v.y), h2 = rna_tf32(v.z), h3 = rna_tf32(v.w);
+        const uint32_t l0 = __float_as_uint(v.x - __uint_as_float(h0)), l1 = __float_as_uint(v.y - __uint_as_float(h1));
+        const uint32_t l2 = __float_as_uint(v.z - __uint_as_float(h2)), l3 = __float_as_uint(v.w - __uint_as_float(h3));
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(hi + off), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(lo + off), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar(ls));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 }  // namespace etc
+
+int g_kc_variant = 0;
+
+int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, int count, int* status_dev, cudaStream_t st) {
+  const size_t smem = (size_t)etc::KC_SMEM + 1024;
+  static bool configured = false;
+  if (!configured) {
+    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_tma_kernel<5, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  etc::tile_task_tma_kernel<5, 2, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, reinterpret_cast<const etc::TaskMaps*>(maps_dev), status_dev);
+  SSO_LAUNCH_OK("tile_task_tma_kernel");
+  return 0;
+}
 
 int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st) {
   const size_t smem = (size_t)etc::KC_SMEM + 1024;
   static bool configured = false;
   if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel<5, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel<4, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel<4, 3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  etc::tile_task_kc_kernel<<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
+  if (g_kc_variant == 1) etc::tile_task_kc_kernel<4, 3, 2><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
+  else if (g_kc_variant == 2) etc::tile_task_kc_kernel<4, 3, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
+  else etc::tile_task_kc_kernel<5, 2, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
   SSO_LAUNCH_OK("tile_task_kc_kernel");
   return 0;
 }

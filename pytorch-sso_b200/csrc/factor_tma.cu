@@ -511,6 +511,21 @@ static void choose_splits(int total_stages, int tiles, int& splits, int& stages_
 
 }  // namespace tma
 
+// Tensor map of a row-major fp32 matrix [rows][cols] with leading dimension ld (elements), for
+// boxes of 32 columns x 128 rows landing in the SWIZZLE_128B layout; out-of-range reads give zero.
+// `out` must hold 128 bytes.  False if the driver entry point is missing or the encode fails.
+bool tma_encode_f32_rows(void* out, const float* base, int64_t rows, int64_t cols, int64_t ld) {
+  auto fn = tma::encode_fn();
+  if (!fn) return false;
+  const cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t gstr[1] = {(cuuint64_t)ld * 4};
+  const cuuint32_t box[2] = {32u, 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  return fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim,
+            gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool factor_tma_supported(const FactorParams& p, int dtype) {
   if (dtype != SSO_BF16 && dtype != SSO_F16) return false;
   if (p.sc != 1 || p.c % 64 != 0 || p.weight != nullptr || p.d != p.dcols) return false;
