@@ -202,6 +202,63 @@ def test_factor_tma_conv_matches_oracle(nat, cfg, dtype):
     assert torch.equal(out, again)
 
 
+@pytest.mark.parametrize('cfg', TMA_CONVS)
+@pytest.mark.parametrize('pair_min_d', [64, 0])
+def test_factor_tma_pair_and_single_kernels(nat, cfg, pair_min_d):
+    """The CTA-pair kernel (tcgen05.mma.cta_group::2, forced for every width) and the single-CTA
+    kernel (pair kernel switched off) both match the oracle, bitwise symmetric and reproducible."""
+    n, c, h, w, k, s, p, d = cfg
+    x = cases.make_normal((n, c, h, w), 291 + c + h).bfloat16()
+    ref = ko.conv_factor_A(x.double(), k, s, p, d, False)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    nat.configure('tma_pair_min_d', pair_min_d)
+    try:
+        out = torch.full(tuple(ref.shape), float('nan'), device='cuda')
+        nat.factor_im2col(xd, k, s, p, d, False, None, 1.0 / n, 0.0, out, nat.IMPL_TMA)
+        again = torch.full_like(out, float('nan'))
+        nat.factor_im2col(xd, k, s, p, d, False, None, 1.0 / n, 0.0, again, nat.IMPL_TMA)
+    finally:
+        nat.configure('tma_pair_min_d', 512)
+    assert rel(out, ref) < FACTOR_TOL
+    assert torch.equal(out, out.t())
+    assert torch.equal(out, again)
+
+
+def test_factor_tma_pair_accumulates_with_beta(nat):
+    """alpha / beta epilogue through both finishing kernels (d = 1152 is wide enough for the
+    row-wise one when there are few splits)."""
+    n, c, h, w = 4, 128, 10, 10
+    x = cases.make_normal((n, c, h, w), 77).bfloat16()
+    ref = ko.conv_factor_A(x.double(), (3, 3), (1, 1), (1, 1), (1, 1), False)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    base = cases.make_normal(tuple(ref.shape), 78)
+    out = dev(base).clone()
+    nat.factor_im2col(xd, (3, 3), (1, 1), (1, 1), (1, 1), False, None, 0.5 / n, 0.25, out, nat.IMPL_TMA)
+    assert rel(out, 0.5 * ref + 0.25 * base.double()) < FACTOR_TOL
+
+
+@pytest.mark.parametrize('engine_tma', [0, 1])
+def test_precondition_kernel_variants_agree(nat, engine_tma):
+    """k-contiguous tile tasks fed by TMA (tensor maps per task) or by cp.async give the oracle's
+    preconditioned gradient."""
+    da, dg = 1152, 256
+    Ai, Gi = spd_pair(da, dg, 160)
+    gw = cases.make_normal((dg, da), 161) * 0.1
+    rw, _ = ko.kron_precondition(Ai.double(), Gi.double(), gw.double(), None)
+    nat.configure('engine_tma', engine_tma)
+    try:
+        dgw = dev(gw)
+        tmp = torch.empty(dg * da, device='cuda')
+        plan = nat.precond_plan([da], [dg], [dev(Ai)], [dev(Gi)], [dgw], [None], [tmp], torch.device('cuda'))
+        kinds = [k for k, _, _ in plan.phases()]
+        nat.precond_plan_run(plan)
+        torch.cuda.synchronize()
+    finally:
+        nat.configure('engine_tma', 1)
+    assert 4 in kinds            # both products run as k-contiguous phases
+    assert rel(dgw, rw) < INV_TOL
+
+
 @pytest.mark.parametrize('rows,cols', [(300, 64), (1000, 2048), (100352, 64), (77, 128)])
 def test_factor_tma_rows_matches_oracle(nat, rows, cols):
     x = cases.make_normal((rows, cols), 5 + rows).clamp_min(-0.5).bfloat16()
