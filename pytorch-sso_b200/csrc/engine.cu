@@ -171,70 +171,80 @@ __global__ void __launch_bounds__(256) diag_block_kernel(const DiagRec* __restri
       a[i][j] = v;
       x[i][j] = (r == c) ? 1.f : 0.f;
     }
-  // ---- Cholesky
-  for (int j = 0; j < NB; ++j) {
-    const int jb = j >> 2, jj = j & 3;
-    if (tx == jb) {
+  // ---- Cholesky.  Columns are walked in groups of four so that the position of column j inside
+  // a thread's 4x4 block (jj) is a compile-time constant and the selects below fold away.
+  for (int jb = 0; jb < NB / 4; ++jb) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+    for (int jj = 0; jj < 4; ++jj) {
+      const int j = 4 * jb + jj;
+      if (tx == jb) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          if (q == jj && r0 + i >= j) colbuf[j & 1][r0 + i] = a[i][q];
-    }
-    __syncthreads();
-    float pv = colbuf[j & 1][j];
-    if (!(pv > 0.f)) {   // non-positive or NaN pivot: record once, continue with 1
-      if (tid == 0 && info && j < n) atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + j + 1);
-      pv = 1.f;
-    }
-    const float inv = 1.f / pv, rs = rsqrtf(pv);
-    float cr[4], cc[4];
+        for (int i = 0; i < 4; ++i)
+          if (r0 + i >= j) colbuf[j & 1][r0 + i] = a[i][jj];
+      }
+      __syncthreads();
+      float pv = colbuf[j & 1][j];
+      if (!(pv > 0.f)) {   // non-positive or NaN pivot: record once, continue with 1
+        if (tid == 0 && info && j < n) atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + j + 1);
+        pv = 1.f;
+      }
+      const float inv = 1.f / pv, rs = rsqrtf(pv);
+      if (ty >= jb && tx >= jb && tx <= ty) {     // blocks that column j still touches (lower triangle)
+        float cr[4], cc[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      cr[i] = colbuf[j & 1][r0 + i];
-      cc[i] = colbuf[j & 1][c0 + i];
-    }
+        for (int i = 0; i < 4; ++i) {
+          cr[i] = colbuf[j & 1][r0 + i];
+          cc[i] = colbuf[j & 1][c0 + i] * inv;
+        }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int r = r0 + i, c = c0 + q;
-        if (r > j && c > j && c <= r) a[i][q] -= cr[i] * cc[q] * inv;
-        if (c == j && r >= j) {          // finish column j of the factor
-          const float l = (r == j) ? sqrtf(pv) : a[i][q] * rs;
-          a[i][q] = l;
-          Ls[r][j] = l;
+          for (int q = 0; q < 4; ++q) {
+            const int r = r0 + i, c = c0 + q;
+            if (r > j && c > j && c <= r) a[i][q] -= cr[i] * cc[q];
+          }
+        if (tx == jb) {                           // finish column j of the factor
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = r0 + i;
+            if (r >= j) {
+              const float l = (r == j) ? sqrtf(pv) : a[i][jj] * rs;
+              a[i][jj] = l;
+              Ls[r][j] = l;
+            }
+          }
         }
       }
-    if (tid == 0) dinv[j] = rs;
+      if (tid == 0) dinv[j] = rs;
+    }
   }
   __syncthreads();
   // ---- inverse of the factor: X starts as I; for k: row k of X /= L_kk, rows r > k -= L_rk * row k
-  for (int k = 0; k < NB; ++k) {
-    const int kb = k >> 2, kk = k & 3;
-    if (ty == kb) {
-      const float d = dinv[k];
+  for (int kb = 0; kb < NB / 4; ++kb) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+    for (int kk = 0; kk < 4; ++kk) {
+      const int k = 4 * kb + kk;
+      if (ty == kb) {
+        const float d = dinv[k];
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          if (i == kk) {
-            x[i][q] *= d;
-            rowbuf[k & 1][c0 + q] = x[i][q];
+        for (int q = 0; q < 4; ++q) {
+          x[kk][q] *= d;
+          rowbuf[k & 1][c0 + q] = x[kk][q];
+        }
+      }
+      __syncthreads();
+      if (c0 <= k && ty >= kb) {
+        float xr[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) xr[q] = rowbuf[k & 1][c0 + q];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = r0 + i;
+          if (r > k) {
+            const float l = Ls[r][k];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) x[i][q] -= l * xr[q];
           }
-    }
-    __syncthreads();
-    if (c0 <= k) {
-      float xr[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) xr[q] = rowbuf[k & 1][c0 + q];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = r0 + i;
-        if (r > k) {
-          const float l = Ls[r][k];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) x[i][q] -= l * xr[q];
         }
       }
     }
