@@ -195,6 +195,9 @@ typedef struct {
   int32_t mat;        /* matrix index (for info) */
   int32_t row0;       /* first global row of the block (for info) */
   int32_t info_slot;  /* 0 inverse pass, 1 Cholesky-of-inverse pass */
+  float* LinvT;       /* optional: also receives the transpose of that inverse (upper triangular) */
+  int32_t ld_invt;
+  int32_t pad;
 } sso_diag_rec;
 
 /* copy record: a run of whole rows of one d x d matrix */

@@ -257,6 +257,7 @@ __global__ void __launch_bounds__(256) diag_block_kernel(const DiagRec* __restri
       if (r < n && c < n) {
         rec.L[(int64_t)r * rec.ld_l + c] = (c <= r) ? a[i][q] : 0.f;
         rec.Linv[(int64_t)r * rec.ld_inv + c] = (c <= r) ? x[i][q] : 0.f;
+        if (rec.LinvT) rec.LinvT[(int64_t)c * rec.ld_invt + r] = (c <= r) ? x[i][q] : 0.f;
       }
     }
 }
@@ -397,6 +398,8 @@ struct Mat {  // one square matrix being factorised
   int d, nb;
   float* W;    // holds M, then L (lower)
   float* Li;   // receives L^-1 (lower)
+  float* X;    // receives L^-T (upper), or null: lets every product of the triangular inverse and of
+               // L^-T L^-1 read both operands along k
   float* T;    // where the finished inverse goes
   int mat_index;
 };
@@ -439,6 +442,7 @@ static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot)
           r.L = blk(m.W, m.d, j, j); r.Linv = blk(m.Li, m.d, j, j);
           r.ld_l = m.d; r.ld_inv = m.d; r.size = bsz(m, j); r.mat = m.mat_index; r.row0 = j * NB;
           r.info_slot = info_slot;
+          r.LinvT = m.X ? blk(m.X, m.d, j, j) : nullptr; r.ld_invt = m.d; r.pad = 0;
           b.p.diags.push_back(r);
         }
       b.end_phase(2, first, (int)b.p.diags.size() - first);
@@ -466,6 +470,12 @@ static void emit_lauum(Builder& b, const std::vector<Mat>& ms) {
           const int mi = std::min(tile, m.d - i * tile), nj = std::min(tile, m.d - j * tile);
           float* C = m.T + (int64_t)i * tile * m.d + (int64_t)j * tile;
           float* C2 = (i == j) ? nullptr : m.T + (int64_t)j * tile * m.d + (int64_t)i * tile;
+          if (m.X) {   // T(i,j) = sum_{k >= i*tile} X(i,k) X(j,k): both operands read along k
+            const float* A = m.X + (int64_t)i * tile * m.d + (int64_t)i * tile;
+            const float* B = m.X + (int64_t)j * tile * m.d + (int64_t)i * tile;
+            b.gemm(A, m.d, false, B, m.d, true, C, m.d, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.d, i == j);
+            continue;
+          }
           // rows k >= i*tile of Li contribute: A = Li[k, i-cols]^T, B = Li[k, j-cols]
           const float* A = m.Li + (int64_t)i * tile * m.d + (int64_t)i * tile;
           const float* B = m.Li + (int64_t)i * tile * m.d + (int64_t)j * tile;
@@ -574,7 +584,7 @@ static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* 
 // task-count estimate without building (used for the *_dev_bytes queries): build and measure.
 static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* const* dst,
                         float* const* work, float* const* std_out, const int32_t* partner,
-                        const int32_t* role) {
+                        const int32_t* role, float* const* xbuf) {
   Plan* p = new Plan();
   std::vector<Mat> ms(n);
   for (int i = 0; i < n; ++i) {
@@ -585,6 +595,7 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
     ms[i].d = (int)dims[i]; ms[i].nb = (ms[i].d + NB - 1) / NB;
     ms[i].W = dst ? dst[i] : nullptr;   // the output buffer first holds M + vI, then L
     ms[i].Li = work ? work[i] : nullptr;
+    ms[i].X = xbuf ? xbuf[i] : nullptr;
     ms[i].T = nullptr;
     ms[i].mat_index = i;
   }
@@ -600,6 +611,7 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
     for (int i = 0; i < n; ++i) {
       emit_copy(b, src ? src[i] : nullptr, ms[i].W, ms[i].d, i, 0);
       emit_copy(b, nullptr, ms[i].Li, ms[i].d, -1, 2);
+      if (ms[i].X) emit_copy(b, nullptr, ms[i].X, ms[i].d, -1, 2);
     }
     b.end_phase(3, first, (int)p->copies.size() - first);
     emit_cholesky(b, ms, 0);
@@ -617,9 +629,14 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
           const int mid = lo + s, hi = std::min(lo + 2 * s, m.nb);
           for (int i = mid; i < hi; i += w)
             for (int j = lo; j < mid; j += w)
-              // Y(i,j)^T = sum_{k in [j,mid)} Inv11(k,j)^T * L(i,k)^T  -> W block (j,i)
-              b.gemm(blk(m.Li, m.d, j, j), m.d, true, blk(m.W, m.d, i, j), m.d, true,
-                     blk(m.W, m.d, j, i), m.d, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
+              // Y(i,j)^T = sum_{k in [j,mid)} Inv11(k,j)^T * L(i,k)^T  -> W block (j,i);
+              // Inv11(k,j)^T = X(j,k) when the transposed inverse is kept
+              if (m.X)
+                b.gemm(blk(m.X, m.d, j, j), m.d, false, blk(m.W, m.d, i, j), m.d, true,
+                       blk(m.W, m.d, j, i), m.d, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
+              else
+                b.gemm(blk(m.Li, m.d, j, j), m.d, true, blk(m.W, m.d, i, j), m.d, true,
+                       blk(m.W, m.d, j, i), m.d, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
         }
       b.end_phase(w == 1 ? 0 : 1, first, b.task_begin() - first);
       first = b.task_begin();
@@ -631,7 +648,8 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
               const int kk = std::min((i + w - mid) * NB, m.d - mid * NB);
               // Inv21(i,j) = - sum_k Inv22(i,k) * Y(k,j),  Y(k,j) stored at W(j,k) transposed
               b.gemm(blk(m.Li, m.d, i, mid), m.d, false, blk(m.W, m.d, j, mid), m.d, true,
-                     blk(m.Li, m.d, i, j), m.d, std::min(T, m.d - i * NB), T, kk, -1.f, 0.f);
+                     blk(m.Li, m.d, i, j), m.d, std::min(T, m.d - i * NB), T, kk, -1.f, 0.f,
+                     m.X ? blk(m.X, m.d, j, i) : nullptr, m.d);
             }
         }
       b.end_phase(w == 1 ? 0 : 1, first, b.task_begin() - first);
@@ -650,6 +668,7 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
       cs[i] = ms[i];
       cs[i].W = work[i];
       cs[i].Li = std_out[i];
+      cs[i].X = nullptr;
       emit_copy(b, dst[i], work[i], ms[i].d, -1, 0);
     }
     b.end_phase(3, first, (int)p->copies.size() - first);
@@ -667,14 +686,21 @@ using namespace sso;
 
 extern "C" {
 
+static size_t kron_scratch_bytes(int n_mats, const int64_t* dims) {
+  size_t b = 0;
+  for (int i = 0; i < n_mats; ++i) b += align_up((size_t)dims[i] * (size_t)dims[i] * sizeof(float));
+  return b;
+}
+
 size_t sso_kron_plan_dev_bytes(int n_mats, const int64_t* dims, int with_std) {
   if (n_mats <= 0 || !dims) return 0;
   std::vector<float*> fake(n_mats, nullptr);
+  std::vector<float*> fake_x(n_mats, reinterpret_cast<float*>(4096));   // non-null: the scratch matrices exist
   Plan* p = build_kron(n_mats, dims, fake.data(), fake.data(), fake.data(),
-                       with_std ? fake.data() : nullptr, nullptr, nullptr);
+                       with_std ? fake.data() : nullptr, nullptr, nullptr, fake_x.data());
   const size_t bytes = plan_table_bytes(p->tasks.size(), p->diags.size(), p->copies.size(), p->mats.size());
   delete p;
-  return bytes;
+  return kron_scratch_bytes(n_mats, dims) + 256 + bytes;
 }
 
 int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src, float* const* dst,
@@ -686,10 +712,22 @@ int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src,
     SSO_CHECK_ARG(src[i] && dst[i] && work[i], "kron plan: null matrix pointer at %d", i);
     if (partner && partner[i] >= 0) SSO_CHECK_ARG(partner[i] < n_mats, "kron plan: bad partner");
   }
-  Plan* p = build_kron(n_mats, dims, src, dst, work, std_out, partner, role);
+  // the head of the plan's memory holds one scratch matrix per factor (the transposed triangular
+  // inverse); the tables follow.  A host-only plan needs (host) memory for the scratch part only.
+  const size_t scratch = kron_scratch_bytes(n_mats, dims) + 256;
+  SSO_CHECK_ARG(dev_mem != nullptr && dev_mem_bytes >= scratch, "kron plan: plan memory too small for the scratch matrices");
+  std::vector<float*> xb(n_mats);
+  {
+    char* q = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(dev_mem)));
+    for (int i = 0; i < n_mats; ++i) {
+      xb[i] = reinterpret_cast<float*>(q);
+      q += align_up((size_t)dims[i] * (size_t)dims[i] * sizeof(float));
+    }
+  }
+  Plan* p = build_kron(n_mats, dims, src, dst, work, std_out, partner, role, xb.data());
   p->host_only = host_only != 0;
   if (!p->host_only) {
-    const int rc = upload(*p, dev_mem, dev_mem_bytes);
+    const int rc = upload(*p, reinterpret_cast<char*>(dev_mem) + scratch, dev_mem_bytes - scratch);
     if (rc != 0) { delete p; return rc; }
   }
   return register_plan(p);

@@ -36,7 +36,8 @@ class TileTask(C.Structure):
 
 class DiagRec(C.Structure):
     _fields_ = [('L', c_vp), ('Linv', c_vp), ('ld_l', C.c_int32), ('ld_inv', C.c_int32),
-                ('size', C.c_int32), ('mat', C.c_int32), ('row0', C.c_int32), ('info_slot', C.c_int32)]
+                ('size', C.c_int32), ('mat', C.c_int32), ('row0', C.c_int32), ('info_slot', C.c_int32),
+                ('LinvT', c_vp), ('ld_invt', C.c_int32), ('pad', C.c_int32)]
 
 
 class CopyRec(C.Structure):
@@ -491,11 +492,23 @@ def kron_plan(dims, src, dst, work, std, partner, role, device, host_only=False)
     n = len(dims)
     d = _i64(dims)
     nbytes = L.sso_kron_plan_dev_bytes(n, d, int(std is not None))
-    mem = None if host_only else torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+    host_mem = None
+    if host_only:
+        # the plan's scratch matrices (the head of its memory block) must exist for a host-side
+        # interpreter of the program; the tables behind them are not uploaded
+        import numpy as np
+        host_mem = np.full(nbytes // 4 + 64, np.nan, dtype=np.float32)
+        mem = None
+        mem_ptr = host_mem.ctypes.data
+    else:
+        mem = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        mem_ptr = mem.data_ptr()
     h = L.sso_kron_plan_create(n, d, _ptrs(src), _ptrs(dst), _ptrs(work),
                                None if std is None else _ptrs(std), _i32(partner), _i32(role),
-                               _ptr(mem), nbytes, int(host_only))
-    return Plan(h, mem, (src, dst, work, std))
+                               mem_ptr, nbytes, int(host_only))
+    plan = Plan(h, mem, (src, dst, work, std, host_mem))
+    plan.host_mem = host_mem
+    return plan
 
 
 def kron_plan_run(plan: Plan, damp_r: torch.Tensor, info: Optional[torch.Tensor], do_inverse: bool,

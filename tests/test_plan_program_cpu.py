@@ -73,7 +73,10 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
                     info[(r.mat, r.info_slot)] = r.row0 + 1
                     L = np.eye(r.size)
                 Lv[...] = L.astype(np.float32)
-                mem.view(r.Linv, r.size, r.size, r.ld_inv)[...] = np.linalg.inv(L).astype(np.float32)
+                Linv = np.linalg.inv(L).astype(np.float32)
+                mem.view(r.Linv, r.size, r.size, r.ld_inv)[...] = Linv
+                if r.LinvT:
+                    mem.view(r.LinvT, r.size, r.size, r.ld_invt)[...] = Linv.T
         elif kind == 3:
             for r in [copies[i] for i in range(first, first + count)]:
                 dst = mem.view(r.dst, r.d, r.d, r.d)
@@ -115,6 +118,7 @@ def test_kron_inverse_and_std_program(dims):
     plan = nat.kron_plan(dims, [a.ctypes.data for a in src], [a.ctypes.data for a in dst],
                          [a.ctypes.data for a in work], [a.ctypes.data for a in std],
                          partner, role, device=None, host_only=True)
+    mem.bufs.append(plan.host_mem)
     r = np.sqrt(1e-3)
     shift = []
     for i, d in enumerate(dims):
@@ -149,6 +153,7 @@ def test_kron_program_reports_bad_pivot():
     src[:] = m.ravel()
     plan = nat.kron_plan([d], [src.ctypes.data], [dst.ctypes.data], [work.ctypes.data], None,
                          [-1], [0], device=None, host_only=True)
+    mem.bufs.append(plan.host_mem)
     info = run_program(plan, mem, shift=[0.0])
     assert info == {(0, 0): 65}          # first row of the failing block, 1-based
 
