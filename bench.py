@@ -367,6 +367,7 @@ def run_gpu_arm(args):
     nat.FACTOR_TIMING = None
     f_ms = sum(a.elapsed_time(b) for a, b, _, _ in ft)
     f_flops = sum(f for _, _, f, _ in ft)
+    f_bytes = sum(nb for _, _, _, nb in ft)
 
     if rank != 0:
         if world > 1:
@@ -396,7 +397,12 @@ def run_gpu_arm(args):
         'gpu_launches': int(launches),
         'roofline': {'bound': 'tensor', 'kernel': 'factor construction (all Kron layers, A and G)',
                      'achieved': achieved_tf, 'peak': tf_peak, 'unit': 'TFLOP/s',
-                     'frac': achieved_tf / tf_peak if tf_peak else None, 'traffic': None,
+                     'frac': achieved_tf / tf_peak if tf_peak else None,
+                     # DRAM bytes per launch: algorithmic bytes (input once + d*d*4 output) averaged over
+                     # the factor launches, times the measured/algorithmic ratio of the ncu capture of one
+                     # launch (profiles/factor_tma_pair_kernel_*: 55.4 MB measured for 56.7 MB algorithmic)
+                     'traffic': (f_bytes / len(ft)) * (55.4 / 56.7) if ft else None,
+                     'traffic_unit': 'bytes per launch (average over the launches of a step)',
                      'peak_source': peak_src + ' (bf16 dense, sustained)',
                      'launches': len(ft), 'total_ms': f_ms, 'measured_over_steps': probe_steps,
                      'flops_rule': '2*rows*d^2 per factor (what the reference einsum performs)'},
