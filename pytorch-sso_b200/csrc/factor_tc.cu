@@ -448,20 +448,39 @@ __global__ void __launch_bounds__(256) factor_tc_reduce(const FactorParams p, in
   }
 }
 
-// Tile-wise variant of the finishing kernel: one CTA sums 1024 elements of one partial tile with
+// Tile-wise variant of the finishing kernel: a CTA sums 1024/SL elements of one partial tile with
 // 16-byte loads and scatters them (and their mirror) to the output.  It wins when many splits
-// make the partial tiles, not the output, the bulk of the traffic.
-__global__ void __launch_bounds__(256) factor_tc_reduce_tiles(const FactorParams p) {
+// make the partial tiles, not the output, the bulk of the traffic.  With many splits and few
+// tiles, SL = 2, 4 or 8 neighbouring lanes share an element group: lane l sums splits l, l+SL, ...
+// and the lanes are combined by shuffles in a fixed tree, so the sum stays deterministic while
+// the chains get shorter and SL times more CTAs are in flight.
+__global__ void __launch_bounds__(256) factor_tc_reduce_tiles(const FactorParams p, int sl) {
   int bi, bj;
   tri_decode(blockIdx.x, bi, bj);
   const float* src = p.partial + (int64_t)blockIdx.x * p.splits * (TILE * TILE);
-  const int e0 = (blockIdx.y * 256 + threadIdx.x) * 4;
+  const int group = (blockIdx.y * 256 + threadIdx.x) / sl, sub = threadIdx.x % sl;
+  const int e0 = group * 4;
   const int r = e0 / TILE, c0 = e0 % TILE;
-  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int sp = 0; sp < p.splits; ++sp) {
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f), s2 = make_float4(0.f, 0.f, 0.f, 0.f);
+  int sp = sub;
+  for (; sp + sl < p.splits; sp += 2 * sl) {      // two independent chains per lane
+    const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)sp * (TILE * TILE) + e0);
+    const float4 w = *reinterpret_cast<const float4*>(src + (int64_t)(sp + sl) * (TILE * TILE) + e0);
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    s2.x += w.x; s2.y += w.y; s2.z += w.z; s2.w += w.w;
+  }
+  if (sp < p.splits) {
     const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)sp * (TILE * TILE) + e0);
     s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
   }
+  s.x += s2.x; s.y += s2.y; s.z += s2.z; s.w += s2.w;
+  for (int o = 1; o < sl; o <<= 1) {
+    s.x += __shfl_xor_sync(0xffffffffu, s.x, o);
+    s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+    s.z += __shfl_xor_sync(0xffffffffu, s.z, o);
+    s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+  }
+  if (sub != 0) return;
   const bool bad = p.status && *p.status != 0;
   auto ext = [&](int j) {
     if (p.perm_c > 0 && j < p.dcols) return (j % p.perm_c) * p.perm_kk + j / p.perm_c;
@@ -518,6 +537,10 @@ size_t factor_tc_workspace_bytes(int64_t rows, int64_t d) {
   int s2, r2;
   tc::choose_splits(rows, tiles, 64, s2, r2);
   if (s2 > splits) splits = s2;
+  // the TMA-fed kernel spreads one- and two-tile problems over all SMs (up to 148 splits); stay
+  // below 12 MB of partial tiles for them
+  const int64_t wide = std::min<int64_t>(std::min<int64_t>(148, 192 / tiles), std::max<int64_t>(1, rows / 512));
+  if (wide > splits) splits = (int)wide;
   return 256 + (size_t)tiles * splits * 128 * 128 * sizeof(float);
 }
 
@@ -573,7 +596,11 @@ int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspac
 int factor_tc_run_reduce(const FactorParams& p, int tiles, cudaStream_t st) {
   // few splits of a large permuted factor: the output dominates, write it in whole rows
   if (!(p.perm_c > 0 && p.splits <= 3 && p.d >= 1024)) {
-    tc::factor_tc_reduce_tiles<<<dim3(tiles, 128 * 128 / (256 * 4)), 256, 0, st>>>(p);
+    // lanes per element group: enough CTAs to fill the GPU when there are few tiles, and chains
+    // of at most ~8 partial tiles per lane
+    int sl = 1;
+    while (sl < 8 && (tiles * 16 * sl < 2 * 148 || p.splits > 8 * sl) && p.splits >= 4 * sl) sl <<= 1;
+    tc::factor_tc_reduce_tiles<<<dim3(tiles, 16 * sl), 256, 0, st>>>(p, sl);
     SSO_LAUNCH_OK("factor_tc_reduce_tiles");
     return 0;
   }

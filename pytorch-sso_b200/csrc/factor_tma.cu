@@ -491,18 +491,18 @@ static bool choose_box(const FactorParams& p, Geom& g) {
 // Splits of the stage range per tile.  More splits fill the 148 SMs more evenly but every split
 // writes a 64 KB partial tile that the finishing kernel reads back.  Cost model (microseconds,
 // constants fitted to measurements on B200): a CTA runs its stages at ~0.75 us each plus ~4 us
-// of prologue / drain, CTAs run in waves of 148, and a partial tile costs ~0.045 us of the
-// whole GPU's memory system (written once, read once at ~3 TB/s).
+// of prologue / drain, CTAs run in waves of 148, and a partial tile costs ~0.03 us of the
+// whole GPU's memory system (written once, read once).
 static void choose_splits(int total_stages, int tiles, int& splits, int& stages_per_split) {
   const int kSMs = 148;
   const int most = std::max(1, total_stages / 4);
   int best = 1;
   double best_cost = 1e30;
-  for (int s = 1; s <= 64 && s <= most; ++s) {
+  for (int s = 1; s <= 148 && s <= most; ++s) {
     const int sps = ceil_div(total_stages, s);
     const int real = ceil_div(total_stages, sps);
     const int64_t ctas = (int64_t)tiles * real;
-    const double cost = (double)ceil_div64(ctas, kSMs) * (sps * 0.75 + 4.0) + (double)ctas * 0.045;
+    const double cost = (double)ceil_div64(ctas, kSMs) * (sps * 0.75 + 4.0) + (double)ctas * 0.03;
     if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
   }
   stages_per_split = ceil_div(total_stages, best);
