@@ -183,18 +183,19 @@ __global__ void __launch_bounds__(256) bn_plane_sums_vec(const T* __restrict__ t
   }
 }
 
-// block = 32 channels x 8 image lanes; each thread sums the split partials of its images with
-// independent accumulators, the 8 lanes are combined in shared memory (fixed order: deterministic)
+// block = 8 channels x 32 image lanes: with the usual 32..256 images a thread owns one to eight
+// images, issues the loads of all their split partials back to back, and the 32 lanes are combined
+// in shared memory (fixed order: deterministic).  Many small blocks keep this latency-bound step short.
 __global__ void __launch_bounds__(256) bn_finish_kernel(const float* __restrict__ sx, const float* __restrict__ sg,
                                                         const float* __restrict__ weight, int n, int c,
                                                         int splits_x, int splits_g, float alpha, float beta,
                                                         float* __restrict__ w_out, float* __restrict__ b_out) {
-  __shared__ float rw[8][33], rb[8][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int ic = blockIdx.x * 32 + tx;
+  __shared__ float rw[32][9], rb[32][9];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int ic = blockIdx.x * 8 + tx;
   float aw = 0.f, ab = 0.f;
   if (ic < c) {
-    for (int in = ty; in < n; in += 8) {
+    for (int in = ty; in < n; in += 32) {
       const float* px = sx + (int64_t)in * splits_x * c + ic;
       const float* pg = sg + (int64_t)in * splits_g * c + ic;
       float x0 = 0.f, x1 = 0.f, g0 = 0.f, g1 = 0.f;
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(256) bn_finish_kernel(const float* __restrict_
   if (ty == 0 && ic < c) {
     float tw = 0.f, tb = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { tw += rw[i][tx]; tb += rb[i][tx]; }
+    for (int i = 0; i < 32; ++i) { tw += rw[i][tx]; tb += rb[i][tx]; }
     const float s = alpha / (float)n;
     w_out[ic] = (beta == 0.f) ? s * tw : fmaf(beta, w_out[ic], s * tw);
     if (b_out) b_out[ic] = (beta == 0.f) ? s * tb : fmaf(beta, b_out[ic], s * tb);
@@ -389,7 +390,7 @@ int sso_bn_diag_finish(const float* sx, const float* sg, const float* sample_wei
                        int splits_x, int splits_g, float alpha, float beta, float* w_out, float* b_out,
                        void* stream) {
   SSO_CHECK_ARG(sx && sg && w_out && n > 0 && c > 0 && splits_x >= 1 && splits_g >= 1, "bn_diag_finish: bad argument");
-  bn_finish_kernel<<<(unsigned)ceil_div64(c, 32), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  bn_finish_kernel<<<(unsigned)ceil_div64(c, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       sx, sg, sample_weight, (int)n, (int)c, splits_x, splits_g, alpha, beta, w_out, b_out);
   SSO_LAUNCH_OK("bn_finish_kernel");
   return 0;
