@@ -16,7 +16,13 @@ def sample_targets(prob: torch.Tensor, num_mc: int) -> torch.Tensor:
     """[num_mc, n] class indices drawn from the model's predictive distribution.
     A module-level function so that a parity harness can substitute a deterministic draw."""
     # same draw as torch.distributions.Categorical(prob).sample((num_mc,)) without the argument
-    # validation, which synchronises with the host (and so cannot be captured in a CUDA graph)
+    # validation, which synchronises with the host (and so cannot be captured in a CUDA graph).
+    # A diverged model produces NaN / all-zero rows, on which the sampling kernel would fail a
+    # device-side assertion and take the CUDA context with it: such rows are sampled uniformly
+    # instead (the loss is already NaN and says so).
+    prob = torch.nan_to_num(prob, nan=0.0, posinf=0.0, neginf=0.0).clamp_min(0.0)
+    dead = prob.sum(dim=1, keepdim=True) <= 0
+    prob = torch.where(dead, torch.ones_like(prob), prob)
     return torch.multinomial(prob, num_mc, replacement=True).t()
 
 

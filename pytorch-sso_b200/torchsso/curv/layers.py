@@ -70,6 +70,18 @@ def _weights(curv, n, device):
 # ---------------------------------------------------------------------------------------------
 # Kronecker-factored
 # ---------------------------------------------------------------------------------------------
+def _channels_last_if_worthwhile(t, d):
+    """NCHW activations (channel stride != 1) can only use the exact-fp32 SIMT factor kernel; the
+    tensor-core kernels gather whole 16-byte runs of channels.  For anything but tiny problems one
+    extra pass over the activation (a layout copy to channels_last) is far cheaper than that."""
+    if t.dim() != 4 or t.stride(1) == 1 or t.shape[1] == 1:
+        return t
+    rows = t.shape[0] * t.shape[2] * t.shape[3]
+    if 2.0 * rows * d * d < 5e8:
+        return t
+    return t.contiguous(memory_format=torch.channels_last)
+
+
 class _KronFactors(KronCurvature):
     """Shared driver: A in the forward hook, G (optionally prob-weighted and accumulated over
     sampling passes) in the backward hook, both by the fused factor kernel."""
@@ -152,6 +164,7 @@ class KronCovConv2d(_KronFactors):
             raise NotImplementedError('grouped / string-padded convolutions have no Kronecker curvature here')
         n, c = x.shape[0], x.shape[1]
         vec = 4 if x.dtype == torch.float32 else 8
+        x = _channels_last_if_worthwhile(x, c * m.kernel_size[0] * m.kernel_size[1])
         if x.stride(1) == 1 and c % vec != 0 and c < 64:
             # Channels-last input whose channel count is not a whole number of 16-byte chunks (the
             # 3-channel stem): zero-pad the channels so the tensor-core kernel applies, then keep
@@ -182,6 +195,8 @@ class KronCovConv2d(_KronFactors):
 
     def _factor_G(self, g, weight, scale, beta, out):
         n, c, h, w = g.shape
+        if c % (4 if g.dtype == torch.float32 else 8) == 0:
+            g = _channels_last_if_worthwhile(g, c)
         self._op(g, self._PLAIN, False, out).run(g, weight, scale / (n * h * w), beta)
 
 

@@ -275,3 +275,15 @@ def test_graphed_closure_equals_eager(torchsso_mod, side_stream):
     assert max(abs(a - b) for a, b in zip(l0, l1)) < 1e-5
     for a, b in zip(p0, p1):
         assert rel(b, a.cpu().numpy()) < 1e-5
+
+
+def test_fisher_sampling_survives_nan_probabilities(torchsso_mod):
+    """NaN / zero rows in the predictive distribution (a diverged model) must not reach the
+    sampling kernel's device-side assertion."""
+    from torchsso.curv import fisher
+    prob = torch.tensor([[float('nan'), 0.5, 0.5], [0.0, 0.0, 0.0], [0.2, 0.3, 0.5]], device='cuda')
+    t = fisher.sample_targets(prob, 4)
+    torch.cuda.synchronize()
+    assert t.shape == (4, 3)
+    assert int(t.min()) >= 0 and int(t.max()) <= 2
+    assert int(t[:, 0].min()) >= 1          # the NaN class is never drawn
