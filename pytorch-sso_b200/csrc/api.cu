@@ -21,6 +21,7 @@ void factor_tc_set_flush(int stages);
 int factor_tc_flush_setting();
 bool factor_tma_supported(const FactorParams& p, int dtype);
 void factor_tma_set_pair_min_d(int d);
+void factor_tma_set_f32(int on);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
 extern int g_engine_tc;
 static int g_tc_auto = 1;    // whether SSO_IMPL_AUTO may pick the tcgen05 kernels
@@ -43,6 +44,7 @@ int sso_configure(const char* key, int value) {
   if (k == "tc_auto") { g_tc_auto = value != 0; return 0; }
   if (k == "tma_auto") { g_tma_auto = value != 0; return 0; }
   if (k == "engine_tc") { g_engine_tc = value != 0; return 0; }
+  if (k == "tma_f32") { factor_tma_set_f32(value); return 0; }
   if (k == "tma_pair_min_d") { factor_tma_set_pair_min_d(value); return 0; }
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }
   if (k == "kc_variant") { g_kc_variant = value; return 0; }

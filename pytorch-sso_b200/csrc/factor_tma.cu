@@ -526,7 +526,330 @@ bool tma_encode_f32_rows(void* out, const float* base, int64_t rows, int64_t col
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// ---- fp32 inputs: TMA-fed 3xTF32 ---------------------------------------------------------------
+// Same idea for fp32 channels-contiguous activations whose channel count is a multiple of 32: a
+// box {32 channels, bw, bh, bn} of the NHWC tensor is 128-byte rows in shared memory, i.e. the
+// MN-major operand of a kind::tf32 MMA in its 32-byte-chunk swizzle (32 columns per block, four blocks per 128-wide
+// operand).  A stage is at most 32 pixels: 2 x 4 blocks x 4 KB = 32 KB land in a ring of five raw
+// stages; eight warps then split the landed stage in place (hi = rna_tf32(x) overwrites x, lo = x - hi
+// goes to a two-stage ring) and the MMA warp issues lo*hi + hi*lo + hi*hi per 8-pixel slice.  The
+// accumulator is drained into fp32 registers every two stages.  Partial tiles and the finishing
+// kernels are those of the other factor kernels.
+namespace tmaf {
+
+using namespace tc;
+
+constexpr int TILE = 128;
+constexpr int EPI_WARPS = 8, MMA_WARP = 8, SPLIT_WARPS = 8;
+constexpr int THREADS = 32 * (EPI_WARPS + 1 + SPLIT_WARPS);
+constexpr int RAW_SLOTS = 5, LO_SLOTS = 2, PREFETCH = 3, FLUSH = 2;
+constexpr int KPAD_MAX = 32;
+constexpr uint32_t BLOCK_BYTES_MAX = KPAD_MAX * 128;          // one 32-column block of one stage
+constexpr uint32_t OPERAND_BYTES = 4 * BLOCK_BYTES_MAX;       // 128 columns
+constexpr uint32_t STAGE_BYTES = 2 * OPERAND_BYTES;           // A and B
+constexpr uint32_t TMEM_COLS = 256;
+
+struct GeomF {
+  int bw, bh, bn;            // box in output pixels
+  int xchunks, ychunks;      // boxes per output row / per image column
+  int kstage, kpad;          // pixels per stage, padded to a multiple of 8
+  int total_stages, stages_per_split;
+};
+
+// MN-major 32-bit operands have one shared-memory layout: 128-byte rows swizzled in 32-byte chunks
+// (chunk index XOR (row & 3)), atoms of 4 rows.  LBO = stride between 32-column blocks, SBO = stride
+// between groups of 4 rows (512 bytes here), descriptor version 1, layout type 1.
+__device__ __forceinline__ uint64_t desc_mn_sw128(uint32_t saddr, uint32_t lbo_bytes) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(512u >> 4) << 32) | (1ull << 46) | (1ull << 61);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+factor_tma_f32_kernel(const FactorParams p, const GeomF g, const __grid_constant__ CUtensorMap tmap) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * RAW_SLOTS + 2 * LO_SLOTS + 4];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int bi, bj;
+  tri_decode(blockIdx.x, bi, bj);
+  const bool share = (bi == bj);
+  const int split = blockIdx.y;
+  const int s_begin = split * g.stages_per_split;
+  const int s_end = min(g.total_stages, s_begin + g.stages_per_split);
+  const int nstages = max(0, s_end - s_begin);
+  const int nchunks = ceil_div(nstages, FLUSH);
+  int* status = p.status;
+
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t lo0 = smem0 + RAW_SLOTS * STAGE_BYTES;
+  const uint32_t bar0 = smem_u32(bars);
+  auto rawfree_bar = [&](int s) { return bar0 + 8u * s; };
+  auto rawfull_bar = [&](int s) { return bar0 + 8u * (RAW_SLOTS + s); };
+  auto full_bar = [&](int s) { return bar0 + 8u * (2 * RAW_SLOTS + s); };
+  auto lofree_bar = [&](int s) { return bar0 + 8u * (2 * RAW_SLOTS + LO_SLOTS + s); };
+  const uint32_t accfull0 = bar0 + 8u * (2 * RAW_SLOTS + 2 * LO_SLOTS), accempty0 = accfull0 + 16u;
+
+  if (tid == 0) {
+    for (int s = 0; s < RAW_SLOTS; ++s) {
+      mbar_init(rawfree_bar(s), 1);
+      mbar_init(rawfull_bar(s), 1);
+    }
+    for (int s = 0; s < LO_SLOTS; ++s) {
+      mbar_init(full_bar(s), SPLIT_WARPS);
+      mbar_init(lofree_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accfull0 + 8u * b, 1);
+      mbar_init(accempty0 + 8u * b, EPI_WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // zero both rings once: padding pixels and blocks past the matrix edge are never written by TMA
+  for (uint32_t o = tid * 16u; o < (RAW_SLOTS + LO_SLOTS) * STAGE_BYTES; o += THREADS * 16u)
+    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(smem0 + o), "r"(0u) : "memory");
+  fence_async_smem();
+  if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
+
+  if (warp < EPI_WARPS) {
+    // ------------------------------------------------------------------ accumulate warps
+    const int q = warp & 3, half = warp >> 2;
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+      const int b = c & 1;
+      if (!mbar_wait(accfull0 + 8u * b, (c >> 1) & 1, status, 53)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * TILE + half * 64);
+      uint32_t v0[32], v1[32];
+      tmem_ld32(taddr, v0);
+      tmem_ld32(taddr + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accempty0 + 8u * b);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        acc[i] += __uint_as_float(v0[i]);
+        acc[32 + i] += __uint_as_float(v1[i]);
+      }
+    }
+    float* dst = p.partial + ((int64_t)blockIdx.x * p.splits + split) * (TILE * TILE) +
+                 (q * 32 + lane) * TILE + half * 64;
+#pragma unroll
+    for (int i = 0; i < 64; i += 4)
+      *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(2u, 1u);     // tf32, MN-major operands
+      const int nk = g.kpad / 8;
+      bool ok = true;
+      for (int s = 0; s < nstages && ok; ++s) {
+        const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS, c = s / FLUSH, b = c & 1;
+        const bool first_of_chunk = (s % FLUSH) == 0;
+        if (first_of_chunk && c >= 2) ok = mbar_wait(accempty0 + 8u * b, ((c >> 1) - 1) & 1, status, 52);
+        if (!ok) break;
+        ok = mbar_wait(full_bar(ls), (s / LO_SLOTS) & 1, status, 51);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ah = smem0 + rs * STAGE_BYTES, al = lo0 + ls * STAGE_BYTES;
+        const uint32_t bh = share ? ah : ah + OPERAND_BYTES, bl = share ? al : al + OPERAND_BYTES;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * TILE);
+        for (int ks = 0; ks < nk; ++ks) {
+          // one slice = 8 pixels = one 1024-byte swizzle atom; the next 32-column block of the
+          // operand starts blk_bytes further on
+          const uint64_t adh = desc_mn_sw128(ah + ks * 1024u, blk_bytes), adl = desc_mn_sw128(al + ks * 1024u, blk_bytes);
+          const uint64_t bdh = desc_mn_sw128(bh + ks * 1024u, blk_bytes), bdl = desc_mn_sw128(bl + ks * 1024u, blk_bytes);
+          umma<true>(d_tmem, adl, bdh, idesc, (first_of_chunk && ks == 0) ? 0u : 1u);
+          umma<true>(d_tmem, adh, bdl, idesc, 1u);
+          umma<true>(d_tmem, adh, bdh, idesc, 1u);
+        }
+        umma_commit(rawfree_bar(rs));
+        umma_commit(lofree_bar(ls));
+        if ((s % FLUSH) == FLUSH - 1 || s == nstages - 1) umma_commit(accfull0 + 8u * b);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ producer thread + split warps
+    const int lt = tid - 32 * (MMA_WARP + 1);
+    int bc0[8], bx[8], by[8];
+    bool bvalid[8];
+    int nvalid = 0;
+    if (lt == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int op = e >> 2;
+        const int j0 = (op == 0 ? bi : bj) * TILE + (e & 3) * 32;
+        bvalid[e] = (j0 < p.dcols) && !(share && op == 1);
+        const int pos = j0 / p.c;
+        const int ky = pos / p.kw, kx = pos - ky * p.kw;
+        bc0[e] = j0 - pos * p.c;
+        bx[e] = kx * p.dil_w - p.pad_w;
+        by[e] = ky * p.dil_h - p.pad_h;
+        nvalid += bvalid[e] ? 1 : 0;
+      }
+    }
+    const uint32_t box_bytes = (uint32_t)g.kstage * 128u;
+    const uint64_t tmap_ptr = reinterpret_cast<uint64_t>(&tmap);
+    bool ok = true;
+    auto issue = [&](int s) {
+      const int rs = s % RAW_SLOTS;
+      if (s >= RAW_SLOTS && !mbar_wait(rawfree_bar(rs), ((s / RAW_SLOTS) - 1) & 1, status, 54)) { ok = false; return; }
+      const int sg = s_begin + s;
+      const int per_img = g.xchunks * g.ychunks;
+      const int n0 = (sg / per_img) * g.bn;
+      const int rem = sg % per_img;
+      const int oy0 = (rem / g.xchunks) * g.bh, ox0 = (rem % g.xchunks) * g.bw;
+      const uint32_t fb = rawfull_bar(rs);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"(box_bytes * nvalid) : "memory");
+      const uint32_t sb = smem0 + rs * STAGE_BYTES;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (!bvalid[e]) continue;
+        const uint32_t dst = sb + (e >> 2) * OPERAND_BYTES + (e & 3) * blk_bytes;
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+            ::"r"(dst), "l"(tmap_ptr), "r"(bc0[e]), "r"(ox0 * p.stride_w + bx[e]), "r"(oy0 * p.stride_h + by[e]), "r"(n0), "r"(fb)
+            : "memory");
+      }
+    };
+    if (lt == 0)
+      for (int s = 0; s < PREFETCH && s < nstages; ++s) issue(s);
+    // the operand bytes of a stage that exist: A always, B unless the tile is on the diagonal
+    const uint32_t split_bytes = share ? OPERAND_BYTES : STAGE_BYTES;
+    for (int s = 0; s < nstages; ++s) {
+      if (lt == 0 && s + PREFETCH < nstages) issue(s + PREFETCH);
+      const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS;
+      if (!mbar_wait(rawfull_bar(rs), (s / RAW_SLOTS) & 1, status, 56)) break;
+      if (s >= LO_SLOTS && !mbar_wait(lofree_bar(ls), ((s / LO_SLOTS) - 1) & 1, status, 55)) break;
+      const uint32_t hi = smem0 + rs * STAGE_BYTES, lo = lo0 + ls * STAGE_BYTES;
+      for (uint32_t off = (uint32_t)lt * 16u; off < split_bytes; off += 32u * SPLIT_WARPS * 16u) {
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(hi + off) : "memory");
+        const uint32_t h0 = rna_tf32(v.x), h1 = rna_tf32(v.y), h2 = rna_tf32(v.z), h3 = rna_tf32(v.w);
+        const uint32_t l0 = __float_as_uint(v.x - __uint_as_float(h0)), l1 = __float_as_uint(v.y - __uint_as_float(h1));
+        const uint32_t l2 = __float_as_uint(v.z - __uint_as_float(h2)), l3 = __float_as_uint(v.w - __uint_as_float(h3));
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(hi + off), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(lo + off), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_bar(ls));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+static int round8(int v) { return (v + 7) / 8 * 8; }
+
+// Output-pixel rectangle of one stage (at most 32 pixels): bw divides the output width, bh the
+// height; whole images are grouped when an image has at most 32 pixels.  Chosen to minimise the
+// padded pixel count, ties to the larger box.
+static bool choose_box(const FactorParams& p, GeomF& g) {
+  const int wo = p.wo, ho = p.ho, hw = wo * ho;
+  double best_cost = 1e30;
+  bool found = false;
+  auto consider = [&](int bw, int bh, int bn) {
+    if (bw * p.stride_w > 256 || bh * p.stride_h > 256 || bn > 256) return;
+    const int ks = bw * bh * bn;
+    if (ks > KPAD_MAX) return;
+    const double stages = (double)(wo / bw) * (ho / bh) * ceil_div(p.n, bn);
+    const double cost = stages * round8(ks) + stages * 4.0;     // padded pixels + a per-stage overhead
+    if (cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && ks > g.kstage)) {
+      best_cost = cost; found = true;
+      g.bw = bw; g.bh = bh; g.bn = bn; g.kstage = ks;
+    }
+  };
+  g.kstage = 0;
+  if (hw <= KPAD_MAX)
+    for (int bn = 1; bn * hw <= KPAD_MAX; ++bn) consider(wo, ho, bn);
+  for (int bw = 1; bw <= wo && bw <= KPAD_MAX; ++bw) {
+    if (wo % bw != 0) continue;
+    for (int bh = 1; bh <= ho && bw * bh <= KPAD_MAX; ++bh)
+      if (ho % bh == 0) consider(bw, bh, 1);
+  }
+  if (!found) return false;
+  g.xchunks = wo / g.bw;
+  g.ychunks = ho / g.bh;
+  g.kpad = round8(g.kstage);
+  g.total_stages = ceil_div(p.n, g.bn) * g.xchunks * g.ychunks;
+  return true;
+}
+
+}  // namespace tmaf
+
+static int g_tma_f32 = 0;     // fp32 inputs may use the TMA-fed 3xTF32 kernel
+void factor_tma_set_f32(int on) { g_tma_f32 = on != 0; }
+
+static bool factor_tma_f32_supported(const FactorParams& p) {
+  if (!g_tma_f32) return false;
+  if (p.sc != 1 || p.c % 32 != 0 || p.weight != nullptr || p.d != p.dcols) return false;
+  if ((reinterpret_cast<uintptr_t>(p.x) & 15) != 0) return false;
+  if (p.stride_h > 8 || p.stride_w > 8) return false;
+  if ((p.sn * 4) % 16 != 0 || (p.h > 1 && (p.sh * 4) % 16 != 0) || (p.w > 1 && (p.sw * 4) % 16 != 0)) return false;
+  tmaf::GeomF g;
+  if (!tmaf::choose_box(p, g)) return false;
+  return tma::encode_fn() != nullptr;
+}
+
+static int factor_tma_f32_launch(FactorParams p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  using namespace tmaf;
+  GeomF g{};
+  SSO_CHECK_ARG(choose_box(p, g), "factor (tma, fp32): unsupported geometry");
+  const int nb = ceil_div(p.d, 128);
+  const int tiles = nb * (nb + 1) / 2;
+  tma::choose_splits(g.total_stages, tiles, p.splits, g.stages_per_split);
+  SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= 256 + (size_t)tiles * 65536,
+                "factor workspace too small for the tensor-core path");
+  const int max_splits = (int)((workspace_bytes - 256) / ((size_t)tiles * 65536));
+  if (p.splits > max_splits) {
+    g.stages_per_split = ceil_div(g.total_stages, max_splits);
+    p.splits = ceil_div(g.total_stages, g.stages_per_split);
+  }
+  p.rows_per_split = 0;
+  p.status = reinterpret_cast<int*>(workspace);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+  SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), st));
+  p.perm_c = (p.kh * p.kw > 1) ? p.c : 0;
+  p.perm_kk = p.kh * p.kw;
+
+  CUtensorMap tmap;
+  const cuuint64_t gdim[4] = {(cuuint64_t)p.c, (cuuint64_t)p.w, (cuuint64_t)p.h, (cuuint64_t)p.n};
+  const cuuint64_t sw_b = (cuuint64_t)(p.w > 1 ? p.sw : p.c) * 4, sh_b = (cuuint64_t)(p.h > 1 ? p.sh : p.sn) * 4;
+  const cuuint64_t gstr[3] = {sw_b, sh_b, (cuuint64_t)p.sn * 4};
+  const cuuint32_t box[4] = {32u, (cuuint32_t)(g.bw * p.stride_w), (cuuint32_t)(g.bh * p.stride_h), (cuuint32_t)g.bn};
+  const cuuint32_t estr[4] = {1u, (cuuint32_t)p.stride_w, (cuuint32_t)p.stride_h, 1u};
+  const CUresult cr = tma::encode_fn()(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(p.x), gdim, gstr, box,
+                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+
+  const size_t smem = (size_t)(RAW_SLOTS + LO_SLOTS) * STAGE_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  factor_tma_f32_kernel<<<dim3(tiles, p.splits), THREADS, smem, st>>>(p, g, tmap);
+  SSO_LAUNCH_OK("factor_tma_f32_kernel");
+  return factor_tc_run_reduce(p, tiles, st);
+}
+
 bool factor_tma_supported(const FactorParams& p, int dtype) {
+  if (dtype == SSO_F32) return factor_tma_f32_supported(p);
   if (dtype != SSO_BF16 && dtype != SSO_F16) return false;
   if (p.sc != 1 || p.c % 64 != 0 || p.weight != nullptr || p.d != p.dcols) return false;
   if ((reinterpret_cast<uintptr_t>(p.x) & 15) != 0) return false;
@@ -542,6 +865,7 @@ void factor_tma_set_pair_min_d(int d) { g_pair_min_d = d < 0 ? 0 : d; }
 
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush,
                       cudaStream_t st) {
+  if (dtype == SSO_F32) return factor_tma_f32_launch(p, workspace, workspace_bytes, st);
   using namespace tma;
   Geom g{};
   SSO_CHECK_ARG(choose_box(p, g), "factor (tma): unsupported geometry");

@@ -237,6 +237,35 @@ def test_factor_tma_pair_accumulates_with_beta(nat):
     assert rel(out, 0.5 * ref + 0.25 * base.double()) < FACTOR_TOL
 
 
+@pytest.mark.parametrize('cfg', [
+    (2, 32, 6, 6, (1, 1), (1, 1), (0, 0), (1, 1)),
+    (2, 64, 6, 6, (3, 3), (1, 1), (1, 1), (1, 1)),
+    (3, 128, 9, 7, (3, 3), (1, 1), (1, 1), (1, 1)),
+    (4, 64, 14, 14, (3, 3), (2, 2), (1, 1), (1, 1)),
+    (2, 96, 20, 20, (3, 3), (1, 1), (1, 1), (1, 1)),
+    (2, 64, 12, 12, (5, 3), (1, 1), (2, 1), (1, 2)),
+    (6, 64, 30, 30, (3, 3), (1, 1), (1, 1), (1, 1)),
+])
+def test_factor_tma_fp32_matches_oracle(nat, cfg):
+    """Opt-in TMA-fed 3xTF32 kernel for fp32 channels-contiguous inputs (MN-major tf32 operands in
+    the 32-byte-chunk swizzle, split into hi / lo in shared memory)."""
+    n, c, h, w, k, s, p, d = cfg
+    x = cases.make_normal((n, c, h, w), 391 + c + h)
+    ref = ko.conv_factor_A(x.double(), k, s, p, d, False)
+    xd = dev(x).contiguous(memory_format=torch.channels_last)
+    nat.configure('tma_f32', 1)
+    try:
+        out = torch.full(tuple(ref.shape), float('nan'), device='cuda')
+        nat.factor_im2col(xd, k, s, p, d, False, None, 1.0 / n, 0.0, out, nat.IMPL_TMA)
+        again = torch.full_like(out, float('nan'))
+        nat.factor_im2col(xd, k, s, p, d, False, None, 1.0 / n, 0.0, again, nat.IMPL_TMA)
+    finally:
+        nat.configure('tma_f32', 0)
+    assert rel(out, ref) < FACTOR_TOL
+    assert torch.equal(out, out.t())
+    assert torch.equal(out, again)
+
+
 @pytest.mark.parametrize('engine_tma', [0, 1])
 def test_precondition_kernel_variants_agree(nat, engine_tma):
     """k-contiguous tile tasks fed by TMA (tensor maps per task) or by cp.async give the oracle's
