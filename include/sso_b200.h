@@ -167,6 +167,28 @@ typedef struct {
 } sso_seg_rec;
 int sso_copy_segments(const sso_seg_rec* recs_dev, int n_recs, float scale, void* stream);
 
+/* Optimizer tail over a table of parameter chunks: weight decay / l2, momentum, gradient moving
+ * average, bias-correction scale and the parameter update in one launch
+ * (replaces the per-group multi-tensor chains of torchsso/optim/secondorder.py:225-283,
+ * update_preprocess + update):
+ *     g += add * p
+ *     if (mbuf) { mbuf = momentum * mbuf + g;  g = mbuf; }
+ *     if (ebuf) { ebuf = (1 - ema) * ebuf + ema * g;  g = ebuf; }
+ *     g *= scale
+ *     if (lr != 0) p -= lr * g
+ * The "raw" stage (before preconditioning) passes add = l2_reg and lr = 0, the "preconditioned"
+ * stage add = weight_decay and the group's lr. */
+typedef struct {
+  float* p;
+  float* g;
+  float* mbuf;       /* nullable */
+  float* ebuf;       /* nullable */
+  int64_t count;
+  float add, momentum, ema, scale, lr;
+  int32_t pad;
+} sso_tail_rec;
+int sso_optimizer_tail(const sso_tail_rec* recs_dev, int n_recs, void* stream);
+
 /* ---------------------------------------------------------------------------------------
  * Tile-task engine.  All dense algebra after factor construction (pi-damped SPD inverse,
  * Cholesky factor of the inverse, G^-1 dW A^-1, posterior sampling) is expressed as phases

@@ -340,11 +340,39 @@ __global__ void __launch_bounds__(256) copy_segments_kernel(const sso_seg_rec* _
   }
 }
 
+__global__ void __launch_bounds__(256) optimizer_tail_kernel(const sso_tail_rec* __restrict__ recs) {
+  const sso_tail_rec r = recs[blockIdx.x];
+  for (int64_t i = threadIdx.x; i < r.count; i += 256) {
+    const float pv = r.p[i];
+    float g = r.g[i];
+    g = fmaf(r.add, pv, g);
+    if (r.mbuf) {
+      g = fmaf(r.momentum, r.mbuf[i], g);
+      r.mbuf[i] = g;
+    }
+    if (r.ebuf) {
+      g = fmaf(r.ema, g, (1.f - r.ema) * r.ebuf[i]);
+      r.ebuf[i] = g;
+    }
+    g *= r.scale;
+    r.g[i] = g;
+    if (r.lr != 0.f) r.p[i] = fmaf(-r.lr, g, pv);
+  }
+}
+
 }  // namespace sso
 
 using namespace sso;
 
 extern "C" {
+
+int sso_optimizer_tail(const sso_tail_rec* recs_dev, int n_recs, void* stream) {
+  SSO_CHECK_ARG(recs_dev != nullptr && n_recs >= 0, "optimizer_tail: bad argument");
+  if (n_recs == 0) return 0;
+  optimizer_tail_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev);
+  SSO_LAUNCH_OK("optimizer_tail_kernel");
+  return 0;
+}
 
 int sso_axpby(const float* src, float* dst, int64_t count, float a, float b, void* stream) {
   SSO_CHECK_ARG(src && dst && count >= 0, "axpby: bad argument");

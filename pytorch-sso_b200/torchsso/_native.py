@@ -94,6 +94,7 @@ SIGNATURES = {
     'sso_plan_num_copy_recs': (c_i32, [c_i64]),
     'sso_plan_copy_copy_recs': (c_i32, [c_i64, c_vp, c_i32]),
     'sso_run_tile_tasks': (c_i32, [c_vp, c_i32, c_i32, c_vp]),
+    'sso_optimizer_tail': (c_i32, [c_vp, c_i32, c_vp]),
 }
 
 
@@ -419,6 +420,30 @@ def seg_records(pairs, device, chunk: int = 1 << 16) -> torch.Tensor:
             recs.append((src.data_ptr() + 4 * o, dst.data_ptr() + 4 * o, min(chunk, n - o)))
     arr = np.array(recs, dtype=SEG_REC_DTYPE)
     return torch.from_numpy(arr.view(np.uint8).copy()).to(device)
+
+
+TAIL_REC_DTYPE = np.dtype([('p', np.uint64), ('g', np.uint64), ('mbuf', np.uint64), ('ebuf', np.uint64),
+                           ('count', np.int64), ('add', np.float32), ('momentum', np.float32),
+                           ('ema', np.float32), ('scale', np.float32), ('lr', np.float32), ('pad', np.int32)])
+
+
+def tail_records(items, device, chunk: int = 1 << 15) -> torch.Tensor:
+    """Device table for sso_optimizer_tail from (p, g, mbuf, ebuf, add, momentum, ema, scale, lr)
+    tuples of flat, equally laid out fp32 tensors (mbuf / ebuf may be None)."""
+    recs = []
+    for p, g, mbuf, ebuf, add, momentum, ema, scale, lr in items:
+        n = p.numel()
+        for o in range(0, n, chunk):
+            recs.append((p.data_ptr() + 4 * o, g.data_ptr() + 4 * o,
+                         0 if mbuf is None else mbuf.data_ptr() + 4 * o,
+                         0 if ebuf is None else ebuf.data_ptr() + 4 * o,
+                         min(chunk, n - o), add, momentum, ema, scale, lr, 0))
+    arr = np.array(recs, dtype=TAIL_REC_DTYPE)
+    return torch.from_numpy(arr.view(np.uint8).copy()).to(device)
+
+
+def optimizer_tail(table: torch.Tensor):
+    _check(lib().sso_optimizer_tail(table.data_ptr(), table.numel() // TAIL_REC_DTYPE.itemsize, _stream()))
 
 
 def copy_segments(table: torch.Tensor, scale: float = 1.0):

@@ -258,15 +258,67 @@ class SecondOrderOptimizer(Optimizer):
                 t.grad = self._grad_view[p]
 
     def _update_groups(self, groups, target, update_inv, update_std):
-        """raw preprocess -> curvature step -> precondition -> preconditioned preprocess -> update."""
+        """raw preprocess -> curvature step -> precondition -> preconditioned preprocess -> update.
+        Groups whose tensors are flat fp32 run each of the two preprocess stages (and the update) as
+        one launch of the fused tail kernel; the others take the per-group multi-tensor path."""
+        fused = self._fused_tail(groups, target, 'raw')
         for group in groups:
-            self.update_preprocess(group, target=target, grad_type='raw')
+            if id(group) not in fused:
+                self.update_preprocess(group, target=target, grad_type='raw')
         self._curvature_step(groups, target, update_inv, update_std)
-        for group in groups:
+        fused = self._fused_tail(groups, target, 'preconditioned')
+        rest = [g for g in groups if id(g) not in fused]
+        for group in rest:
             self.update_preprocess(group, target=target, grad_type='preconditioned')
-        self._apply_update(groups, target)
+        self._apply_update(rest, target)
         for group in groups:
             self.update_postprocess(group, target=target)
+
+    def _fused_tail(self, groups, target, stage):
+        """torchsso/optim/secondorder.py:225-283 for all eligible groups in one kernel launch.
+        Returns the ids of the groups it handled."""
+        raw = stage == 'raw'
+        items, key, handled = [], [], set()
+        for group in groups:
+            if group['lars']:
+                continue                      # needs per-tensor norms: multi-tensor path
+            params = [p for p in group[target] if p.grad is not None]
+            if not params or any(p.dtype != torch.float32 or p.grad.dtype != torch.float32 or
+                                 not p.data.is_contiguous() or not p.grad.is_contiguous() for p in params):
+                continue
+            add = group['l2_reg'] if raw else group['weight_decay']
+            use_m = group['momentum'] != 0 and group['momentum_type'] == stage
+            use_e = group['grad_ema_decay'] != 1 and group['grad_ema_type'] == stage
+            scale = 1.0
+            if not raw and group['bias_correction']:
+                curv = group['curv']
+                bc1 = 1 - (1 - group['grad_ema_decay']) ** self.optim_state['step']
+                bc2 = 1 - (1 - curv.ema_decay) ** self.optim_state['step']
+                if getattr(curv, 'use_sqrt_ema', False):
+                    bc2 = math.sqrt(bc2)
+                scale = bc2 / bc1
+            lr = 0.0 if raw else group['lr']
+            handled.add(id(group))
+            if raw and group['l2_reg'] != 0 and group['curv'] is not None:
+                group['curv'].l2_reg = group['l2_reg']
+            if raw and add == 0 and not use_m and not use_e:
+                continue                      # nothing to apply at this stage
+            for p in params:
+                st = self.state[p]
+                items.append((p.data, p.grad, st['momentum_buffer'] if use_m else None,
+                              st['grad_ema_buffer'] if use_e else None, float(add), float(group['momentum']),
+                              float(group['grad_ema_decay']), float(scale), float(lr)))
+                key.append((p.data.data_ptr(), p.grad.data_ptr(), use_m, use_e, add, group['momentum'],
+                            group['grad_ema_decay'], scale, lr))
+        if items:
+            cache = self.__dict__.setdefault('_tail_tables', {})
+            ent = cache.get((target, stage))
+            key = tuple(key)
+            if ent is None or ent[0] != key:
+                ent = (key, nat.tail_records(items, items[0][0].device))
+                cache[(target, stage)] = ent
+            nat.optimizer_tail(ent[1])
+        return handled
 
     def _curvature_step(self, groups, target, update_inv, update_std):
         pooled = [g for g in groups if g['curv'] is not None and _is_pooled(g['curv'])]

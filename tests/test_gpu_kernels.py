@@ -530,3 +530,41 @@ def test_sample_matches_oracle(nat, da, dg, bias):
     assert rel(w, rw) < 1e-5
     if bias:
         assert rel(b, rb) < 1e-5
+
+
+def test_optimizer_tail_matches_torch(nat):
+    """sso_optimizer_tail against the chain of multi-tensor torch ops it replaces
+    (torchsso/optim/secondorder.py:225-283): l2 / weight decay, momentum, gradient moving average,
+    bias-correction scale, update."""
+    torch.manual_seed(3)
+    shapes = [(70000,), (33,), (128, 65)]
+    items, ref = [], []
+    for i, shp in enumerate(shapes):
+        p, g = torch.randn(shp, device='cuda'), torch.randn(shp, device='cuda')
+        m, e = torch.randn(shp, device='cuda'), torch.randn(shp, device='cuda')
+        use_m, use_e = i != 1, i != 0
+        add, mom, ema, scale, lr = 1e-2 * (i + 1), 0.9, 0.3, 1.5, 0.05 if i != 2 else 0.0
+        rp, rg, rm, re = p.double(), g.double(), m.double(), e.double()
+        rg = rg + add * rp
+        if use_m:
+            rm = mom * rm + rg
+            rg = rm
+        if use_e:
+            re = (1 - ema) * re + ema * rg
+            rg = re
+        rg = rg * scale
+        rp = rp - lr * rg
+        ref.append((rp, rg, rm, re))
+        items.append((p, g, m if use_m else None, e if use_e else None, add, mom, ema, scale, lr))
+    table = nat.tail_records([(p.view(-1), g.view(-1), None if m is None else m.view(-1),
+                               None if e is None else e.view(-1), a, mo, em, sc, lr)
+                              for p, g, m, e, a, mo, em, sc, lr in items], torch.device('cuda'))
+    untouched = [(None if it[2] is None else it[2].clone(), None if it[3] is None else it[3].clone()) for it in items]
+    nat.optimizer_tail(table)
+    torch.cuda.synchronize()
+    for (p, g, m, e, *_), (rp, rg, rm, re) in zip(items, ref):
+        assert rel(p, rp) < 1e-6 and rel(g, rg) < 1e-6
+        if m is not None:
+            assert rel(m, rm) < 1e-6
+        if e is not None:
+            assert rel(e, re) < 1e-6
