@@ -159,15 +159,23 @@ __global__ void __launch_bounds__(256) bn_plane_sums_vec(const T* __restrict__ t
       sh[i] = (IS_Y && shift) ? shift[c0 + i] : 0.f;
     }
     const T* base = t + (int64_t)in * sn + c0;
-    for (int p = p0 + pp; p < p1; p += npp) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)p * sp));
+    auto add = [&](const uint4& raw) {
       const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         const float v = (to_f32<T>(e[i]) - sh[i]) * isc[i];
         acc[i] = fmaf(v, v, acc[i]);
       }
+    };
+    int p = p0 + pp;
+    for (; p + 3 * npp < p1; p += 4 * npp) {      // four independent 16-byte loads in flight per thread
+      const uint4 r0 = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)p * sp));
+      const uint4 r1 = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(p + npp) * sp));
+      const uint4 r2 = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(p + 2 * npp) * sp));
+      const uint4 r3 = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)(p + 3 * npp) * sp));
+      add(r0); add(r1); add(r2); add(r3);
     }
+    for (; p < p1; p += npp) add(__ldg(reinterpret_cast<const uint4*>(base + (int64_t)p * sp)));
   }
 #pragma unroll
   for (int i = 0; i < V; ++i) red[threadIdx.x][i] = acc[i];
@@ -233,8 +241,8 @@ static int bn_vec_splits(int64_t n, int64_t c, int64_t hw, int vec) {
   const int lp = bn_vec_lanes(c, vec);
   if (lp == 0 || hw <= 1) return 1;
   const int npp = 256 / lp;
-  int64_t s = ceil_div64(3 * kSMs / 2, n);                   // about one and a half waves of blocks
-  const int64_t most = std::max<int64_t>(1, hw / (4 * npp)); // at least four pixels per lane
+  int64_t s = ceil_div64(4 * kSMs, n);                       // about four blocks per SM
+  const int64_t most = std::max<int64_t>(1, hw / (8 * npp)); // at least eight pixels per lane
   if (s > most) s = most;
   return (int)std::max<int64_t>(1, s);
 }
