@@ -27,7 +27,9 @@ class GraphedClosure:
         # Warm up and capture on ONE side stream: autograd's gradient-accumulation nodes run on the
         # stream they were created on, so they must be (re)created on the stream that captures.
         torch.cuda.synchronize()
-        side = torch.cuda.Stream()
+        # high priority: the model's own kernels (the critical path) go before the curvature kernels
+        # that the hooks fork to the (default-priority) curvature stream
+        side = torch.cuda.Stream(priority=-1)
         side.wait_stream(torch.cuda.current_stream())
         from torchsso import _native as nat
         with torch.cuda.stream(side):
