@@ -113,13 +113,20 @@ class DevicePacker:
 
 class KFACCommunicator:
 
-    def __init__(self, group=None, packer=None):
+    def __init__(self, group=None, packer=None, wire_dtype=None):
+        """``wire_dtype`` (torch.bfloat16 / torch.float16, default None = fp32): the packed buffers
+        cross the links in that type (half the bytes), as the reference's ``allreduce_grad_dtype``
+        option does (pure_nccl_communicator.py:359-412).  It rounds factors and gradients to 8 / 11
+        mantissa bits, so it is off in every parity configuration."""
         if not dist.is_initialized():
             raise RuntimeError('torch.distributed is not initialised')
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
         self.packer = packer if packer is not None else DevicePacker()
+        if wire_dtype not in (None, torch.float32, torch.bfloat16, torch.float16):
+            raise ValueError('wire_dtype must be None, torch.bfloat16 or torch.float16')
+        self.wire_dtype = None if wire_dtype == torch.float32 else wire_dtype
         self.indices = None
         self._optimizer = None
         self._bufs = {}
@@ -161,7 +168,7 @@ class KFACCommunicator:
             recv = send[:seg]
         if arrays[self.rank]:
             self.packer.unpack(arrays[self.rank], recv, 0, True)
-        self.last_bytes['rsv'] = 4 * seg * self.size
+        self.last_bytes['rsv'] = (4 if self.wire_dtype is None else 2) * seg * self.size
 
     def allgatherv_arrays(self, arrays: Arrays, symmetric=True):
         """Every rank ends up with rank r's values of every array in arrays[r]."""
@@ -180,9 +187,34 @@ class KFACCommunicator:
         for r, local in enumerate(arrays):
             if local and r != self.rank:
                 self.packer.unpack(local, recv, r * seg, symmetric)
-        self.last_bytes['agv'] = 4 * seg * self.size
+        self.last_bytes['agv'] = (4 if self.wire_dtype is None else 2) * seg * self.size
+
+    def _wire(self, name, like):
+        b = self._bufs.get(name)
+        if b is None or b.numel() < like.numel() or b.device != like.device or b.dtype != self.wire_dtype:
+            b = torch.empty(like.numel(), dtype=self.wire_dtype, device=like.device)
+            self._bufs[name] = b
+        return b[:like.numel()]
 
     def _reduce_scatter(self, recv, send, seg):
+        if self.wire_dtype is not None:
+            send16, recv16 = self._wire('rsv_send16', send), self._wire('rsv_recv16', recv)
+            send16.copy_(send)
+            self._reduce_scatter_raw(recv16, send16, seg)
+            recv.copy_(recv16)
+            return
+        self._reduce_scatter_raw(recv, send, seg)
+
+    def _all_gather(self, recv, send, seg):
+        if self.wire_dtype is not None:
+            send16, recv16 = self._wire('agv_send16', send), self._wire('agv_recv16', recv)
+            send16.copy_(send)
+            self._all_gather_raw(recv16, send16, seg)
+            recv.copy_(recv16)
+            return
+        self._all_gather_raw(recv, send, seg)
+
+    def _reduce_scatter_raw(self, recv, send, seg):
         backend = dist.get_backend(self.group)
         if backend == 'nccl':
             dist.reduce_scatter_tensor(recv, send, op=dist.ReduceOp.SUM, group=self.group)
@@ -190,7 +222,7 @@ class KFACCommunicator:
             dist.all_reduce(send, op=dist.ReduceOp.SUM, group=self.group)
             recv.copy_(send[self.rank * seg:(self.rank + 1) * seg])
 
-    def _all_gather(self, recv, send, seg):
+    def _all_gather_raw(self, recv, send, seg):
         backend = dist.get_backend(self.group)
         if backend == 'nccl':
             dist.all_gather_into_tensor(recv, send, group=self.group)
@@ -248,6 +280,6 @@ class KFACCommunicator:
                     curv._have.add('std')
 
 
-def create_communicator(group=None, packer=None, **unused):
+def create_communicator(group=None, packer=None, wire_dtype=None, **unused):
     """Communicator over the default (or given) process group; one process per GPU, NCCL backend."""
-    return KFACCommunicator(group=group, packer=packer)
+    return KFACCommunicator(group=group, packer=packer, wire_dtype=wire_dtype)

@@ -56,19 +56,19 @@ def _make_arrays(rank, world, dims):
     return arrays
 
 
-def _worker(rank, world, port, dims, ret):
+def _worker(rank, world, port, dims, ret, wire_dtype=None, atol=1e-6):
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     dist.init_process_group('gloo', rank=rank, world_size=world)
     try:
         from torchsso.utils.communicator import KFACCommunicator
-        comm = KFACCommunicator(packer=TorchPacker())
+        comm = KFACCommunicator(packer=TorchPacker(), wire_dtype=wire_dtype)
         arrays = _make_arrays(rank, world, dims)
         expect = ko.reduce_scatterv_mean([[t for t, _ in _make_arrays(r, world, dims)[rank]]
                                           for r in range(world)])
         comm.reduce_scatterv_arrays(arrays)
         for (got, _), exp in zip(arrays[rank], expect):
-            assert torch.allclose(got, exp, atol=1e-6), 'owner did not receive the world mean'
+            assert torch.allclose(got, exp, atol=atol), 'owner did not receive the world mean'
         # arrays owned by other ranks are untouched
         other = (rank + 1) % world
         for (got, _), (orig, _) in zip(arrays[other], _make_arrays(rank, world, dims)[other]):
@@ -79,7 +79,7 @@ def _worker(rank, world, port, dims, ret):
             exp = ko.reduce_scatterv_mean([[t for t, _ in _make_arrays(r, world, dims)[owner]]
                                            for r in range(world)])
             for (got, _), e in zip(arrays[owner], exp):
-                assert torch.allclose(got, e, atol=1e-6)
+                assert torch.allclose(got, e, atol=atol)
         sizes, seg = comm.segment_sizes(arrays)
         assert seg % 64 == 0 and seg >= max(sizes)
         ret[rank] = 'ok'
@@ -93,6 +93,16 @@ def test_two_rank_exchange_gloo():
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, port, dims, ret), nprocs=world, join=True)
+    assert dict(ret) == {0: 'ok', 1: 'ok'}
+
+
+def test_two_rank_exchange_gloo_half_wire():
+    """Optional 16-bit wire format: same exchange, values rounded to fp16 on the way."""
+    world, dims = 2, [5, 9]
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, port, dims, ret, torch.float16, 2e-2), nprocs=world, join=True)
     assert dict(ret) == {0: 'ok', 1: 'ok'}
 
 
