@@ -92,3 +92,94 @@ def test_two_gpu_data_parallel_equals_accumulation(balance):
             assert err < 2e-5, (rank, err)
     for a, b in zip(ret[0], ret[1]):
         assert torch.equal(a, b), 'ranks disagree after the all-gather'
+
+
+# ---------------------------------------------------------------------------------------------
+# MC-sample parallel VI: two ranks with one weight sample each on the SAME batch equal one process
+# with two samples, when rank r draws the noise the single process draws for its sample r.
+# ---------------------------------------------------------------------------------------------
+VI_STEPS = 3
+
+
+def _vi_setup(device, num_mc, distributed):
+    import torchsso
+    model = cases.make_model('tiny_vgg', seed=4).to(device)
+    cls = torchsso.optim.DistributedVIOptimizer if distributed else torchsso.optim.VIOptimizer
+    opt = cls(model, 1000, 'Cov', KRON, {'ema_decay': 0.95, 'damping': 1e-3}, lr=1e-2,
+              num_mc_samples=num_mc, val_num_mc_samples=2, kl_weighting=1, prior_variance=1)
+    return model, opt
+
+
+def _vi_noise_patch(state):
+    def fake_randn_like(t, **kw):
+        s = state['seed'] * 1000 + state['count']
+        state['count'] += 1
+        return cases.make_normal(tuple(t.shape), s).to(device=t.device, dtype=t.dtype)
+    torch.randn_like = fake_randn_like
+
+
+def _vi_closure(model, opt, x, y):
+    import torch.nn.functional as F
+
+    def closure():
+        opt.zero_grad()
+        o = model(x)
+        loss = F.cross_entropy(o, y)
+        loss.backward()
+        return loss, o
+    return closure
+
+
+def _run_vi_single(device):
+    model, opt = _vi_setup(device, 2, False)
+    state = {'seed': 0, 'count': 0}
+    _vi_noise_patch(state)
+    per_sample = None
+    for t in range(VI_STEPS):
+        x, y = cases.make_batch((8, 3, 8, 8), 6, seed=600 + t)
+        state['seed'], state['count'] = 700 + t, 0
+        opt.step(closure=_vi_closure(model, opt, x.to(device), y.to(device)))
+        per_sample = state['count'] // 2
+    means = [m.detach().cpu().clone() for g in opt.param_groups for m in g['mean']]
+    return means, per_sample
+
+
+def _vi_worker(rank, world, port, per_sample, ret):
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ['NCCL_NVLS_ENABLE'] = '0'
+    torch.cuda.set_device(rank)
+    device = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    try:
+        model, opt = _vi_setup(device, 1, True)
+        state = {'seed': 0, 'count': 0}
+        _vi_noise_patch(state)
+        for t in range(VI_STEPS):
+            x, y = cases.make_batch((8, 3, 8, 8), 6, seed=600 + t)     # same batch on both ranks
+            state['seed'], state['count'] = 700 + t, rank * per_sample
+            opt.step(closure=_vi_closure(model, opt, x.to(device), y.to(device)))
+        opt.pool.check_info()
+        ret[rank] = [m.detach().cpu().clone() for g in opt.param_groups for m in g['mean']]
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_vi_mc_parallel_equals_two_samples():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    real = torch.randn_like
+    try:
+        ref, per_sample = _run_vi_single(torch.device('cuda', 0))
+    finally:
+        torch.randn_like = real
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_vi_worker, args=(2, _free_port(), per_sample, ret), nprocs=2, join=True)
+    for rank in range(2):
+        for got, exp in zip(ret[rank], ref):
+            err = ((got - exp).norm() / exp.norm().clamp_min(1e-12)).item()
+            assert err < 5e-5, (rank, err)
+    for a, b in zip(ret[0], ret[1]):
+        assert torch.equal(a, b), 'ranks disagree after the all-gather'
