@@ -5,6 +5,7 @@
     python pytorch-sso_b200/microbench.py inverse  [--case I]      damped SPD inverse, d in 64..4608
     python pytorch-sso_b200/microbench.py precond  [--case I]      G^-1 dW A^-1
     python pytorch-sso_b200/microbench.py stream                   EMA / axpby / BN plane sums
+    python pytorch-sso_b200/microbench.py steps                    whole steps of the smaller reference configurations
     python pytorch-sso_b200/microbench.py peaks                    cuBLAS bf16 / TF32 GEMM and copy, for reference
     torchrun ... pytorch-sso_b200/microbench.py collective         factor exchange sweep (N > 1)
 
@@ -184,6 +185,130 @@ def suite_peaks(args):
     emit(suite='peaks', kernel='copy 1 GiB', ms=round(ms, 4), gbs=round(2.0 * 4 * (1 << 28) / ms / 1e6, 1))
 
 
+def suite_steps(args):
+    """Whole optimizer steps of the smaller reference configurations (fp32, eager launches, a fresh
+    seeded batch every step): the 784-1000-1000-10 MLP at batch 128 with inverses every step, the
+    5x5/5x5/3x3 ConvNet at batch 256 with inverses every 5 steps, and the VGG-16-style network under
+    VIOptimizer with 4 weight samples per step at batch 128."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+    import torchsso
+
+    class MLP(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.f1, self.f2, self.f3 = nn.Linear(784, 1000), nn.Linear(1000, 1000), nn.Linear(1000, 10)
+
+        def forward(self, x):
+            return self.f3(F.relu(self.f2(F.relu(self.f1(x.flatten(1))))))
+
+    class ConvNet(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1, self.c2 = nn.Conv2d(3, 64, 5, padding=2), nn.Conv2d(64, 128, 5, padding=2)
+            self.c3 = nn.Conv2d(128, 256, 3, padding=1)
+            self.f1, self.f2 = nn.Linear(4096, 512), nn.Linear(512, 10)
+
+        def forward(self, x):
+            x = F.max_pool2d(F.relu(self.c1(x)), 2)
+            x = F.max_pool2d(F.relu(self.c2(x)), 2)
+            x = F.max_pool2d(F.relu(self.c3(x)), 2)
+            return self.f2(F.relu(self.f1(x.flatten(1))))
+
+    class VGG(nn.Module):
+        def __init__(self):
+            super().__init__()
+            cfg = [64, 64, 'M', 128, 128, 'M', 256, 256, 256, 'M', 512, 512, 512, 'M', 512, 512, 512, 'M']
+            layers, c = [], 3
+            for v in cfg:
+                if v == 'M':
+                    layers.append(None)
+                else:
+                    layers.append(nn.Conv2d(c, v, 3, padding=1))
+                    c = v
+            self.convs = nn.ModuleList([l for l in layers if l is not None])
+            self.plan = [l is not None for l in layers]
+            self.fc = nn.Linear(512, 100)
+
+        def forward(self, x):
+            it = iter(self.convs)
+            for is_conv in self.plan:
+                x = F.relu(next(it)(x)) if is_conv else F.max_pool2d(x, 2)
+            return self.fc(x.flatten(1))
+
+    kron = {'Conv2d': 'Kron', 'Linear': 'Kron'}
+    kw = {'ema_decay': 0.95, 'damping': 1e-3}
+    dev = torch.device('cuda')
+
+    def batches(shape, classes, count=8):
+        g = torch.Generator(device='cuda').manual_seed(11)
+        xs = [torch.randn(shape, device='cuda', generator=g) for _ in range(count)]
+        ys = [torch.randint(0, classes, (shape[0],), device='cuda', generator=g) for _ in range(count)]
+        return xs, ys
+
+    def run(name, step, batch, iters):
+        for i in range(3):
+            step(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            loss = step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        emit(suite='steps', config=name, batch=batch, ms_per_step=round(ms, 3),
+             images_per_sec=round(batch / ms * 1e3, 1), last_loss=round(float(loss), 4))
+
+    torch.manual_seed(0)
+    # MLP, inverse every step
+    model = MLP().to(dev)
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', kron, kw, lr=1e-2)
+    xs, ys = batches((128, 1, 28, 28), 10)
+    x, y = xs[0].clone(), ys[0].clone()
+    closure = torchsso.get_closure_for_fisher(opt, model, x, y, approx_type='mc', num_mc=1)
+
+    def step_mlp(i):
+        x.copy_(xs[i % 8]); y.copy_(ys[i % 8])
+        opt.update_inv = True
+        return opt.step(closure=closure)[0]
+    run('mlp 784-1000-1000-10, Fisher MC, inverse every step', step_mlp, 128, args.iters * 3)
+
+    # ConvNet (NCHW, as a reference user would run it), inverse every 5 steps
+    model2 = ConvNet().to(dev)
+    opt2 = torchsso.optim.SecondOrderOptimizer(model2, 'Fisher', kron, kw, lr=1e-3)
+    xs2, ys2 = batches((256, 3, 32, 32), 10)
+    x2, y2 = xs2[0].clone(), ys2[0].clone()
+    closure2 = torchsso.get_closure_for_fisher(opt2, model2, x2, y2, approx_type='mc', num_mc=1)
+
+    def step_conv(i):
+        x2.copy_(xs2[i % 8]); y2.copy_(ys2[i % 8])
+        opt2.update_inv = (i % 5 == 0)
+        return opt2.step(closure=closure2)[0]
+    run('convnet 5x5-5x5-3x3 + 4096-512-10, Fisher MC, inverse every 5', step_conv, 256, args.iters * 2)
+
+    # VGG-16-style under VIOptimizer, 4 weight samples per step
+    model3 = VGG().to(dev)
+    # kl_weighting 0.01 (the start value of the reference's warm-up, vi.py:302-319): with 1.0 the weight
+    # noise of the untrained network overflows the activations on N(0,1) inputs within two steps
+    opt3 = torchsso.optim.VIOptimizer(model3, 50000, 'Cov', kron, kw, lr=1e-3, num_mc_samples=4,
+                                      kl_weighting=0.01, prior_variance=1)
+    xs3, ys3 = batches((128, 3, 32, 32), 100, count=4)
+    x3, y3 = xs3[0].clone(), ys3[0].clone()
+
+    def closure3():
+        opt3.zero_grad()
+        o = model3(x3)
+        loss = F.cross_entropy(o, y3)
+        loss.backward()
+        return loss, o
+
+    def step_vi(i):
+        x3.copy_(xs3[i % 4]); y3.copy_(ys3[i % 4])
+        return opt3.step(closure=closure3)[0]
+    run('vgg16-style, VIOptimizer, 4 MC samples, inverse + std every step', step_vi, 128, max(3, args.iters // 2))
+
+
 def suite_collective(args):
     """Reduce-scatter of the tri-packed ResNet-50 factors to owner ranks and all-gather of the
     parameter-sized updates, as the distributed optimizer issues them (padded equal segments)."""
@@ -226,7 +351,7 @@ def suite_collective(args):
     dist.destroy_process_group()
 
 
-SUITES = {'peaks': suite_peaks, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
+SUITES = {'peaks': suite_peaks, 'steps': suite_steps, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
           'stream': suite_stream, 'collective': suite_collective}
 
 
