@@ -231,7 +231,7 @@ typedef struct {
   int32_t mat;        /* index into the diagonal-shift table, or -1 */
   int32_t mode;       /* 0 dst = src (+ shift on the diagonal), 1 dst = upper-triangular transpose
                          of src's lower triangle, 2 dst = 0 */
-  int32_t pad;
+  int32_t ld;         /* leading dimension of src and dst */
 } sso_copy_rec;
 
 typedef struct {
@@ -256,7 +256,8 @@ size_t sso_kron_plan_dev_bytes(int n_mats, const int64_t* dims, int with_std);
 int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src, float* const* dst,
                              float* const* work, float* const* std_out /* nullable */,
                              const int32_t* partner, const int32_t* role,
-                             void* dev_mem, size_t dev_mem_bytes, int host_only);
+                             void* dev_mem, size_t dev_mem_bytes, int host_only,
+                             const int64_t* lds /* nullable: leading dimensions of src/dst/work/std, default dims */);
 /* damp_r_dev: per-matrix r = sqrt(damping); info_dev: per-matrix status (2 ints: inverse, std) */
 int sso_kron_plan_run(int64_t plan, const float* damp_r_dev, int* info_dev,
                       int do_inverse, int do_std, void* stream);
@@ -269,7 +270,9 @@ size_t sso_precond_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t
 int64_t sso_precond_plan_create(int n_layers, const int64_t* dA, const int64_t* dG,
                                 float* const* A_inv, float* const* G_inv,
                                 float* const* gw, float* const* gb, float* const* tmp,
-                                void* dev_mem, size_t dev_mem_bytes, int host_only);
+                                void* dev_mem, size_t dev_mem_bytes, int host_only,
+                                const int64_t* ldA, const int64_t* ldG /* nullable: leading dimensions of
+                                A_inv / G_inv (default dA / dG); tmp is [dA x dG] with leading dimension ldG */);
 int sso_precond_plan_run(int64_t plan, void* stream);
 
 /* Posterior sampling  [W|b] <- [W|b] + s * U_G E U_A  (W, b pre-loaded with the mean by the
@@ -279,7 +282,8 @@ size_t sso_sample_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t*
 int64_t sso_sample_plan_create(int n_layers, const int64_t* dA, const int64_t* dG,
                                float* const* U_A, float* const* U_G, float* const* noise,
                                float* const* w, float* const* b, float* const* tmp,
-                               void* dev_mem, size_t dev_mem_bytes, int host_only);
+                               void* dev_mem, size_t dev_mem_bytes, int host_only,
+                               const int64_t* ldA, const int64_t* ldG /* nullable: leading dimensions of U_A / U_G */);
 int sso_sample_plan_run(int64_t plan, float std_scale, void* stream);
 
 int sso_plan_destroy(int64_t plan);

@@ -40,7 +40,7 @@ struct MatRec {       // per-matrix data for the trace / pi kernel
   int32_t d;
   int32_t partner;
   int32_t role;
-  int32_t pad;
+  int32_t ld;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(256) trace_kernel(const MatRec* __restrict__ m
   __shared__ float red[256];
   const MatRec m = mats[blockIdx.x];
   float s = 0.f;
-  for (int i = threadIdx.x; i < m.d; i += 256) s += m.src[(int64_t)i * m.d + i];
+  for (int i = threadIdx.x; i < m.d; i += 256) s += m.src[(int64_t)i * m.ld + i];
   red[threadIdx.x] = s;
   __syncthreads();
   for (int o = 128; o > 0; o >>= 1) {
@@ -298,18 +298,19 @@ __global__ void __launch_bounds__(256) copy_kernel(const CopyRec* __restrict__ r
                                                    const float* __restrict__ shift) {
   const CopyRec r = recs[blockIdx.x];
   const float v = (r.mat >= 0) ? shift[r.mat] : 0.f;
+  const int ld = r.ld;
   const int64_t total = (int64_t)r.nrows * r.d;
   for (int64_t e = threadIdx.x; e < total; e += 256) {
     const int row = r.row0 + (int)(e / r.d), col = (int)(e % r.d);
     if (r.mode == 2) {
-      r.dst[(int64_t)row * r.d + col] = 0.f;
+      r.dst[(int64_t)row * ld + col] = 0.f;
     } else if (r.mode == 1) {
       // dst = L^T restricted to the upper triangle (row <= col reads L[col][row])
-      r.dst[(int64_t)row * r.d + col] = (row <= col) ? r.src[(int64_t)col * r.d + row] : 0.f;
+      r.dst[(int64_t)row * ld + col] = (row <= col) ? r.src[(int64_t)col * ld + row] : 0.f;
     } else {
-      float x = r.src[(int64_t)row * r.d + col];
+      float x = r.src[(int64_t)row * ld + col];
       if (row == col) x += v;
-      r.dst[(int64_t)row * r.d + col] = x;
+      r.dst[(int64_t)row * ld + col] = x;
     }
   }
 }
@@ -394,8 +395,12 @@ struct Builder {
   }
 };
 
+static inline int padded_ld(int d) { return (d + 3) / 4 * 4; }   // rows of plan-owned matrices start on 16 bytes
+
 struct Mat {  // one square matrix being factorised
   int d, nb;
+  int ld;      // leading dimension of W, Li and T (the caller's buffers)
+  int ldx;     // leading dimension of X (plan-owned)
   float* W;    // holds M, then L (lower)
   float* Li;   // receives L^-1 (lower)
   float* X;    // receives L^-T (upper), or null: lets every product of the triangular inverse and of
@@ -421,7 +426,7 @@ static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot)
       for (auto& m : ms) {
         const int np = (m.d + PB - 1) / PB;
         for (int i = p; i < np; ++i)
-          b.gemm(blk2(m.W, m.d, i, 0), m.d, false, blk2(m.W, m.d, p, 0), m.d, true, blk2(m.W, m.d, i, p), m.d,
+          b.gemm(blk2(m.W, m.ld, i, 0), m.ld, false, blk2(m.W, m.ld, p, 0), m.ld, true, blk2(m.W, m.ld, i, p), m.ld,
                  std::min(PB, m.d - i * PB), std::min(PB, m.d - p * PB), p * PB, -1.f, 1.f);
       }
     b.end_phase(1, first, b.task_begin() - first);
@@ -431,26 +436,26 @@ static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot)
         first = b.task_begin();
         for (auto& m : ms)
           for (int i = j; i < m.nb; ++i)
-            b.gemm(blk(m.W, m.d, i, j - 1), m.d, false, blk(m.W, m.d, j, j - 1), m.d, true,
-                   blk(m.W, m.d, i, j), m.d, bsz(m, i), bsz(m, j), NB, -1.f, 1.f);
+            b.gemm(blk(m.W, m.ld, i, j - 1), m.ld, false, blk(m.W, m.ld, j, j - 1), m.ld, true,
+                   blk(m.W, m.ld, i, j), m.ld, bsz(m, i), bsz(m, j), NB, -1.f, 1.f);
         b.end_phase(0, first, b.task_begin() - first);
       }
       first = (int)b.p.diags.size();
       for (auto& m : ms)
         if (j < m.nb) {
           DiagRec r;
-          r.L = blk(m.W, m.d, j, j); r.Linv = blk(m.Li, m.d, j, j);
-          r.ld_l = m.d; r.ld_inv = m.d; r.size = bsz(m, j); r.mat = m.mat_index; r.row0 = j * NB;
+          r.L = blk(m.W, m.ld, j, j); r.Linv = blk(m.Li, m.ld, j, j);
+          r.ld_l = m.ld; r.ld_inv = m.ld; r.size = bsz(m, j); r.mat = m.mat_index; r.row0 = j * NB;
           r.info_slot = info_slot;
-          r.LinvT = m.X ? blk(m.X, m.d, j, j) : nullptr; r.ld_invt = m.d; r.pad = 0;
+          r.LinvT = m.X ? blk(m.X, m.ldx, j, j) : nullptr; r.ld_invt = m.ldx; r.pad = 0;
           b.p.diags.push_back(r);
         }
       b.end_phase(2, first, (int)b.p.diags.size() - first);
       first = b.task_begin();
       for (auto& m : ms)
         for (int i = j + 1; i < m.nb; ++i)
-          b.gemm(blk(m.W, m.d, i, j), m.d, false, blk(m.Li, m.d, j, j), m.d, true,
-                 blk(m.W, m.d, i, j), m.d, bsz(m, i), NB, NB, 1.f, 0.f);
+          b.gemm(blk(m.W, m.ld, i, j), m.ld, false, blk(m.Li, m.ld, j, j), m.ld, true,
+                 blk(m.W, m.ld, i, j), m.ld, bsz(m, i), NB, NB, 1.f, 0.f);
       b.end_phase(0, first, b.task_begin() - first);
     }
   }
@@ -468,30 +473,30 @@ static void emit_lauum(Builder& b, const std::vector<Mat>& ms) {
       for (int i = 0; i < nt; ++i)
         for (int j = 0; j <= i; ++j) {
           const int mi = std::min(tile, m.d - i * tile), nj = std::min(tile, m.d - j * tile);
-          float* C = m.T + (int64_t)i * tile * m.d + (int64_t)j * tile;
-          float* C2 = (i == j) ? nullptr : m.T + (int64_t)j * tile * m.d + (int64_t)i * tile;
+          float* C = m.T + (int64_t)i * tile * m.ld + (int64_t)j * tile;
+          float* C2 = (i == j) ? nullptr : m.T + (int64_t)j * tile * m.ld + (int64_t)i * tile;
           if (m.X) {   // T(i,j) = sum_{k >= i*tile} X(i,k) X(j,k): both operands read along k
-            const float* A = m.X + (int64_t)i * tile * m.d + (int64_t)i * tile;
-            const float* B = m.X + (int64_t)j * tile * m.d + (int64_t)i * tile;
-            b.gemm(A, m.d, false, B, m.d, true, C, m.d, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.d, i == j);
+            const float* A = m.X + (int64_t)i * tile * m.ldx + (int64_t)i * tile;
+            const float* B = m.X + (int64_t)j * tile * m.ldx + (int64_t)i * tile;
+            b.gemm(A, m.ldx, false, B, m.ldx, true, C, m.ld, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.ld, i == j);
             continue;
           }
           // rows k >= i*tile of Li contribute: A = Li[k, i-cols]^T, B = Li[k, j-cols]
-          const float* A = m.Li + (int64_t)i * tile * m.d + (int64_t)i * tile;
-          const float* B = m.Li + (int64_t)i * tile * m.d + (int64_t)j * tile;
-          b.gemm(A, m.d, true, B, m.d, false, C, m.d, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.d, i == j);
+          const float* A = m.Li + (int64_t)i * tile * m.ld + (int64_t)i * tile;
+          const float* B = m.Li + (int64_t)i * tile * m.ld + (int64_t)j * tile;
+          b.gemm(A, m.ld, true, B, m.ld, false, C, m.ld, mi, nj, m.d - i * tile, 1.f, 0.f, C2, m.ld, i == j);
         }
     }
     b.end_phase(pass == 0 ? 0 : 1, first, b.task_begin() - first);
   }
 }
 
-static void emit_copy(Builder& b, const float* src, float* dst, int d, int mat, int mode) {
+static void emit_copy(Builder& b, const float* src, float* dst, int d, int ld, int mat, int mode) {
   const int rows_per = std::max(1, 16384 / d);
   for (int r0 = 0; r0 < d; r0 += rows_per) {
     CopyRec c;
     c.src = src; c.dst = dst; c.d = d; c.row0 = r0; c.nrows = std::min(rows_per, d - r0);
-    c.mat = mat; c.mode = mode; c.pad = 0;
+    c.mat = mat; c.mode = mode; c.ld = ld;
     b.p.copies.push_back(c);
   }
 }
@@ -584,15 +589,17 @@ static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* 
 // task-count estimate without building (used for the *_dev_bytes queries): build and measure.
 static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* const* dst,
                         float* const* work, float* const* std_out, const int32_t* partner,
-                        const int32_t* role, float* const* xbuf) {
+                        const int32_t* role, float* const* xbuf, const int64_t* lds) {
   Plan* p = new Plan();
   std::vector<Mat> ms(n);
   for (int i = 0; i < n; ++i) {
     MatRec mr;
     mr.src = src ? src[i] : nullptr; mr.d = (int)dims[i];
-    mr.partner = partner ? partner[i] : -1; mr.role = role ? role[i] : 0; mr.pad = 0;
+    mr.partner = partner ? partner[i] : -1; mr.role = role ? role[i] : 0;
+    mr.ld = lds ? (int)lds[i] : (int)dims[i];
     p->mats.push_back(mr);
     ms[i].d = (int)dims[i]; ms[i].nb = (ms[i].d + NB - 1) / NB;
+    ms[i].ld = mr.ld; ms[i].ldx = padded_ld(ms[i].d);
     ms[i].W = dst ? dst[i] : nullptr;   // the output buffer first holds M + vI, then L
     ms[i].Li = work ? work[i] : nullptr;
     ms[i].X = xbuf ? xbuf[i] : nullptr;
@@ -609,9 +616,9 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
     Builder b(*p, &p->inv_phases);
     int first = (int)p->copies.size();
     for (int i = 0; i < n; ++i) {
-      emit_copy(b, src ? src[i] : nullptr, ms[i].W, ms[i].d, i, 0);
-      emit_copy(b, nullptr, ms[i].Li, ms[i].d, -1, 2);
-      if (ms[i].X) emit_copy(b, nullptr, ms[i].X, ms[i].d, -1, 2);
+      emit_copy(b, src ? src[i] : nullptr, ms[i].W, ms[i].d, ms[i].ld, i, 0);
+      emit_copy(b, nullptr, ms[i].Li, ms[i].d, ms[i].ld, -1, 2);
+      if (ms[i].X) emit_copy(b, nullptr, ms[i].X, ms[i].d, ms[i].ldx, -1, 2);
     }
     b.end_phase(3, first, (int)p->copies.size() - first);
     emit_cholesky(b, ms, 0);
@@ -632,11 +639,11 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
               // Y(i,j)^T = sum_{k in [j,mid)} Inv11(k,j)^T * L(i,k)^T  -> W block (j,i);
               // Inv11(k,j)^T = X(j,k) when the transposed inverse is kept
               if (m.X)
-                b.gemm(blk(m.X, m.d, j, j), m.d, false, blk(m.W, m.d, i, j), m.d, true,
-                       blk(m.W, m.d, j, i), m.d, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
+                b.gemm(blk(m.X, m.ldx, j, j), m.ldx, false, blk(m.W, m.ld, i, j), m.ld, true,
+                       blk(m.W, m.ld, j, i), m.ld, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
               else
-                b.gemm(blk(m.Li, m.d, j, j), m.d, true, blk(m.W, m.d, i, j), m.d, true,
-                       blk(m.W, m.d, j, i), m.d, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
+                b.gemm(blk(m.Li, m.ld, j, j), m.ld, true, blk(m.W, m.ld, i, j), m.ld, true,
+                       blk(m.W, m.ld, j, i), m.ld, T, std::min(T, m.d - i * NB), (mid - j) * NB, 1.f, 0.f);
         }
       b.end_phase(w == 1 ? 0 : 1, first, b.task_begin() - first);
       first = b.task_begin();
@@ -647,9 +654,9 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
             for (int j = lo; j < mid; j += w) {
               const int kk = std::min((i + w - mid) * NB, m.d - mid * NB);
               // Inv21(i,j) = - sum_k Inv22(i,k) * Y(k,j),  Y(k,j) stored at W(j,k) transposed
-              b.gemm(blk(m.Li, m.d, i, mid), m.d, false, blk(m.W, m.d, j, mid), m.d, true,
-                     blk(m.Li, m.d, i, j), m.d, std::min(T, m.d - i * NB), T, kk, -1.f, 0.f,
-                     m.X ? blk(m.X, m.d, j, i) : nullptr, m.d);
+              b.gemm(blk(m.Li, m.ld, i, mid), m.ld, false, blk(m.W, m.ld, j, mid), m.ld, true,
+                     blk(m.Li, m.ld, i, j), m.ld, std::min(T, m.d - i * NB), T, kk, -1.f, 0.f,
+                     m.X ? blk(m.X, m.ldx, j, i) : nullptr, m.ldx);
             }
         }
       b.end_phase(w == 1 ? 0 : 1, first, b.task_begin() - first);
@@ -669,12 +676,12 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
       cs[i].W = work[i];
       cs[i].Li = std_out[i];
       cs[i].X = nullptr;
-      emit_copy(b, dst[i], work[i], ms[i].d, -1, 0);
+      emit_copy(b, dst[i], work[i], ms[i].d, ms[i].ld, -1, 0);
     }
     b.end_phase(3, first, (int)p->copies.size() - first);
     emit_cholesky(b, cs, 1);
     first = (int)p->copies.size();
-    for (int i = 0; i < n; ++i) emit_copy(b, work[i], std_out[i], ms[i].d, -1, 1);
+    for (int i = 0; i < n; ++i) emit_copy(b, work[i], std_out[i], ms[i].d, ms[i].ld, -1, 1);
     b.end_phase(3, first, (int)p->copies.size() - first);
   }
   return p;
@@ -688,7 +695,7 @@ extern "C" {
 
 static size_t kron_scratch_bytes(int n_mats, const int64_t* dims) {
   size_t b = 0;
-  for (int i = 0; i < n_mats; ++i) b += align_up((size_t)dims[i] * (size_t)dims[i] * sizeof(float));
+  for (int i = 0; i < n_mats; ++i) b += align_up((size_t)dims[i] * (size_t)padded_ld((int)dims[i]) * sizeof(float));
   return b;
 }
 
@@ -697,7 +704,7 @@ size_t sso_kron_plan_dev_bytes(int n_mats, const int64_t* dims, int with_std) {
   std::vector<float*> fake(n_mats, nullptr);
   std::vector<float*> fake_x(n_mats, reinterpret_cast<float*>(4096));   // non-null: the scratch matrices exist
   Plan* p = build_kron(n_mats, dims, fake.data(), fake.data(), fake.data(),
-                       with_std ? fake.data() : nullptr, nullptr, nullptr, fake_x.data());
+                       with_std ? fake.data() : nullptr, nullptr, nullptr, fake_x.data(), nullptr);
   const size_t bytes = plan_table_bytes(p->tasks.size(), p->diags.size(), p->copies.size(), p->mats.size());
   delete p;
   return kron_scratch_bytes(n_mats, dims) + 256 + bytes;
@@ -705,7 +712,8 @@ size_t sso_kron_plan_dev_bytes(int n_mats, const int64_t* dims, int with_std) {
 
 int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src, float* const* dst,
                              float* const* work, float* const* std_out, const int32_t* partner,
-                             const int32_t* role, void* dev_mem, size_t dev_mem_bytes, int host_only) {
+                             const int32_t* role, void* dev_mem, size_t dev_mem_bytes, int host_only,
+                             const int64_t* lds) {
   SSO_CHECK_ARG(n_mats > 0 && dims && src && dst && work, "kron plan: null argument");
   for (int i = 0; i < n_mats; ++i) {
     SSO_CHECK_ARG(dims[i] > 0 && dims[i] <= 32768, "kron plan: bad dim %lld", (long long)dims[i]);
@@ -721,10 +729,12 @@ int64_t sso_kron_plan_create(int n_mats, const int64_t* dims, float* const* src,
     char* q = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(dev_mem)));
     for (int i = 0; i < n_mats; ++i) {
       xb[i] = reinterpret_cast<float*>(q);
-      q += align_up((size_t)dims[i] * (size_t)dims[i] * sizeof(float));
+      q += align_up((size_t)dims[i] * (size_t)padded_ld((int)dims[i]) * sizeof(float));
     }
   }
-  Plan* p = build_kron(n_mats, dims, src, dst, work, std_out, partner, role, xb.data());
+  if (lds)
+    for (int i = 0; i < n_mats; ++i) SSO_CHECK_ARG(lds[i] >= dims[i], "kron plan: leading dimension %lld < dim %lld", (long long)lds[i], (long long)dims[i]);
+  Plan* p = build_kron(n_mats, dims, src, dst, work, std_out, partner, role, xb.data(), lds);
   p->host_only = host_only != 0;
   if (!p->host_only) {
     const int rc = upload(*p, reinterpret_cast<char*>(dev_mem) + scratch, dev_mem_bytes - scratch);
@@ -760,45 +770,50 @@ int sso_kron_plan_run(int64_t plan, const float* damp_r_dev, int* info_dev, int 
 
 // ---- precondition --------------------------------------------------------------------------
 static Plan* build_precond(int n, const int64_t* dA, const int64_t* dG, float* const* A_inv,
-                           float* const* G_inv, float* const* gw, float* const* gb, float* const* tmp) {
+                           float* const* G_inv, float* const* gw, float* const* gb, float* const* tmp,
+                           const int64_t* ldA, const int64_t* ldG) {
   Plan* p = new Plan();
   Builder b(*p, &p->run_phases);
   constexpr int T = 128;
   // Both factors are symmetric, which lets every operand be read along its contiguous
   // direction (the fast path of the tensor-core tasks):
   //   tmp = U^T = A_inv[:, :wc] * gw^T (+ A_inv[:, wc] * gb^T),   [gw | gb] = G_inv * U.
+  // la / lg: leading dimensions of A_inv / G_inv; tmp is [d_A x d_G] with leading dimension lg.
   int first = b.task_begin();
   for (int l = 0; l < n; ++l) {
     const int a = (int)dA[l], g = (int)dG[l];
+    const int la = ldA ? (int)ldA[l] : a, lg = ldG ? (int)ldG[l] : g;
     const bool bias = gb && gb[l];
     const int wcols = bias ? a - 1 : a;
     for (int i = 0; i < a; i += T)
       for (int j = 0; j < g; j += T)
-        b.gemm(A_inv[l] + (int64_t)i * a, a, false, gw[l] + (int64_t)j * wcols, wcols, true,
-               tmp[l] + (int64_t)i * g + j, g, std::min(T, a - i), std::min(T, g - j), wcols, 1.f, 0.f);
+        b.gemm(A_inv[l] + (int64_t)i * la, la, false, gw[l] + (int64_t)j * wcols, wcols, true,
+               tmp[l] + (int64_t)i * lg + j, lg, std::min(T, a - i), std::min(T, g - j), wcols, 1.f, 0.f);
   }
   b.end_phase(1, first, b.task_begin() - first);
   first = b.task_begin();
   for (int l = 0; l < n; ++l) {
     const int a = (int)dA[l], g = (int)dG[l];
+    const int la = ldA ? (int)ldA[l] : a, lg = ldG ? (int)ldG[l] : g;
     if (!(gb && gb[l])) continue;
     for (int i = 0; i < a; i += NB)
       for (int j = 0; j < g; j += NB)
-        b.gemm(A_inv[l] + (int64_t)i * a + (a - 1), a, false, gb[l] + j, g, false,
-               tmp[l] + (int64_t)i * g + j, g, std::min(NB, a - i), std::min(NB, g - j), 1, 1.f, 1.f);
+        b.gemm(A_inv[l] + (int64_t)i * la + (a - 1), la, false, gb[l] + j, g, false,
+               tmp[l] + (int64_t)i * lg + j, lg, std::min(NB, a - i), std::min(NB, g - j), 1, 1.f, 1.f);
   }
   b.end_phase(0, first, b.task_begin() - first);
   first = b.task_begin();
   for (int l = 0; l < n; ++l) {
     const int a = (int)dA[l], g = (int)dG[l];
+    const int lg = ldG ? (int)ldG[l] : g;
     const bool bias = gb && gb[l];
     const int wcols = bias ? a - 1 : a;
     for (int i = 0; i < g; i += T) {
       for (int j = 0; j < wcols; j += T)
-        b.gemm(G_inv[l] + (int64_t)i * g, g, false, tmp[l] + (int64_t)j * g, g, true,
+        b.gemm(G_inv[l] + (int64_t)i * lg, lg, false, tmp[l] + (int64_t)j * lg, lg, true,
                gw[l] + (int64_t)i * wcols + j, wcols, std::min(T, g - i), std::min(T, wcols - j), g, 1.f, 0.f);
       if (bias)
-        b.gemm(G_inv[l] + (int64_t)i * g, g, false, tmp[l] + (int64_t)wcols * g, g, true,
+        b.gemm(G_inv[l] + (int64_t)i * lg, lg, false, tmp[l] + (int64_t)wcols * lg, lg, true,
                gb[l] + i, 1, std::min(T, g - i), 1, g, 1.f, 0.f);
     }
   }
@@ -818,12 +833,12 @@ size_t sso_precond_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t
 int64_t sso_precond_plan_create(int n_layers, const int64_t* dA, const int64_t* dG,
                                 float* const* A_inv, float* const* G_inv, float* const* gw,
                                 float* const* gb, float* const* tmp, void* dev_mem,
-                                size_t dev_mem_bytes, int host_only) {
+                                size_t dev_mem_bytes, int host_only, const int64_t* ldA, const int64_t* ldG) {
   SSO_CHECK_ARG(n_layers > 0 && dA && dG && A_inv && G_inv && gw && tmp, "precond plan: null argument");
   for (int l = 0; l < n_layers; ++l)
     SSO_CHECK_ARG(dA[l] > 0 && dG[l] > 0 && A_inv[l] && G_inv[l] && gw[l] && tmp[l],
                   "precond plan: bad layer %d", l);
-  Plan* p = build_precond(n_layers, dA, dG, A_inv, G_inv, gw, gb, tmp);
+  Plan* p = build_precond(n_layers, dA, dG, A_inv, G_inv, gw, gb, tmp, ldA, ldG);
   p->host_only = host_only != 0;
   if (!p->host_only) {
     const int rc = upload(*p, dev_mem, dev_mem_bytes);
@@ -841,7 +856,7 @@ int sso_precond_plan_run(int64_t plan, void* stream) {
 // ---- posterior sampling --------------------------------------------------------------------
 static Plan* build_sample(int n, const int64_t* dA, const int64_t* dG, float* const* U_A,
                           float* const* U_G, float* const* noise, float* const* w, float* const* bvec,
-                          float* const* tmp) {
+                          float* const* tmp, const int64_t* ldA, const int64_t* ldG) {
   Plan* p = new Plan();
   Builder b(*p, &p->run_phases);
   constexpr int T = 128;
@@ -851,7 +866,7 @@ static Plan* build_sample(int n, const int64_t* dA, const int64_t* dG, float* co
     const int a = (int)dA[l], g = (int)dG[l];
     for (int i = 0; i < g; i += T)
       for (int j = 0; j < a; j += T)
-        b.gemm(U_G[l] + (int64_t)i * g + i, g, false, noise[l] + (int64_t)i * a + j, a, false,
+        b.gemm(U_G[l] + (int64_t)i * (ldG ? (int)ldG[l] : g) + i, ldG ? (int)ldG[l] : g, false, noise[l] + (int64_t)i * a + j, a, false,
                tmp[l] + (int64_t)i * a + j, a, std::min(T, g - i), std::min(T, a - j), g - i, 1.f, 0.f);
   }
   b.end_phase(1, first, b.task_begin() - first);
@@ -864,11 +879,11 @@ static Plan* build_sample(int n, const int64_t* dA, const int64_t* dG, float* co
     const int wcols = bias ? a - 1 : a;
     for (int i = 0; i < g; i += T) {
       for (int j = 0; j < wcols; j += T)
-        b.gemm(tmp[l] + (int64_t)i * a, a, false, U_A[l] + j, a, false,
+        b.gemm(tmp[l] + (int64_t)i * a, a, false, U_A[l] + j, ldA ? (int)ldA[l] : a, false,
                w[l] + (int64_t)i * wcols + j, wcols, std::min(T, g - i), std::min(T, wcols - j),
                std::min(a, j + T), 1.f, 1.f);
       if (bias)
-        b.gemm(tmp[l] + (int64_t)i * a, a, false, U_A[l] + wcols, a, false, bvec[l] + i, 1,
+        b.gemm(tmp[l] + (int64_t)i * a, a, false, U_A[l] + wcols, ldA ? (int)ldA[l] : a, false, bvec[l] + i, 1,
                std::min(T, g - i), 1, a, 1.f, 1.f);
     }
   }
@@ -884,9 +899,9 @@ size_t sso_sample_plan_dev_bytes(int n_layers, const int64_t* dA, const int64_t*
 int64_t sso_sample_plan_create(int n_layers, const int64_t* dA, const int64_t* dG, float* const* U_A,
                                float* const* U_G, float* const* noise, float* const* w,
                                float* const* b, float* const* tmp, void* dev_mem,
-                               size_t dev_mem_bytes, int host_only) {
+                               size_t dev_mem_bytes, int host_only, const int64_t* ldA, const int64_t* ldG) {
   SSO_CHECK_ARG(n_layers > 0 && dA && dG && U_A && U_G && noise && w && tmp, "sample plan: null argument");
-  Plan* p = build_sample(n_layers, dA, dG, U_A, U_G, noise, w, b, tmp);
+  Plan* p = build_sample(n_layers, dA, dG, U_A, U_G, noise, w, b, tmp, ldA, ldG);
   p->host_only = host_only != 0;
   if (!p->host_only) {
     const int rc = upload(*p, dev_mem, dev_mem_bytes);

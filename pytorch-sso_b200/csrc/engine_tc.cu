@@ -447,11 +447,14 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_kc_kernel(const sso_tile
         const uint32_t off = (uint32_t)(j & 3) * 4096u + (uint32_t)(j >> 2) * OPB;
         float4 v;
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(hi + off) : "memory");
-        // raw word = hi (the MMA ignores the low 13 mantissa bits), lo = what that truncation drops
-        const uint32_t h0 = __float_as_uint(v.x) & 0xFFFFE000u, h1 = __float_as_uint(v.y) & 0xFFFFE000u;
-        const uint32_t h2 = __float_as_uint(v.z) & 0xFFFFE000u, h3 = __float_as_uint(v.w) & 0xFFFFE000u;
+        // hi is rounded to nearest and written back in place.  Leaving the raw word as hi (the MMA
+        // reads only its top 19 bits) saves this store and 10-15 % of the kernel, but a truncated hi
+        // doubles |lo| and makes the dropped lo*lo term one-signed: on ill-conditioned factors the
+        // preconditioned gradient then misses the 1e-4 bound (3.7e-4 measured against 2e-4).
+        const uint32_t h0 = rna_tf32(v.x), h1 = rna_tf32(v.y), h2 = rna_tf32(v.z), h3 = rna_tf32(v.w);
         const uint32_t l0 = __float_as_uint(v.x - __uint_as_float(h0)), l1 = __float_as_uint(v.y - __uint_as_float(h1));
         const uint32_t l2 = __float_as_uint(v.z - __uint_as_float(h2)), l3 = __float_as_uint(v.w - __uint_as_float(h3));
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(hi + off), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(lo + off), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
       }
       fence_async_smem();
@@ -473,7 +476,7 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_kc_kernel(const sso_tile
 // TMA-fed variant of the k-contiguous kernel: the two operand boxes of a stage (128 rows x 32 k,
 // fp32) are fetched by one thread with cp.async.bulk.tensor into the raw ring (tensor maps made
 // on the host when the plan is built, two per task), so the loads no longer pass through the
-// load/store units.  The load warps only compute lo = x - trunc(x) into the second ring; the raw tile is the hi operand.
+// load/store units.  The load warps only split: hi in place, lo into the second ring.
 // ------------------------------------------------------------------------------------------
 struct alignas(128) TaskMaps {
   unsigned char a[128];
@@ -580,13 +583,14 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tma_kernel(const sso_til
         const uint32_t off = (uint32_t)(j & 3) * 4096u + (uint32_t)(j >> 2) * OPB;
         float4 v;
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(hi + off) : "memory");
-        // the raw fp32 word serves as hi: a kind::tf32 MMA reads the top 19 bits of each operand
-        // word and ignores the rest (checked numerically: inverse residual 3e-6 with this split,
-        // 2e-6 with an explicit round-to-nearest hi), so only lo = x - trunc(x) has to be stored
-        const uint32_t h0 = __float_as_uint(v.x) & 0xFFFFE000u, h1 = __float_as_uint(v.y) & 0xFFFFE000u;
-        const uint32_t h2 = __float_as_uint(v.z) & 0xFFFFE000u, h3 = __float_as_uint(v.w) & 0xFFFFE000u;
+        // hi is rounded to nearest and written back in place.  Leaving the raw word as hi (the MMA
+        // reads only its top 19 bits) saves this store and 10-15 % of the kernel, but a truncated hi
+        // doubles |lo| and makes the dropped lo*lo term one-signed: on ill-conditioned factors the
+        // preconditioned gradient then misses the 1e-4 bound (3.7e-4 measured against 2e-4).
+        const uint32_t h0 = rna_tf32(v.x), h1 = rna_tf32(v.y), h2 = rna_tf32(v.z), h3 = rna_tf32(v.w);
         const uint32_t l0 = __float_as_uint(v.x - __uint_as_float(h0)), l1 = __float_as_uint(v.y - __uint_as_float(h1));
         const uint32_t l2 = __float_as_uint(v.z - __uint_as_float(h2)), l3 = __float_as_uint(v.w - __uint_as_float(h3));
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(hi + off), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
         asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(lo + off), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
       }
       fence_async_smem();

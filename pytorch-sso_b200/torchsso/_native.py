@@ -42,7 +42,7 @@ class DiagRec(C.Structure):
 
 class CopyRec(C.Structure):
     _fields_ = [('src', c_vp), ('dst', c_vp), ('d', C.c_int32), ('row0', C.c_int32),
-                ('nrows', C.c_int32), ('mat', C.c_int32), ('mode', C.c_int32), ('pad', C.c_int32)]
+                ('nrows', C.c_int32), ('mat', C.c_int32), ('mode', C.c_int32), ('ld', C.c_int32)]
 
 
 class Phase(C.Structure):
@@ -75,13 +75,13 @@ SIGNATURES = {
     'sso_tri_unpack': (c_i32, [c_vp, c_i32, c_f32, c_i32, c_vp]),
     'sso_copy_segments': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
     'sso_kron_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_i32]),
-    'sso_kron_plan_create': (c_i64, [c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_i32]),
+    'sso_kron_plan_create': (c_i64, [c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_i32, c_vp]),
     'sso_kron_plan_run': (c_i32, [c_i64, c_vp, c_vp, c_i32, c_i32, c_vp]),
     'sso_precond_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_vp]),
-    'sso_precond_plan_create': (c_i64, [c_i32] + [c_vp] * 8 + [c_sz, c_i32]),
+    'sso_precond_plan_create': (c_i64, [c_i32] + [c_vp] * 8 + [c_sz, c_i32, c_vp, c_vp]),
     'sso_precond_plan_run': (c_i32, [c_i64, c_vp]),
     'sso_sample_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_vp]),
-    'sso_sample_plan_create': (c_i64, [c_i32] + [c_vp] * 9 + [c_sz, c_i32]),
+    'sso_sample_plan_create': (c_i64, [c_i32] + [c_vp] * 9 + [c_sz, c_i32, c_vp, c_vp]),
     'sso_sample_plan_run': (c_i32, [c_i64, c_f32, c_vp]),
     'sso_plan_destroy': (c_i32, [c_i64]),
     'sso_plan_status': (c_i32, [c_i64]),
@@ -512,7 +512,24 @@ class Plan:
         return arr, n
 
 
-def kron_plan(dims, src, dst, work, std, partner, role, device, host_only=False) -> Plan:
+def _lds(*lists):
+    """Leading dimensions (row strides) shared by the matrices at the same position of every list,
+    or None when the entries are raw addresses (dense matrices assumed)."""
+    first = lists[0]
+    if not all(isinstance(m, torch.Tensor) for lst in lists if lst is not None for m in lst):
+        return None
+    out = []
+    for i, m in enumerate(first):
+        ld = m.stride(0) if m.dim() == 2 and m.shape[0] > 1 else m.shape[-1]
+        for lst in lists[1:]:
+            if lst is not None:
+                o = lst[i]
+                assert o.stride(-1) == 1 and (o.shape[0] == 1 or o.stride(0) == ld), 'matrices of one factor must share their leading dimension'
+        out.append(ld)
+    return _i64(out)
+
+
+def kron_plan(dims, src, dst, work, std, partner, role, device, host_only=False, lds=None) -> Plan:
     L = lib()
     n = len(dims)
     d = _i64(dims)
@@ -530,7 +547,7 @@ def kron_plan(dims, src, dst, work, std, partner, role, device, host_only=False)
         mem_ptr = mem.data_ptr()
     h = L.sso_kron_plan_create(n, d, _ptrs(src), _ptrs(dst), _ptrs(work),
                                None if std is None else _ptrs(std), _i32(partner), _i32(role),
-                               mem_ptr, nbytes, int(host_only))
+                               mem_ptr, nbytes, int(host_only), _i64(lds) if lds is not None else _lds(src, dst, work, std))
     plan = Plan(h, mem, (src, dst, work, std, host_mem))
     plan.host_mem = host_mem
     return plan
@@ -549,7 +566,7 @@ def precond_plan(dA, dG, A_inv, G_inv, gw, gb, tmp, device, host_only=False) -> 
     nbytes = L.sso_precond_plan_dev_bytes(n, a, g)
     mem = None if host_only else torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
     h = L.sso_precond_plan_create(n, a, g, _ptrs(A_inv), _ptrs(G_inv), _ptrs(gw), _ptrs(gb), _ptrs(tmp),
-                                  _ptr(mem), nbytes, int(host_only))
+                                  _ptr(mem), nbytes, int(host_only), _lds(A_inv), _lds(G_inv))
     return Plan(h, mem, (A_inv, G_inv, gw, gb, tmp))
 
 
@@ -564,7 +581,7 @@ def sample_plan(dA, dG, U_A, U_G, noise, w, b, tmp, device, host_only=False) -> 
     nbytes = L.sso_sample_plan_dev_bytes(n, a, g)
     mem = None if host_only else torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
     h = L.sso_sample_plan_create(n, a, g, _ptrs(U_A), _ptrs(U_G), _ptrs(noise), _ptrs(w), _ptrs(b),
-                                 _ptrs(tmp), _ptr(mem), nbytes, int(host_only))
+                                 _ptrs(tmp), _ptr(mem), nbytes, int(host_only), _lds(U_A), _lds(U_G))
     return Plan(h, mem, (U_A, U_G, noise, w, b, tmp))
 
 

@@ -31,6 +31,14 @@ def _round_up(v: int, a: int = _ALIGN) -> int:
     return (v + a - 1) // a * a
 
 
+def _ld(d: int) -> int:
+    """Leading dimension of a d x d factor inside the pool: rows padded to a multiple of four floats,
+    so that every row starts on 16 bytes and the tile tasks that read the factor (inverse, std,
+    precondition, sampling) can fetch it with TMA / 16-byte loads even when d is odd (layers with a
+    bias).  The padding columns are zero and stay zero."""
+    return (d + 3) // 4 * 4
+
+
 class FactorPool:
 
     def __init__(self, kron: Sequence, diag: Sequence, device):
@@ -44,9 +52,9 @@ class FactorPool:
         for c in self.kron:
             (da, _), (dg, _) = c._get_shape()
             a_off = off
-            off = _round_up(off + da * da)
+            off = _round_up(off + da * _ld(da))
             g_off = off
-            off = _round_up(off + dg * dg)
+            off = _round_up(off + dg * _ld(dg))
             self.k_off[id(c)] = (a_off, da, g_off, dg)
         self.k_total = off
         # --- diagonal layout: parameters of each layer back to back, layers back to back
@@ -81,7 +89,9 @@ class FactorPool:
     def mat(self, role: str, curv, which: int) -> torch.Tensor:
         a_off, da, g_off, dg = self.k_off[id(curv)]
         off, d = (a_off, da) if which == 0 else (g_off, dg)
-        return self.buf(role)[off: off + d * d].view(d, d)
+        ld = _ld(d)
+        m = self.buf(role)[off: off + d * ld].view(d, ld)
+        return m if ld == d else m[:, :d]
 
     def vec(self, role: str, curv, j: int) -> torch.Tensor:
         off, shape = self.d_off[id(curv)][j]
@@ -216,7 +226,8 @@ class FactorPool:
                 A_inv.append(a); G_inv.append(g)
                 gw.append(gs[0]); gb.append(gs[1] if has_b else None)
                 # scratch: the A-slot of `work` is dA*dA >= ... not always >= dG*dA; own buffer
-                tmp.append(torch.empty(g.shape[0] * a.shape[0], dtype=torch.float32, device=self.device))
+                # [d_A x d_G] with the leading dimension of G_inv
+                tmp.append(torch.empty(a.shape[0] * max(g.stride(0), g.shape[0]), dtype=torch.float32, device=self.device))
             plan = nat.precond_plan(dA, dG, A_inv, G_inv, gw, gb, tmp, self.device)
             self._trim_plans()
             self._plans[key] = plan

@@ -79,15 +79,15 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
                     mem.view(r.LinvT, r.size, r.size, r.ld_invt)[...] = Linv.T
         elif kind == 3:
             for r in [copies[i] for i in range(first, first + count)]:
-                dst = mem.view(r.dst, r.d, r.d, r.d)
+                dst = mem.view(r.dst, r.d, r.d, r.ld)
                 rows = slice(r.row0, r.row0 + r.nrows)
                 if r.mode == 2:
                     dst[rows] = 0
                 elif r.mode == 1:
-                    src = mem.view(r.src, r.d, r.d, r.d)
+                    src = mem.view(r.src, r.d, r.d, r.ld)
                     dst[rows] = np.triu(np.tril(src).T)[rows]
                 else:
-                    src = mem.view(r.src, r.d, r.d, r.d)
+                    src = mem.view(r.src, r.d, r.d, r.ld)
                     dst[rows] = src[rows]
                     if r.mat >= 0:
                         for i in range(r.row0, r.row0 + r.nrows):
@@ -142,6 +142,40 @@ def test_kron_inverse_and_std_program(dims):
         assert np.array_equal(U, np.triu(U))
         refU = np.linalg.cholesky(ref).T
         assert np.linalg.norm(U - refU) / np.linalg.norm(refU) < 1e-3, (d, 'std')
+
+
+def test_kron_program_with_padded_leading_dimension():
+    """Matrices whose rows are padded to a multiple of four floats (what the factor pool does for
+    odd dimensions, so that every row starts on 16 bytes)."""
+    mem = Mem()
+    dims = [65, 201]
+    lds = [(d + 3) // 4 * 4 for d in dims]
+    src = [mem.new(d * l) for d, l in zip(dims, lds)]
+    dst = [mem.new(d * l) for d, l in zip(dims, lds)]
+    work = [mem.new(d * l) for d, l in zip(dims, lds)]
+    std = [mem.new(d * l) for d, l in zip(dims, lds)]
+    mats = []
+    for i, (d, l) in enumerate(zip(dims, lds)):
+        m = spd(d, 300 + i)
+        mats.append(m)
+        np.lib.stride_tricks.as_strided(src[i], shape=(d, d), strides=(4 * l, 4))[...] = m
+    plan = nat.kron_plan(dims, [a.ctypes.data for a in src], [a.ctypes.data for a in dst],
+                         [a.ctypes.data for a in work], [a.ctypes.data for a in std],
+                         [1, 0], [0, 1], device=None, host_only=True, lds=lds)
+    mem.bufs.append(plan.host_mem)
+    r = np.sqrt(1e-3)
+    ta, tg = np.trace(mats[0]) / dims[0], np.trace(mats[1]) / dims[1]
+    pi = np.sqrt(ta / tg)
+    shift = [r * pi, r / pi]
+    assert not run_program(plan, mem, shift=shift)
+    for i, (d, l) in enumerate(zip(dims, lds)):
+        inv = np.lib.stride_tricks.as_strided(dst[i], shape=(d, d), strides=(4 * l, 4))
+        ref = np.linalg.inv(mats[i].astype(np.float64) + shift[i] * np.eye(d))
+        assert np.linalg.norm(inv - ref) / np.linalg.norm(ref) < 1e-4
+        assert np.array_equal(inv, inv.T)
+        U = np.lib.stride_tricks.as_strided(std[i], shape=(d, d), strides=(4 * l, 4))
+        refU = np.linalg.cholesky(ref).T
+        assert np.linalg.norm(U - refU) / np.linalg.norm(refU) < 1e-3
 
 
 def test_kron_program_reports_bad_pivot():
