@@ -167,6 +167,22 @@ typedef struct {
 } sso_seg_rec;
 int sso_copy_segments(const sso_seg_rec* recs_dev, int n_recs, float scale, void* stream);
 
+/* Diagonal curvature of Linear / Conv2d layers: mean over samples of the squared per-sample weight
+ * gradient (torchsso/curv/cov/linear.py:28-45, torchsso/curv/cov/conv.py:15-42; the reference builds
+ * it from F.unfold + a batched matmul + elementwise squares):
+ *     out_w[o][j] <- alpha * sum_b w_b * ( sum_l g[b,o,l] * u[b,l,j] )^2 + beta * out_w[o][j]
+ *     out_b[o]    <- alpha * sum_b w_b *   sum_l g[b,o,l]^2              + beta * out_b[o]   (out_b nullable)
+ * x [n,c,h,w] and g [n,oc,ho,wo] with element strides; a Linear layer is h = w = 1 with a 1x1 kernel;
+ * j runs over (c, ky, kx) like the weight itself.  Exact fp32 accumulation. */
+size_t sso_diag_sq_workspace_bytes(int64_t n, int64_t oc, int64_t d);
+int sso_diag_sq_im2col(const void* x, const void* g, int dtype, int64_t n, int64_t c, int64_t h, int64_t w,
+                       int64_t sxn, int64_t sxc, int64_t sxh, int64_t sxw, int64_t oc,
+                       int64_t sgn, int64_t sgc, int64_t sgh, int64_t sgw,
+                       int kh, int kw, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                       const float* sample_weight /* [n] or NULL */, float alpha, float beta,
+                       float* out_w /* [oc][c*kh*kw] */, float* out_b /* [oc] or NULL */,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* Optimizer tail over a table of parameter chunks: weight decay / l2, momentum, gradient moving
  * average, bias-correction scale and the parameter update in one launch
  * (replaces the per-group multi-tensor chains of torchsso/optim/secondorder.py:225-283,

@@ -134,6 +134,29 @@ def bn_diag(xhat: Tensor, g: Tensor, prob: Optional[Tensor] = None,
 # --------------------------------------------------------------------------
 # EMA, damping, inverse
 # --------------------------------------------------------------------------
+def diag_linear(x: Tensor, g: Tensor, prob: Optional[Tensor] = None):
+    """Diagonal curvature of a Linear layer (torchsso/curv/cov/linear.py:28-45; with `prob` the
+    Fisher weighting of torchsso/curv/fisher/linear.py:11-32): mean over samples of g^2 (x) x^2 and
+    of g^2.  Returns (weight part [f_out, f_in], bias part [f_out]), before the n^2 rescale."""
+    n = x.shape[0]
+    gg = g * g if prob is None else g * g * prob.reshape(n, 1)
+    return gg.t() @ (x * x) / n, gg.mean(dim=0)
+
+
+def diag_conv(x: Tensor, g: Tensor, kernel_size, stride, padding, dilation, prob: Optional[Tensor] = None):
+    """Diagonal curvature of a Conv2d layer (torchsso/curv/cov/conv.py:15-42): mean over samples of
+    the squared per-sample weight gradient; bias part: mean over samples of the pixel sum of g^2.
+    Returns (weight part [c_out, c_in, kh, kw], bias part [c_out]), before the n^2 rescale."""
+    n, c_out = g.shape[0], g.shape[1]
+    g2 = g.reshape(n, c_out, -1)
+    rows = unfold_rows(x, kernel_size, stride, padding, dilation).reshape(n, g2.shape[2], -1)  # n, L, c_in*kh*kw
+    per = torch.einsum('bik,bkj->bij', g2, rows)                          # per-sample gradients
+    sq = per * per if prob is None else per * per * prob.reshape(n, 1, 1)
+    gg = g2 * g2 if prob is None else g2 * g2 * prob.reshape(n, 1, 1)
+    kh, kw = _pair(kernel_size)
+    return sq.mean(dim=0).reshape(c_out, -1, kh, kw), gg.sum(dim=2).mean(dim=0)
+
+
 def ema_update(data: Tensor, ema: Optional[Tensor], beta: float) -> Tensor:
     """ema <- data on the first call or when beta == 1, else beta*data + (1-beta)*ema
     (beta weights the NEW data).  torchsso/curv/curvature.py:174-191."""

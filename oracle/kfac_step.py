@@ -36,6 +36,8 @@ class _Layer:
         self.params = list(module.parameters())
         self.is_bn = isinstance(module, (nn.BatchNorm1d, nn.BatchNorm2d))
         self.is_conv = isinstance(module, nn.Conv2d)
+        self.is_diag = self.is_bn    # BatchNorm is always diagonal; Linear / Conv2d on request
+        self.x = None
         self.has_bias = getattr(module, 'bias', None) is not None
         self.data: Optional[List[torch.Tensor]] = None      # Kron: [A, G]; Diag: [w(, b)]
         self.A = None
@@ -55,7 +57,10 @@ class OracleKFAC:
 
     def __init__(self, model: nn.Module, curv_type: str = 'Fisher', ema_decay: float = 1.0,
                  damping: float = 1e-7, lr: float = 0.01, momentum: float = 0.0,
-                 l2_reg: float = 0.0, weight_decay: float = 0.0, acc_steps: int = 1):
+                 l2_reg: float = 0.0, weight_decay: float = 0.0, acc_steps: int = 1,
+                 diag: tuple = ()):
+        """``diag``: class names ('Linear', 'Conv2d') that get the diagonal curvature of
+        torchsso/curv/cov/linear.py:28-45 / cov/conv.py:15-42 instead of the Kronecker one."""
         assert curv_type in ('Cov', 'Fisher')
         self.model = model
         self.curv_type = curv_type
@@ -78,6 +83,7 @@ class OracleKFAC:
             if not isinstance(m, (nn.Linear, nn.Conv2d, nn.BatchNorm1d, nn.BatchNorm2d)):
                 raise AssertionError('no curvature for %s' % type(m).__name__)
             L = _Layer(m)
+            L.is_diag = L.is_bn or type(m).__name__ in diag
             self.layers.append(L)
             m.register_forward_hook(self._make_fwd(L))
 
@@ -89,6 +95,8 @@ class OracleKFAC:
                 # curvature.py:123-134
                 L.xhat = ko.bn_restore_input(output.detach(), module.weight.detach(),
                                              module.bias.detach())
+            elif L.is_diag:
+                L.x = x
             elif L.is_conv:
                 L.A = ko.conv_factor_A(x, module.kernel_size, module.stride, module.padding,
                                        module.dilation, L.has_bias)
@@ -111,6 +119,14 @@ class OracleKFAC:
             p = self.prob if fisher else None
             if L.is_bn:
                 new = ko.bn_diag(L.xhat, g, p, L.has_bias)
+            elif L.is_diag:
+                m = L.module
+                if L.is_conv:
+                    new = list(ko.diag_conv(L.x, g, m.kernel_size, m.stride, m.padding, m.dilation, p))
+                else:
+                    new = list(ko.diag_linear(L.x, g, p))
+                    new[0] = new[0].reshape(m.weight.shape)
+                new = new if L.has_bias else new[:1]
             elif L.is_conv:
                 new = [ko.conv_factor_G(g, p)]
             else:
@@ -119,7 +135,7 @@ class OracleKFAC:
                 # accumulate UNSCALED; the scale below touches only the per-pass copy
                 L.acc = new if L.acc is None else [a + b for a, b in zip(L.acc, new)]
         scale = float(n * n)
-        if L.is_bn:
+        if L.is_diag:
             L.data = [d * scale for d in new]
         else:
             L.data = [L.A, new[0] * scale]
@@ -209,13 +225,13 @@ class OracleKFAC:
         if not self.update_inv:
             return
         damping = self.damping + L.l2_reg_ema
-        if L.is_bn:
+        if L.is_diag:
             L.inv = [ko.diag_inverse(e, damping) for e in L.ema]
         else:
             L.inv = list(ko.kron_damped_inverse(L.ema[0], L.ema[1], damping))
 
     def precondition(self, L: _Layer):
-        if L.is_bn:
+        if L.is_diag:
             for p, inv in zip(L.params, L.inv):
                 p.grad.copy_(inv * p.grad)
             return

@@ -108,6 +108,28 @@ def suite_rows(args):
              input_gbs=round(4.0 * rows * d / ms / 1e6, 1))
 
 
+# (n, c, h, w, oc, k, stride, pad): convolutions of the VGG / ResNet configurations, and two Linear
+# layers written as 1x1 convolutions over one pixel
+DIAG_CASES = [(128, 64, 32, 32, 64, 3, 1, 1), (128, 256, 8, 8, 256, 3, 1, 1), (32, 64, 56, 56, 64, 3, 1, 1),
+              (32, 256, 14, 14, 256, 3, 1, 1), (128, 512, 1, 1, 10, 1, 1, 0), (128, 4096, 1, 1, 1000, 1, 1, 0)]
+
+
+def suite_diag(args):
+    """Squared per-sample gradient kernel (diagonal curvature of Linear / Conv2d): exact fp32 FFMA,
+    2 * n * L * oc * d flops per launch."""
+    for i, (n, c, h, w, oc, k, s, p) in select(DIAG_CASES, args.case):
+        g = torch.Generator(device='cuda').manual_seed(i)
+        ho, wo = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+        x = torch.randn((n, c, h, w), device='cuda', generator=g).bfloat16().contiguous(memory_format=torch.channels_last)
+        go = torch.randn((n, oc, ho, wo), device='cuda', generator=g).bfloat16().contiguous(memory_format=torch.channels_last)
+        d = c * k * k
+        ow, ob = torch.empty((oc, d), device='cuda'), torch.empty((oc,), device='cuda')
+        ms = timeit(lambda: nat.diag_sq(x, go, (k, k), (s, s), (p, p), (1, 1), None, 1.0 / n, 0.0, ow, ob), args.iters)
+        fl = 2.0 * n * ho * wo * oc * d
+        emit(suite='diag', case=i, dtype='bf16 in, fp32 math', n=n, c=c, hw=[h, w], oc=oc, k=k, ms=round(ms, 4),
+             tflops=round(fl / ms / 1e9, 2))
+
+
 def spd(d, seed):
     g = torch.Generator(device='cuda').manual_seed(seed)
     x = torch.randn((4 * d, d), device='cuda', generator=g)
@@ -351,7 +373,7 @@ def suite_collective(args):
     dist.destroy_process_group()
 
 
-SUITES = {'peaks': suite_peaks, 'steps': suite_steps, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
+SUITES = {'diag': suite_diag, 'peaks': suite_peaks, 'steps': suite_steps, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
           'stream': suite_stream, 'collective': suite_collective}
 
 

@@ -95,6 +95,9 @@ SIGNATURES = {
     'sso_plan_copy_copy_recs': (c_i32, [c_i64, c_vp, c_i32]),
     'sso_run_tile_tasks': (c_i32, [c_vp, c_i32, c_i32, c_vp]),
     'sso_optimizer_tail': (c_i32, [c_vp, c_i32, c_vp]),
+    'sso_diag_sq_workspace_bytes': (c_sz, [c_i64, c_i64, c_i64]),
+    'sso_diag_sq_im2col': (c_i32, [c_vp, c_vp, c_i32] + [c_i64] * 8 + [c_i64] * 5 + [c_i32] * 8 +
+                           [c_vp, c_f32, c_f32, c_vp, c_vp, c_vp, c_sz, c_vp]),
 }
 
 
@@ -363,6 +366,34 @@ def bn_plane_sums(t: torch.Tensor, is_output: bool, scale, shift, out: torch.Ten
 def bn_diag_finish(sx, sg, sample_weight, n, c, splits_x, splits_g, alpha, beta, w_out, b_out):
     _check(lib().sso_bn_diag_finish(sx.data_ptr(), sg.data_ptr(), _ptr(sample_weight), n, c, splits_x,
                                     splits_g, alpha, beta, w_out.data_ptr(), _ptr(b_out), _stream()))
+
+
+def diag_sq(x: torch.Tensor, g: torch.Tensor, kernel_size, stride, padding, dilation,
+            sample_weight: Optional[torch.Tensor], alpha: float, beta: float,
+            out_w: torch.Tensor, out_b: Optional[torch.Tensor]):
+    """out_w <- alpha * sum_b w_b (per-sample weight gradient of sample b)^2 + beta * out_w (and the
+    same for the bias) for a convolution with input x [n,c,h,w] and output gradient g [n,oc,ho,wo];
+    a Linear layer passes x [n,f_in], g [n,f_out]."""
+    _require_cuda(x, 'layer input')
+    if x.dim() == 2:
+        x, g = x[:, :, None, None], g[:, :, None, None]
+        kernel_size, stride, padding, dilation = (1, 1), (1, 1), (0, 0), (1, 1)
+    if g.dtype != x.dtype:
+        x, g = x.float(), g.float()
+    n, c, h, w = x.shape
+    oc = g.shape[1]
+    d = c * kernel_size[0] * kernel_size[1]
+    assert out_w.is_contiguous() and out_w.dtype == torch.float32 and out_w.numel() == oc * d
+    assert out_b is None or (out_b.is_contiguous() and out_b.numel() == oc)
+    assert sample_weight is None or (sample_weight.dtype == torch.float32 and sample_weight.is_contiguous()
+                                     and sample_weight.numel() == n)
+    L = lib()
+    ws = workspace(x.device, L.sso_diag_sq_workspace_bytes(n, oc, d))
+    _check(L.sso_diag_sq_im2col(x.data_ptr(), g.data_ptr(), _dtype_code(x), n, c, h, w, *x.stride(), oc,
+                                *g.stride(), kernel_size[0], kernel_size[1], stride[0], stride[1],
+                                padding[0], padding[1], dilation[0], dilation[1], _ptr(sample_weight),
+                                alpha, beta, out_w.data_ptr(), _ptr(out_b), _ptr(ws),
+                                0 if ws is None else ws.numel(), _stream()))
 
 
 def ema_update(data: torch.Tensor, ema: torch.Tensor, beta: float, first: bool):

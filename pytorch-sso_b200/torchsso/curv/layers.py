@@ -307,22 +307,19 @@ class DiagFisherBatchNorm2d(DiagCovBatchNorm2d, Fisher):
 
 
 # ---------------------------------------------------------------------------------------------
-# diagonal Linear / Conv2d (not accelerated: torch device ops)
+# diagonal Linear / Conv2d: mean over samples of the squared per-sample gradient
 # ---------------------------------------------------------------------------------------------
-class _DiagTorch(DiagCurvature):
+class _DiagSq(DiagCurvature):
+    """torchsso/curv/cov/linear.py:28-45 and torchsso/curv/cov/conv.py:15-42 (the Fisher variants
+    weight each sample by its probability, torchsso/curv/fisher/linear.py:11-32): one launch of
+    the fused kernel per backward pass; the im2col matrix and the per-sample gradients are never
+    materialised."""
 
-    def _store(self, new, scale):
-        fisher = isinstance(self, Fisher)
-        views = self._views('data')
-        first = not (fisher and self._passes > 0)
-        for v, t in zip(views, new):
-            if first:
-                v.copy_(t * scale)
-            else:
-                v.add_(t * scale)
-        if fisher:
-            self._passes += 1
-        self._have.add('data')
+    def _geometry(self):
+        raise NotImplementedError
+
+    def _operands(self, x, g):
+        return x, g
 
     def update_in_backward(self, g):
         fisher = isinstance(self, Fisher)
@@ -331,38 +328,37 @@ class _DiagTorch(DiagCurvature):
         if fisher and not self.do_backward:
             self._passes = 0
             return
+        x, g = self._operands(self._module.data_input, g)
         n = g.shape[0]
         p, ws = _weights(self, n, g.device)
-        self._store(self._per_sample_sq(g.float(), p), ws * float(n) * float(n))
+        views = self._views('data')
+        first = not (fisher and self._passes > 0)
+        # mean over samples, then the n^2 that undoes the mean reduction of the loss
+        nat.diag_sq(x, g, *self._geometry(), p, ws * float(n), 0.0 if first else 1.0,
+                    views[0], views[1] if self.bias else None)
+        if fisher:
+            self._passes += 1
+        self._have.add('data')
 
 
-class DiagCovLinear(_DiagTorch):
+class DiagCovLinear(_DiagSq):
 
-    def _per_sample_sq(self, g, p):
-        x = self._module.data_input.float()
-        n = x.shape[0]
-        gg = g * g if p is None else g * g * p.reshape(n, 1)
-        out = [gg.t() @ (x * x) / n]
-        if self.bias:
-            out.append(gg.mean(dim=0))
-        return out
+    def _geometry(self):
+        return (1, 1), (1, 1), (0, 0), (1, 1)
+
+    def _operands(self, x, g):
+        if x.dim() != 2:        # [.., f_in]: every leading index is a sample
+            x, g = x.reshape(-1, x.shape[-1]), g.reshape(-1, g.shape[-1])
+        return x, g
 
 
-class DiagCovConv2d(_DiagTorch):
+class DiagCovConv2d(_DiagSq):
 
-    def _per_sample_sq(self, g, p):
+    def _geometry(self):
         m = self._module
-        x = self._module.data_input.float()
-        cols = F.unfold(x, m.kernel_size, m.dilation, m.padding, m.stride)   # n, ckk, L
-        n, c_out = g.shape[0], g.shape[1]
-        g2 = g.reshape(n, c_out, -1)
-        per = torch.einsum('bik,bjk->bij', g2, cols)                         # n, c_out, ckk
-        sq = per * per if p is None else per * per * p.reshape(n, 1, 1)
-        out = [sq.mean(dim=0).reshape(m.weight.shape)]
-        if self.bias:
-            gg = g2 * g2 if p is None else g2 * g2 * p.reshape(n, 1, 1)
-            out.append(gg.sum(dim=2).mean(dim=0))
-        return out
+        if m.groups != 1 or isinstance(m.padding, str):
+            raise NotImplementedError('grouped / string-padded convolutions have no diagonal curvature here')
+        return m.kernel_size, m.stride, m.padding, m.dilation
 
 
 class DiagFisherLinear(DiagCovLinear, Fisher):

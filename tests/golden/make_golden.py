@@ -128,6 +128,41 @@ def case_tiny_convnet_fisher_exact(torchsso):
     return out
 
 
+DIAG = {'Linear': 'Diag', 'Conv2d': 'Diag', 'BatchNorm1d': 'Diag', 'BatchNorm2d': 'Diag'}
+
+
+def case_tiny_convnet_diag(torchsso):
+    """Diagonal curvature for every layer: two Fisher (MC) steps, then on a fresh model two
+    empirical-covariance steps."""
+    out = {}
+    model = cases.make_model('tiny_convnet', seed=4)
+    opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
+        model, 'Fisher', DIAG, {'ema_decay': 0.9, 'damping': 1e-3}, lr=1e-2))
+    for t in range(2):
+        x, y = cases.make_batch((6, 3, 8, 8), 5, seed=500 + t)
+        STATE['u'] = cases.make_uniform((2, 6), seed=600 + t)
+        closure = torchsso.get_closure_for_fisher(opt, model, x, y, approx_type='mc', num_mc=2)
+        loss, _ = opt.step(closure=closure)
+        out['fisher%d/loss' % t] = np.float64(loss.item())
+        dump_groups(out, 'fisher%d' % t, opt)
+    model = cases.make_model('tiny_convnet', seed=5)
+    opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
+        model, 'Cov', DIAG, {'ema_decay': 0.9, 'damping': 1e-3}, lr=1e-2))
+    for t in range(2):
+        x, y = cases.make_batch((6, 3, 8, 8), 5, seed=700 + t)
+
+        def closure():
+            opt.zero_grad()
+            o = model(x)
+            loss = F.cross_entropy(o, y)
+            loss.backward()
+            return loss, o
+        loss, _ = opt.step(closure=closure)
+        out['cov%d/loss' % t] = np.float64(loss.item())
+        dump_groups(out, 'cov%d' % t, opt)
+    return out
+
+
 def case_small_mlp_cov(torchsso):
     model = cases.make_model('small_mlp', seed=3)
     opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
@@ -206,6 +241,7 @@ CASES = OrderedDict([
     ('tiny_convnet_fisher', case_tiny_convnet_fisher),
     ('tiny_convnet_fisher_exact', case_tiny_convnet_fisher_exact),
     ('small_mlp_cov', case_small_mlp_cov),
+    ('tiny_convnet_diag', case_tiny_convnet_diag),
     ('tiny_vgg_vi', case_tiny_vgg_vi),
     ('mnist_mlp_fisher', case_mnist_mlp_fisher),
 ])

@@ -568,3 +568,43 @@ def test_optimizer_tail_matches_torch(nat):
             assert rel(m, rm) < 1e-6
         if e is not None:
             assert rel(e, re) < 1e-6
+
+
+# ------------------------------------------------------------------ diagonal Linear / Conv2d
+@pytest.mark.parametrize('n,fi,fo,weighted', [(12, 37, 10, False), (128, 200, 130, True), (5, 64, 64, False)])
+def test_diag_sq_linear_matches_oracle(nat, n, fi, fo, weighted):
+    x = cases.make_normal((n, fi), 801)
+    g = cases.make_normal((n, fo), 802) * 0.1
+    prob = cases.make_uniform((n,), 803).float() if weighted else None
+    rw, rb = ko.diag_linear(x.double(), g.double(), None if prob is None else prob.double())
+    out_w = torch.full((fo, fi), float('nan'), device='cuda')
+    out_b = torch.full((fo,), float('nan'), device='cuda')
+    nat.diag_sq(dev(x), dev(g), None, None, None, None, None if prob is None else dev(prob), 1.0 / n, 0.0, out_w, out_b)
+    assert rel(out_w, rw) < FACTOR_TOL and rel(out_b, rb) < FACTOR_TOL
+    # accumulate (beta = 1) doubles the result
+    nat.diag_sq(dev(x), dev(g), None, None, None, None, None if prob is None else dev(prob), 1.0 / n, 1.0, out_w, out_b)
+    assert rel(out_w, 2 * rw) < FACTOR_TOL and rel(out_b, 2 * rb) < FACTOR_TOL
+
+
+@pytest.mark.parametrize('cfg', [
+    (4, 3, 8, 8, 6, (3, 3), (1, 1), (1, 1), (1, 1)),
+    (3, 16, 9, 7, 70, (3, 3), (2, 2), (1, 1), (1, 1)),
+    (2, 8, 12, 12, 5, (5, 3), (1, 1), (2, 1), (1, 2)),
+    (6, 32, 6, 6, 33, (1, 1), (1, 1), (0, 0), (1, 1)),
+])
+@pytest.mark.parametrize('channels_last,dtype', [(False, torch.float32), (True, torch.float32), (True, torch.bfloat16)])
+def test_diag_sq_conv_matches_oracle(nat, cfg, channels_last, dtype):
+    n, c, h, w, oc, k, s, p, d = cfg
+    x = cases.make_normal((n, c, h, w), 811 + c).to(dtype)
+    ho = (h + 2 * p[0] - d[0] * (k[0] - 1) - 1) // s[0] + 1
+    wo = (w + 2 * p[1] - d[1] * (k[1] - 1) - 1) // s[1] + 1
+    g = (cases.make_normal((n, oc, ho, wo), 812 + oc) * 0.1).to(dtype)
+    prob = cases.make_uniform((n,), 813).float()
+    rw, rb = ko.diag_conv(x.double(), g.double(), k, s, p, d, prob.double())
+    xd, gd = dev(x), dev(g)
+    if channels_last:
+        xd, gd = xd.contiguous(memory_format=torch.channels_last), gd.contiguous(memory_format=torch.channels_last)
+    out_w = torch.full((oc, c, k[0], k[1]), float('nan'), device='cuda')
+    out_b = torch.full((oc,), float('nan'), device='cuda')
+    nat.diag_sq(xd, gd, k, s, p, d, dev(prob), 1.0 / n, 0.0, out_w, out_b)
+    assert rel(out_w, rw) < FACTOR_TOL and rel(out_b, rb) < FACTOR_TOL
