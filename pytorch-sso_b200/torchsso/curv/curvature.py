@@ -130,8 +130,15 @@ class Curvature(object):
         d['data_output'] = output.detach()   # detached: keeping the graph alive between steps would
                                              # pin last step's activations and autograd nodes
         nat.run_on_curvature_stream(self.update_in_forward, output.detach() if self._is_norm else x)
+        d.pop('output_edge', None)
         if output.requires_grad and torch.is_grad_enabled():
             output.register_hook(self._backward_hook)
+            if getattr(self, '_keep_output_edge', False):
+                # where the output gradient enters the autograd graph (taken now: a later
+                # in-place op would move the tensor to another node); the Fisher sampling passes
+                # ask for exactly these gradients and nothing else.  The closure takes it away
+                # again, so no graph stays alive between steps.
+                d['output_edge'] = torch.autograd.graph.get_gradient_edge(output)
 
     def _backward_hook(self, grad_output):
         self.backward_postprocess(self._module, None, (grad_output,))

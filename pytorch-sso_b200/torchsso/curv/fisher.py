@@ -1,7 +1,13 @@
 """Closure factory for Fisher curvatures (same protocol as
 torchsso/curv/fisher/__init__.py:34-90): forward once, then one extra backward pass per Monte
-Carlo target (or per class for the exact Fisher) with parameter gradients frozen so that only
-the curvature hooks see those passes, then the real backward for the loss gradient."""
+Carlo target (or per class for the exact Fisher) that only the curvature hooks see, then the
+real backward for the loss gradient.
+
+The reference freezes the parameters for the sampling passes (requires_grad = False after the
+forward), which still computes every weight gradient and drops it at the accumulation node.
+Here a sampling pass asks autograd for the output gradients of the hooked modules only
+(``prune_sampling_pass=True``, the default): the hooks see the same values, the weight-gradient
+kernels of those passes never run.  ``prune_sampling_pass=False`` is the reference's protocol."""
 from __future__ import annotations
 
 import torch
@@ -26,7 +32,8 @@ def sample_targets(prob: torch.Tensor, num_mc: int) -> torch.Tensor:
     return torch.multinomial(prob, num_mc, replacement=True).t()
 
 
-def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num_mc=1):
+def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num_mc=1,
+                           prune_sampling_pass=True):
 
     def set_sampling(on: bool):
         for group in optimizer.param_groups:
@@ -35,8 +42,15 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
                 curv.turn_on_backward()
             else:
                 curv.turn_off_backward()
-            for param in group['params']:
-                param.requires_grad = not on
+            if not prune_sampling_pass:
+                for param in group['params']:
+                    param.requires_grad = not on
+
+    def sampling_backward(loss, edges):
+        if prune_sampling_pass:
+            torch.autograd.grad(loss, edges, retain_graph=True, allow_unused=True)
+        else:
+            loss.backward(retain_graph=True)
 
     def closure():
         for group in optimizer.param_groups:
@@ -48,6 +62,15 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
         output = model(data)
         prob = F.softmax(output, dim=1)
 
+        edges = []
+        if prune_sampling_pass:
+            for group in optimizer.param_groups:
+                edge = group['curv'].module.__dict__.pop('output_edge', None)
+                if edge is not None:
+                    edges.append(edge)
+            if not edges:
+                raise RuntimeError('no hooked module produced an output that requires grad')
+
         set_sampling(True)
         if approx_type == _APPROX_TYPE_MC:
             mc_targets = sample_targets(prob.detach(), num_mc)
@@ -56,15 +79,16 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
                 group['curv'].prob = weight
                 group['curv'].prob_scale = 1.0 / num_mc
             for i in range(num_mc):
-                F.cross_entropy(output, mc_targets[i]).backward(retain_graph=True)
+                sampling_backward(F.cross_entropy(output, mc_targets[i]), edges)
         else:
             for i in range(model.num_classes):
                 weight = prob[:, i].detach().float().contiguous()
                 for group in optimizer.param_groups:
                     group['curv'].prob = weight
                     group['curv'].prob_scale = None
-                F.cross_entropy(output, torch.full_like(target, i)).backward(retain_graph=True)
+                sampling_backward(F.cross_entropy(output, torch.full_like(target, i)), edges)
         set_sampling(False)
+        del edges
 
         loss = F.cross_entropy(output, target)
         loss.backward()

@@ -33,6 +33,7 @@ class Fisher(object):
         self.prob_scale = None
         self._do_backward = True
         self._acc_cov = TensorAccumulator()
+        self._keep_output_edge = True     # the sampling passes ask autograd for the output gradient
 
     @property
     def do_backward(self):

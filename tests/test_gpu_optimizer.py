@@ -59,7 +59,10 @@ def check(gold, tag, opt, f_tol, i_tol, with_std=False, grad_floor=1e-30):
             assert rel(p.grad, gold['%s/g%d/grad%d' % (tag, gi, j)], grad_floor) < i_tol * 3, (tag, gi, 'grad', j)
 
 
-def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch):
+@pytest.mark.parametrize('prune', [True, False])
+def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch, prune):
+    """prune: the sampling passes ask autograd for the hooked output gradients only (default) or
+    run the reference's full backward with frozen parameters; same vectors either way."""
     torchsso = torchsso_mod
     gold = load('tiny_convnet_fisher')
     state = {}
@@ -71,8 +74,11 @@ def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch):
         x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100 + t)
         state['u'] = cases.make_uniform((2, 6), seed=200 + t)
         opt.update_inv = (t != 2)
-        closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2)
+        closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2,
+                                                  prune_sampling_pass=prune)
         loss, _ = opt.step(closure=closure)
+        for group in opt.param_groups:
+            assert 'output_edge' not in group['curv'].module.__dict__ or not prune
         opt.pool.check_info()
         g = float(gold['step%d/loss' % t])
         assert abs(loss.item() - g) <= 1e-3 * max(1.0, abs(g))
