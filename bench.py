@@ -290,6 +290,9 @@ def run_gpu_arm(args):
     x_static = torch.empty_like(resident[0][0])
     y_static = torch.empty_like(resident[0][1])
     x_static.copy_(resident[0][0]); y_static.copy_(resident[0][1])
+    # autograd assigns fresh gradient tensors instead of accumulating into the optimizer's flat buffer
+    # (one add kernel per parameter per backward pass); one multi-tensor copy harvests them
+    opt.zero_grad_to_none = (args.grads == 'assign')
     closure = fisher_closure(torchsso, opt, model, x_static, y_static)
     eager_closure = closure
     if args.graph:
@@ -445,6 +448,9 @@ def main():
     ap.add_argument('--no-sgd-baseline', action='store_true')
     ap.add_argument('--weights', default='contiguous', choices=['channels_last', 'contiguous'],
                     help='memory format of the convolution weights (activations are channels_last)')
+    ap.add_argument('--grads', default='assign', choices=['assign', 'accumulate'],
+                    help="zero_grad(): 'assign' sets .grad to None (autograd assigns, one harvest copy), "
+                         "'accumulate' binds .grad to the flat buffer (autograd adds in place)")
     ap.add_argument('--no-side-stream', dest='side_stream', action='store_false',
                     help='launch the curvature kernels of the hooks on the main stream')
     ap.add_argument('--no-graph', dest='graph', action='store_false',

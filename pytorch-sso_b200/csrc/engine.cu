@@ -298,10 +298,37 @@ __global__ void __launch_bounds__(256) copy_kernel(const CopyRec* __restrict__ r
                                                    const float* __restrict__ shift) {
   const CopyRec r = recs[blockIdx.x];
   const float v = (r.mat >= 0) ? shift[r.mat] : 0.f;
-  const int ld = r.ld;
-  const int64_t total = (int64_t)r.nrows * r.d;
+  const int ld = r.ld, d = r.d;
+  if (r.mode != 1 && (ld & 3) == 0 && ((reinterpret_cast<uintptr_t>(r.dst) | reinterpret_cast<uintptr_t>(r.src)) & 15) == 0) {
+    // rows are 16-byte aligned: whole float4s, then the ragged end of each row
+    const int d4 = d >> 2, per_row = d4 + (d & 3);
+    const int total = r.nrows * per_row;
+    for (int e = threadIdx.x; e < total; e += 256) {
+      const int lr = e / per_row, i = e - lr * per_row, row = r.row0 + lr;
+      float* drow = r.dst + (int64_t)row * ld;
+      if (i < d4) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r.mode == 0) {
+          x = *reinterpret_cast<const float4*>(r.src + (int64_t)row * ld + 4 * i);
+          const int dc = row - 4 * i;
+          if (dc == 0) x.x += v; else if (dc == 1) x.y += v; else if (dc == 2) x.z += v; else if (dc == 3) x.w += v;
+        }
+        *reinterpret_cast<float4*>(drow + 4 * i) = x;
+      } else {
+        const int col = 4 * d4 + (i - d4);
+        float x = 0.f;
+        if (r.mode == 0) {
+          x = r.src[(int64_t)row * ld + col];
+          if (row == col) x += v;
+        }
+        drow[col] = x;
+      }
+    }
+    return;
+  }
+  const int64_t total = (int64_t)r.nrows * d;
   for (int64_t e = threadIdx.x; e < total; e += 256) {
-    const int row = r.row0 + (int)(e / r.d), col = (int)(e % r.d);
+    const int row = r.row0 + (int)(e / d), col = (int)(e % d);
     if (r.mode == 2) {
       r.dst[(int64_t)row * ld + col] = 0.f;
     } else if (r.mode == 1) {

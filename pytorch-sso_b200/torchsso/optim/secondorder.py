@@ -169,10 +169,26 @@ class SecondOrderOptimizer(Optimizer):
     def local_param_groups(self):
         return self.param_groups
 
-    def zero_grad(self, set_to_none: bool = False):
+    #: what ``zero_grad()`` does when called without an argument (as the closures do).  True (torch's
+    #: own default): set every ``p.grad`` to None, autograd assigns its own tensors and one
+    #: multi-tensor copy after the closure brings them into the flat buffer (100 MB more memory for
+    #: ResNet-50).  False: zero the flat buffer and bind every ``p.grad`` to its view of it, autograd
+    #: accumulates in place (one small add kernel per parameter in every backward pass; ResNet-50:
+    #: 0.3 ms per step slower).
+    zero_grad_to_none = True
+
+    def zero_grad(self, set_to_none=None):
         """Zero the flat gradient buffer.  Parameters that are fp32 and contiguous get ``p.grad``
         bound to their view of it, so autograd accumulates in place; others (channels_last
-        weights, 16-bit parameters) get ``None`` and are copied in after the backward pass."""
+        weights, 16-bit parameters) get ``None`` and are copied in after the backward pass.
+        With ``set_to_none`` every parameter is treated like the latter."""
+        if set_to_none is None:
+            set_to_none = self.zero_grad_to_none
+        if set_to_none:
+            for p in self._grad_view:
+                if p.grad is not None:
+                    p.grad = None
+            return
         self._grad_flat.zero_()
         for p, v in self._grad_view.items():
             if p.dtype == torch.float32 and p.is_contiguous():

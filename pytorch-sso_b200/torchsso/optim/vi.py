@@ -93,8 +93,8 @@ class VIOptimizer(SecondOrderOptimizer):
                 curv.element_wise_init(init_precision)
                 curv.step(update_std=(group['std_scale'] > 0))
 
-    def zero_grad(self, set_to_none: bool = False):
-        super(VIOptimizer, self).zero_grad()
+    def zero_grad(self, set_to_none=None):
+        super(VIOptimizer, self).zero_grad(set_to_none)
         for group in self.param_groups:
             for m, p in zip(group['mean'], group['params']):
                 if m.grad is not None and m.grad.data_ptr() != self._grad_view[p].data_ptr():
@@ -256,8 +256,8 @@ class DistributedVIOptimizer(DistributedSecondOrderOptimizer, VIOptimizer):
     def actual_optimizer(self):
         return VIOptimizer
 
-    def zero_grad(self, set_to_none: bool = False):
-        self.actual_optimizer.zero_grad(self)
+    def zero_grad(self, set_to_none=None):
+        self.actual_optimizer.zero_grad(self, set_to_none)
 
     def extractors_for_rsv(self):
         return ['grad', 'curv.data']

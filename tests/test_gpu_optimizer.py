@@ -329,3 +329,25 @@ def test_fisher_sampling_survives_nan_probabilities(torchsso_mod):
     assert t.shape == (4, 3)
     assert int(t.min()) >= 0 and int(t.max()) <= 2
     assert int(t[:, 0].min()) >= 1          # the NaN class is never drawn
+
+
+def test_zero_grad_to_none_same_step(torchsso_mod, monkeypatch):
+    """Both gradient protocols of zero_grad() (bind to the flat buffer / set to None and harvest)
+    give the same update."""
+    torchsso = torchsso_mod
+    state = {}
+    patch_targets(monkeypatch, torchsso, state)
+    outs = []
+    for to_none in (False, True):
+        model = cases.make_model('tiny_convnet', seed=1).cuda()
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, {'ema_decay': 0.95, 'damping': 1e-3},
+                                                  lr=1e-2, momentum=0.9, weight_decay=1e-4)
+        opt.zero_grad_to_none = to_none
+        for t in range(3):
+            x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100 + t)
+            state['u'] = cases.make_uniform((2, 6), seed=200 + t)
+            closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2)
+            opt.step(closure=closure)
+        outs.append([p.detach().clone() for p in model.parameters()])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
