@@ -350,6 +350,29 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     state['step'] = 1
     ms_e2e, _, last_e2e = timed(args.steps, e2e=True)
+    # The metric's second figure, "K-FAC optimizer step ms": what optimizer.step() adds to its closure
+    # (EMA, exchange on N > 1, precondition, update; plus the round of inverses on every 10th step) =
+    # step time minus the time of the closure alone, CUDA events, same for every rank.
+    def avg_ms(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / n
+
+    def closure_only():
+        closure()
+        nat.join_curvature_stream(None)
+
+    def step_with(inv):
+        opt.update_inv = inv
+        opt.step(closure=closure)
+    closure_ms = avg_ms(closure_only, 5)
+    step_noinv_ms = avg_ms(lambda: step_with(False), 5)
+    step_inv_ms = avg_ms(lambda: step_with(True), 3)
     # Per-kernel timing of the dominant kernel (factor construction): CUDA events around every
     # factor launch, on the launching stream, over a few more steps of the same workload issued
     # eagerly (a replayed graph has no host-side call to bracket).
@@ -398,6 +421,10 @@ def run_gpu_arm(args):
                 'h2d_bytes_per_step': int(x_pin.numel() * 4 + y_pin.numel() * 8), 'd2h_bytes_per_step': 4,
                 'final_loss': float(last_e2e)},
         'gpu_launches': int(launches),
+        'optimizer_step_ms': {'closure': closure_ms, 'without_inverses': step_noinv_ms - closure_ms,
+                              'with_inverses': step_inv_ms - closure_ms,
+                              'note': 'optimizer.step() minus its closure (forward, sampling pass, backward, '
+                                      'curvature hooks); inverses run on every %dth step' % INV_INTERVAL},
         'roofline': {'bound': 'tensor', 'kernel': 'factor construction (all Kron layers, A and G)',
                      'achieved': achieved_tf, 'peak': tf_peak, 'unit': 'TFLOP/s',
                      'frac': achieved_tf / tf_peak if tf_peak else None,

@@ -489,6 +489,11 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tma_kernel(const sso_til
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * RAW_SLOTS + 2 * LO_SLOTS + 4];
   __shared__ uint32_t tmem_base_slot;
+  // the descriptors of this task's two operands: fetched while barriers and TMEM are set up
+  if (threadIdx.x == 32 * (MMA_WARP + 1)) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(maps[blockIdx.x].a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(maps[blockIdx.x].b)) : "memory");
+  }
   const sso_tile_task t = tasks[blockIdx.x];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nstages = ceil_div(t.k, KS);
