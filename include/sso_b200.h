@@ -43,7 +43,9 @@ const char* sso_last_error(void);
 uint64_t sso_launch_count(void);
 /* process-wide switches: "tc_auto" / "tma_auto" (0/1: may SSO_IMPL_AUTO choose the tcgen05 kernels /
  * the TMA-fed one), "engine_tc" (0/1: 128-wide tile phases of the engine on tcgen05 3xTF32 or fp32 FFMA),
- * "tc_flush" (stages of tensor-core accumulation between drains into fp32 registers) */
+ * "tc_flush" (stages of tensor-core accumulation between drains into fp32 registers),
+ * "chol_ksplit" (first 128-column panel of the blocked Cholesky whose update tasks are cut along K;
+ * 0 = never; read when a plan is built) */
 int sso_configure(const char* key, int value);
 
 /* ---------------------------------------------------------------------------------------

@@ -25,6 +25,7 @@ int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_
 int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
 int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, int count, int* status_dev, cudaStream_t st);
 bool tma_encode_f32_rows(void* out, const float* base, int64_t rows, int64_t cols, int64_t ld);
+int g_chol_ksplit = 16;  // Cholesky panel updates from this panel index on are cut along K (0: never)
 int g_engine_tma = 1;   // k-contiguous 128-wide tasks fetch their operands with TMA (tensor maps per task)
 int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
 
@@ -297,8 +298,21 @@ __global__ void shift_kernel(const MatRec* __restrict__ mats, const float* __res
 __global__ void __launch_bounds__(256) copy_kernel(const CopyRec* __restrict__ recs,
                                                    const float* __restrict__ shift) {
   const CopyRec r = recs[blockIdx.x];
-  const float v = (r.mat >= 0) ? shift[r.mat] : 0.f;
   const int ld = r.ld, d = r.d;
+  if (r.mode == 3) {
+    // dst (a tile of nrows x d) += its r.mat partial products, which sit side by side 128 columns
+    // apart starting at src; summed in that order
+    const int total = r.nrows * d;
+    for (int e = threadIdx.x; e < total; e += 256) {
+      const int row = e / d, col = e - row * d;
+      const int64_t o = (int64_t)row * ld + col;
+      float x = r.dst[o];
+      for (int q = 0; q < r.mat; ++q) x += r.src[o + q * 128];
+      r.dst[o] = x;
+    }
+    return;
+  }
+  const float v = (r.mat >= 0) ? shift[r.mat] : 0.f;
   if (r.mode != 1 && (ld & 3) == 0 && ((reinterpret_cast<uintptr_t>(r.dst) | reinterpret_cast<uintptr_t>(r.src)) & 15) == 0) {
     // rows are 16-byte aligned: whole float4s, then the ragged end of each row
     const int d4 = d >> 2, per_row = d4 + (d & 3);
@@ -449,14 +463,57 @@ static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot)
   auto blk2 = [](float* base, int d, int pi, int pj) { return base + (int64_t)pi * PB * d + (int64_t)pj * PB; };
   for (int p = 0; p < max_np; ++p) {
     int first = b.task_begin();
+    // Late panels have few tasks with a long K (one CTA each, most SMs idle): their K range is cut
+    // into `ksplit` slices of whole 128-column blocks.  Slice 0 updates the tile itself, the
+    // others write partial products into free 128x128 blocks of W's upper triangle (scratch
+    // during the factorisation), and a copy phase adds them to the tile in a fixed order.
+    int n_tasks = 0;
+    if (p > 0)
+      for (auto& m : ms) n_tasks += std::max(0, (m.d + PB - 1) / PB - p);
+    int ksplit = 1;
+    if (g_chol_ksplit > 0 && p >= g_chol_ksplit && n_tasks > 0) ksplit = std::max(1, std::min(std::min(8, 148 / n_tasks), p / 2));
+    const int first_sum = (int)b.p.copies.size();
     if (p > 0)
       for (auto& m : ms) {
         const int np = (m.d + PB - 1) / PB;
-        for (int i = p; i < np; ++i)
-          b.gemm(blk2(m.W, m.ld, i, 0), m.ld, false, blk2(m.W, m.ld, p, 0), m.ld, true, blk2(m.W, m.ld, i, p), m.ld,
-                 std::min(PB, m.d - i * PB), std::min(PB, m.d - p * PB), p * PB, -1.f, 1.f);
+        // free scratch blocks (r, c), r < c <= np - 2 (full 128x128 blocks above the diagonal), handed
+        // out as runs of ksplit - 1 neighbours in one block row
+        int sr = 0, sc = 1;
+        auto take_run = [&](int len) -> float* {
+          while (sr <= np - 3) {
+            if (sc + len - 1 <= np - 2) {
+              float* q = blk2(m.W, m.ld, sr, sc);
+              sc += len;
+              return q;
+            }
+            ++sr; sc = sr + 1;
+          }
+          return nullptr;
+        };
+        for (int i = p; i < np; ++i) {
+          const int mi = std::min(PB, m.d - i * PB), nj = std::min(PB, m.d - p * PB);
+          float* C = blk2(m.W, m.ld, i, p);
+          float* run = ksplit > 1 ? take_run(ksplit - 1) : nullptr;
+          const int parts = run ? ksplit : 1;
+          const int per = (p + parts - 1) / parts;        // 128-column blocks of K per slice
+          int used = 0;
+          for (int s = 0; s < parts; ++s) {
+            const int kb0 = s * per, kb1 = std::min(p, kb0 + per);
+            if (kb0 >= kb1) break;
+            float* dst = s == 0 ? C : run + (int64_t)(s - 1) * PB;
+            b.gemm(blk2(m.W, m.ld, i, kb0), m.ld, false, blk2(m.W, m.ld, p, kb0), m.ld, true, dst, m.ld, mi, nj,
+                   (kb1 - kb0) * PB, -1.f, s == 0 ? 1.f : 0.f);
+            used = s;
+          }
+          if (used > 0) {
+            CopyRec c;
+            c.src = run; c.dst = C; c.d = nj; c.row0 = 0; c.nrows = mi; c.mat = used; c.mode = 3; c.ld = m.ld;
+            b.p.copies.push_back(c);
+          }
+        }
       }
     b.end_phase(1, first, b.task_begin() - first);
+    b.end_phase(3, first_sum, (int)b.p.copies.size() - first_sum);
     for (int half = 0; half < 2; ++half) {
       const int j = 2 * p + half;
       if (half == 1) {   // second block column of the panel: update by the first

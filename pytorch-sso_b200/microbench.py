@@ -387,10 +387,15 @@ def main():
     ap.add_argument('--rows', type=int, default=0)
     ap.add_argument('--rotate', type=int, default=4, help='input buffers rotated between launches')
     ap.add_argument('--impl', type=int, default=nat.IMPL_AUTO, help='0 auto, 1 SIMT, 2 tcgen05 gather, 3 TMA')
+    ap.add_argument('--configure', action='append', default=[], metavar='KEY=VALUE',
+                    help='library switches (sso_configure), e.g. chol_ksplit=0')
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit('microbench needs a CUDA device: there is no CPU path')
     nat.lib()
+    for kv in args.configure:
+        k, v = kv.split('=')
+        nat.configure(k, int(v))
     SUITES[args.suite](args)
 
 

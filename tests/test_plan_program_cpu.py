@@ -79,6 +79,14 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
                     mem.view(r.LinvT, r.size, r.size, r.ld_invt)[...] = Linv.T
         elif kind == 3:
             for r in [copies[i] for i in range(first, first + count)]:
+                if r.mode == 3:     # tile += its partial products (128 columns apart, from src on)
+                    tile = mem.view(r.dst, r.nrows, r.d, r.ld)
+                    assert r.mat >= 1
+                    for q in range(r.mat):
+                        part = mem.view(r.src + 4 * 128 * q, r.nrows, r.d, r.ld)
+                        assert not np.isnan(part).any(), 'partial product was never written'
+                        tile += part
+                    continue
                 dst = mem.view(r.dst, r.d, r.d, r.ld)
                 rows = slice(r.row0, r.row0 + r.nrows)
                 if r.mode == 2:
@@ -103,8 +111,18 @@ def spd(d, seed):
     return (x.T @ x / x.shape[0]).astype(np.float32)
 
 
-@pytest.mark.parametrize('dims', [[10, 28], [64, 65], [130, 200], [257, 64, 1, 513]])
+@pytest.mark.parametrize('dims', [[10, 28], [64, 65], [130, 200], [257, 64, 1, 513], [1100, 700]])
 def test_kron_inverse_and_std_program(dims):
+    # cut the panel updates along K from the fourth panel on (default: the 16th), so that the small
+    # matrices of this test exercise the partial-product tasks and the summing copies
+    nat.configure('chol_ksplit', 4)
+    try:
+        _kron_inverse_and_std_program(dims)
+    finally:
+        nat.configure('chol_ksplit', 16)
+
+
+def _kron_inverse_and_std_program(dims):
     mem = Mem()
     n = len(dims)
     src = [mem.new(d * d) for d in dims]
