@@ -33,8 +33,8 @@ constexpr int DT = 64, DK = 16;
 // the samples themselves are the contraction index and the operands are squared while staged.
 template <typename T, bool ONE_PIXEL>
 __global__ void __launch_bounds__(256) diag_sq_kernel(const DiagSqParams p) {
-  __shared__ float Gs[DK][DT + 1];
-  __shared__ float Us[DK][DT + 1];
+  __shared__ __align__(16) float Gs[DK][DT + 4];   // row pitch 68 floats: float4 rows stay 16-byte aligned
+  __shared__ __align__(16) float Us[DK][DT + 4];
   __shared__ int64_t col_off[DT];
   __shared__ int col_dh[DT], col_dw[DT];
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
@@ -81,11 +81,9 @@ __global__ void __launch_bounds__(256) diag_sq_kernel(const DiagSqParams p) {
       __syncthreads();
 #pragma unroll
       for (int k = 0; k < DK; ++k) {
-        float gr[4], ur[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gr[i] = Gs[k][ty * 4 + i];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) ur[q] = Us[k][tx * 4 + q];
+        const float4 g4 = *reinterpret_cast<const float4*>(&Gs[k][ty * 4]);
+        const float4 u4 = *reinterpret_cast<const float4*>(&Us[k][tx * 4]);
+        const float gr[4] = {g4.x, g4.y, g4.z, g4.w}, ur[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -100,34 +98,38 @@ __global__ void __launch_bounds__(256) diag_sq_kernel(const DiagSqParams p) {
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[i][q] = 0.f;
-    for (int l0 = 0; l0 < L; l0 += DK) {
+    // the gathers of chunk l0 + DK are in flight while chunk l0 is multiplied
+    T gv[4], uv[4];    // raw values: converted when stored, so that nothing waits on the loads here
+    auto gather = [&](int l0) {
       const int l = l0 + ll;
       const bool lv = l < L;
       const int oy = lv ? l / p.wo : 0, ox = lv ? l - oy * p.wo : 0;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const int o = o0 + c4 + q;
-        float gv = 0.f;
+        gv[q] = T(0.f);
         if (lv && o < p.oc)
-          gv = to_f32<T>(__ldg(G + (int64_t)b * p.sgn + (int64_t)o * p.sgc + (int64_t)oy * p.sgh + (int64_t)ox * p.sgw));
-        Gs[ll][c4 + q] = gv;
-        float uv = 0.f;
+          gv[q] = __ldg(G + (int64_t)b * p.sgn + (int64_t)o * p.sgc + (int64_t)oy * p.sgh + (int64_t)ox * p.sgw);
+        uv[q] = T(0.f);
         const int64_t off = col_off[c4 + q];
         if (lv && off >= 0) {
           const int ih = oy * p.stride_h + col_dh[c4 + q], iw = ox * p.stride_w + col_dw[c4 + q];
           if ((unsigned)ih < (unsigned)p.h && (unsigned)iw < (unsigned)p.w)
-            uv = to_f32<T>(__ldg(X + (int64_t)b * p.sxn + off + (int64_t)ih * p.sxh + (int64_t)iw * p.sxw));
+            uv[q] = __ldg(X + (int64_t)b * p.sxn + off + (int64_t)ih * p.sxh + (int64_t)iw * p.sxw);
         }
-        Us[ll][c4 + q] = uv;
       }
+    };
+    gather(0);
+    for (int l0 = 0; l0 < L; l0 += DK) {
+      *reinterpret_cast<float4*>(&Gs[ll][c4]) = make_float4(to_f32<T>(gv[0]), to_f32<T>(gv[1]), to_f32<T>(gv[2]), to_f32<T>(gv[3]));
+      *reinterpret_cast<float4*>(&Us[ll][c4]) = make_float4(to_f32<T>(uv[0]), to_f32<T>(uv[1]), to_f32<T>(uv[2]), to_f32<T>(uv[3]));
       __syncthreads();
+      if (l0 + DK < L) gather(l0 + DK);
 #pragma unroll
       for (int k = 0; k < DK; ++k) {
-        float gr[4], ur[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gr[i] = Gs[k][ty * 4 + i];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) ur[q] = Us[k][tx * 4 + q];
+        const float4 g4 = *reinterpret_cast<const float4*>(&Gs[k][ty * 4]);
+        const float4 u4 = *reinterpret_cast<const float4*>(&Us[k][tx * 4]);
+        const float gr[4] = {g4.x, g4.y, g4.z, g4.w}, ur[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
