@@ -25,7 +25,7 @@ int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_
 int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
 int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, int count, int* status_dev, cudaStream_t st);
 bool tma_encode_f32_rows(void* out, const float* base, int64_t rows, int64_t cols, int64_t ld);
-int g_chol_ksplit = 16;  // Cholesky panel updates from this panel index on are cut along K (0: never)
+int g_chol_ksplit = 6;  // Cholesky panel updates from this panel index on are cut along K (0: never)
 int g_engine_tma = 1;   // k-contiguous 128-wide tasks fetch their operands with TMA (tensor maps per task)
 int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
 
@@ -307,7 +307,11 @@ __global__ void __launch_bounds__(256) copy_kernel(const CopyRec* __restrict__ r
       const int row = e / d, col = e - row * d;
       const int64_t o = (int64_t)row * ld + col;
       float x = r.dst[o];
-      for (int q = 0; q < r.mat; ++q) x += r.src[o + q * 128];
+      float pv[7];      // at most 7 partial products (8 slices); the loads are independent of each other
+#pragma unroll
+      for (int q = 0; q < 7; ++q) pv[q] = q < r.mat ? r.src[o + q * 128] : 0.f;
+#pragma unroll
+      for (int q = 0; q < 7; ++q) x += pv[q];
       r.dst[o] = x;
     }
     return;
@@ -505,9 +509,11 @@ static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot)
                    (kb1 - kb0) * PB, -1.f, s == 0 ? 1.f : 0.f);
             used = s;
           }
-          if (used > 0) {
+          // one record (one CTA of the copy phase) per 16 rows of the tile
+          for (int r0 = 0; used > 0 && r0 < mi; r0 += 16) {
             CopyRec c;
-            c.src = run; c.dst = C; c.d = nj; c.row0 = 0; c.nrows = mi; c.mat = used; c.mode = 3; c.ld = m.ld;
+            c.src = run + (int64_t)r0 * m.ld; c.dst = C + (int64_t)r0 * m.ld; c.d = nj; c.row0 = 0;
+            c.nrows = std::min(16, mi - r0); c.mat = used; c.mode = 3; c.ld = m.ld;
             b.p.copies.push_back(c);
           }
         }

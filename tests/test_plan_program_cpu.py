@@ -113,13 +113,13 @@ def spd(d, seed):
 
 @pytest.mark.parametrize('dims', [[10, 28], [64, 65], [130, 200], [257, 64, 1, 513], [1100, 700]])
 def test_kron_inverse_and_std_program(dims):
-    # cut the panel updates along K from the fourth panel on (default: the 16th), so that the small
+    # cut the panel updates along K from the fourth panel on (default: the sixth), so that the small
     # matrices of this test exercise the partial-product tasks and the summing copies
     nat.configure('chol_ksplit', 4)
     try:
         _kron_inverse_and_std_program(dims)
     finally:
-        nat.configure('chol_ksplit', 16)
+        nat.configure('chol_ksplit', 6)
 
 
 def _kron_inverse_and_std_program(dims):
