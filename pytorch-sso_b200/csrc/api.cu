@@ -30,7 +30,7 @@ static int g_tma_auto = 1;   // whether SSO_IMPL_AUTO may pick the TMA-fed tcgen
 
 using namespace sso;
 
-namespace sso { extern int g_kc_variant; extern int g_engine_tma; extern int g_chol_ksplit; }
+namespace sso { extern int g_kc_variant; extern int g_engine_tma; extern int g_chol_ksplit; extern int g_phase_lpt; }
 
 extern "C" {
 
@@ -47,6 +47,7 @@ int sso_configure(const char* key, int value) {
   if (k == "tma_f32") { factor_tma_set_f32(value); return 0; }
   if (k == "tma_pair_min_d") { factor_tma_set_pair_min_d(value); return 0; }
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }
+  if (k == "phase_lpt") { g_phase_lpt = value != 0; return 0; }
   if (k == "chol_ksplit") { g_chol_ksplit = (int)value; return 0; }
   if (k == "kc_variant") { g_kc_variant = value; return 0; }
   if (k == "tc_flush") { factor_tc_set_flush(value); return 0; }

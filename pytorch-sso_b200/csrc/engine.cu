@@ -25,6 +25,7 @@ int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_
 int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st);
 int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, int count, int* status_dev, cudaStream_t st);
 bool tma_encode_f32_rows(void* out, const float* base, int64_t rows, int64_t cols, int64_t ld);
+int g_phase_lpt = 1;    // tasks of a 128-wide phase sorted by decreasing K
 int g_chol_ksplit = 6;  // Cholesky panel updates from this panel index on are cut along K (0: never)
 int g_engine_tma = 1;   // k-contiguous 128-wide tasks fetch their operands with TMA (tensor maps per task)
 int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
@@ -435,6 +436,12 @@ struct Builder {
     // (kind 1) as two launches
     auto mid = std::stable_partition(p.tasks.begin() + first, p.tasks.begin() + first + count, k_contiguous);
     const int nfast = (int)(mid - (p.tasks.begin() + first));
+    // CTAs are handed out in task order: longest K first keeps the tail of each launch short
+    if (g_phase_lpt) {
+      auto longer = [](const sso_tile_task& a, const sso_tile_task& b) { return a.k > b.k; };
+      std::stable_sort(p.tasks.begin() + first, mid, longer);
+      std::stable_sort(mid, p.tasks.begin() + first + count, longer);
+    }
     push_phase(4, first, nfast);
     push_phase(1, first + nfast, count - nfast);
   }
