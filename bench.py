@@ -151,88 +151,169 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference path on the host cores
 # ---------------------------------------------------------------------------------------------
-def cpu_port_images_per_sec(batch, steps, seed=0):
-    """Times oracle.kfac_step.OracleKFAC (torch CPU ops, all host threads) on ResNet-50 with a
-    reduced batch: `steps` steps without inverse + one step with the inverses, combined as the
-    workload's 1-in-10 inverse schedule.  Returns (images/sec, cores, sample description)."""
-    from oracle.kfac_step import OracleKFAC
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    torch.manual_seed(seed)
-    model = ResNet50()
-    opt = OracleKFAC(model, 'Fisher', ema_decay=CURV_KW['ema_decay'], damping=CURV_KW['damping'], lr=1e-3)
-    x, y = synthetic_batch(batch, 1000, seed)
-    mc = torch.randint(0, 1000, (1, batch), generator=torch.Generator().manual_seed(seed + 1))
-    t0 = time.perf_counter()
-    opt.update_inv = True
-    opt.step(x, y, mc)
-    t_inv = time.perf_counter() - t0
-    opt.update_inv = False
-    ts = []
-    for _ in range(max(1, steps)):
+class CpuPort:
+    """oracle.kfac_step.OracleKFAC (torch CPU ops, all host threads) on the benchmark's own
+    configuration: ResNet-50, `batch` images of the rank-0 stream (seed = step index), fp32, Fisher
+    MC(1), inverses on every INV_INTERVAL-th step starting with the first."""
+
+    def __init__(self, batch):
+        from oracle.kfac_step import OracleKFAC
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        torch.manual_seed(0)
+        self.batch = batch
+        self.model = ResNet50()
+        self.opt = OracleKFAC(self.model, 'Fisher', ema_decay=CURV_KW['ema_decay'], damping=CURV_KW['damping'], lr=1e-3)
+        self.step_index = 0
+        self.first = None
+
+    def step(self):
+        """One optimizer step; returns its wall time in seconds."""
+        i = self.step_index
+        x, y = synthetic_batch(self.batch, 1000, i)
+        mc = torch.randint(0, 1000, (1, self.batch), generator=torch.Generator().manual_seed(50000 + i))
+        self.opt.update_inv = (i % INV_INTERVAL == 0)
         t0 = time.perf_counter()
-        opt.step(x, y, mc)
-        ts.append(time.perf_counter() - t0)
+        loss, _ = self.opt.step(x, y, mc)
+        dt = time.perf_counter() - t0
+        if self.first is None:
+            self.first = {'loss': float(loss), 'stem_A_norm': float(self.opt.layers[0].ema[0].double().norm()),
+                          'layer1_conv1_A_norm': float(self.opt.layers[2].ema[0].double().norm())}
+        self.step_index += 1
+        return dt
+
+
+def cpu_port_sample(batch, budget_s=25.0):
+    """Bounded sample for the GPU arm's `cpu_baseline`: the first step (with inverses) and as many
+    plain steps as fit in the budget (at least one), combined with the 1-in-INV_INTERVAL schedule."""
+    port = CpuPort(batch)
+    t_inv = port.step()
+    ts = []
+    while not ts or (sum(ts) + t_inv + ts[-1] < budget_s and len(ts) < 4):
+        ts.append(port.step())
     t_plain = sorted(ts)[len(ts) // 2]
     per_step = t_plain + max(0.0, t_inv - t_plain) / INV_INTERVAL
-    sample = ('ResNet-50 K-FAC step at batch %d (full model, all 107 curvature groups): 1 step with '
-              'inverses (%.1f s) + %d without (median %.1f s), combined 1-in-%d'
+    sample = ('ResNet-50 K-FAC steps at batch %d (the benchmark\'s configuration, full model, 107 curvature '
+              'groups): 1 step with inverses (%.1f s) + %d without (median %.1f s), combined 1-in-%d'
               % (batch, t_inv, len(ts), t_plain, INV_INTERVAL))
-    return batch / per_step, cores, sample, per_step
+    return batch / per_step, port.cores, sample, port.first
 
 
-def sgd_images_per_sec(batch, dev, steps=20):
-    """Stock torch SGD (momentum 0.9) on the same ResNet-50, bf16 autocast, channels_last inputs,
-    the whole step replayed from a CUDA graph: the denominator of the "fraction of SGD" figure."""
+def sgd_images_per_sec(batch, dev, world, rank, steps=20):
+    """Stock torch SGD (momentum 0.9) on the same ResNet-50, bf16 autocast, channels_last inputs: the
+    denominator of the "fraction of SGD" figure, whole job over `world` GPUs.  Forward + backward are
+    replayed from one CUDA graph and the update from another; between them, on more than one GPU,
+    the flat gradient buffer is all-reduced (what DistributedDataParallel does, in one bucket)."""
+    import torch.distributed as dist
+    torch.manual_seed(0)
     model = ResNet50().to(dev)
     opt = torch.optim.SGD(model.parameters(), lr=1e-3, momentum=0.9)
-    x, y = synthetic_batch(batch, 1000, 7)
+    x, y = synthetic_batch(batch, 1000, 7 + 1000 * rank)
     x = x.to(dev).contiguous(memory_format=torch.channels_last)
     y = y.to(dev)
+    params = list(model.parameters())
+    flat = torch.zeros(sum(p.numel() for p in params), device=dev)
+    off = 0
+    for p in params:
+        p.grad = flat[off:off + p.numel()].view_as(p)
+        off += p.numel()
 
-    def step():
-        opt.zero_grad(set_to_none=True)
+    def fwd_bwd():
+        flat.zero_()
         with torch.autocast('cuda', dtype=torch.bfloat16):
             loss = F.cross_entropy(model(x).float(), y)
         loss.backward()
+
+    def update():
+        if world > 1:
+            flat.mul_(1.0 / world)
         opt.step()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         for _ in range(3):
-            step()
+            fwd_bwd()
+            update()
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        step()
+    g1, g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g1):
+        fwd_bwd()
+    with torch.cuda.graph(g2):
+        update()
+
+    def step():
+        g1.replay()
+        if world > 1:
+            dist.all_reduce(flat)
+        g2.replay()
     for _ in range(3):
-        graph.replay()
+        step()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        graph.replay()
+        step()
     e1.record()
+    if world > 1:
+        dist.barrier()
     torch.cuda.synchronize()
-    return batch * steps / (e0.elapsed_time(e1) / 1e3)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return world * batch * steps / (ms / 1e3)
 
 
 def run_reference_arm(args):
+    """CPU arm: the oracle port of the reference path on all host cores, same configuration as the GPU
+    arm (batch 32 per step, inverses every INV_INTERVAL-th step).  The reference itself is Python
+    over CuPy / ChainerMN and cannot be installed here, and its sources do not travel to the
+    benchmark machine; the port is bit-identical to the reference's CPU run on the committed fixtures.
+    W warm-up steps and K timed steps are executed as asked as long as they fit a wall-clock budget;
+    the JSON line reports the steps that were actually run and timed."""
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    val, cores, sample, per_step = cpu_port_images_per_sec(args.cpu_batch, max(1, min(args.steps, 2)))
+    t_start = time.perf_counter()
+    budget = args.cpu_budget
+    port = CpuPort(args.batch)
+    warm = 0
+    for _ in range(args.warmup):
+        if warm >= 1 and time.perf_counter() - t_start > 0.2 * budget:
+            break
+        port.step()
+        warm += 1
+    # keep the timed window on the schedule's phase: it starts on a step with inverses
+    port.step_index = 0
+    ts = []
+    for _ in range(args.steps):
+        if ts and time.perf_counter() - t_start + max(ts) > budget:
+            break
+        ts.append(port.step())
+    steps = len(ts)
+    total = sum(ts)
+    val = args.batch * steps / total
+    n_inv = sum(1 for i in range(steps) if i % INV_INTERVAL == 0)
+    sample = ('%d consecutive optimizer steps at batch %d (%d with inverses), %.1f s; asked for %d steps / %d warm-up, '
+              'budget %.0f s' % (steps, args.batch, n_inv, total, args.steps, args.warmup, budget))
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': val, 'unit': 'images/sec', 'n_gpus': args.gpus,
-        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': per_step * 1e3,
+        'steps': steps, 'warmup': warm, 'ms_per_step': total / steps * 1e3,
         'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
         'data': 'synthetic',
-        'config': {'workload': 'resnet50_kfac_b32', 'batch_per_gpu': 32, 'inverse_every': INV_INTERVAL,
-                   'note': 'CPU restatement of the reference path (the reference GPU path needs '
-                           'CuPy/ChainerMN, absent here); bounded sample at batch %d' % args.cpu_batch},
-        'cpu_baseline': {'value': val, 'unit': 'images/sec', 'cores': cores, 'kind': 'port', 'sample': sample},
+        'config': {'workload': 'resnet50_kfac_b32', 'batch_per_gpu': args.batch, 'global_batch': args.batch,
+                   'image': '3x224x224', 'curvature': 'Fisher MC(1): Kron conv/linear + diag BN',
+                   'factors_every': 1, 'inverse_every': INV_INTERVAL,
+                   'steps_requested': args.steps, 'warmup_requested': args.warmup,
+                   'note': 'CPU restatement (oracle/) of the reference path on the host cores; the reference '
+                           'needs CuPy/ChainerMN for its GPU path and is Python, so it neither installs nor travels'},
+        'cpu_baseline': {'value': val, 'unit': 'images/sec', 'cores': port.cores, 'kind': 'port', 'sample': sample},
         'e2e': {'value': val, 'unit': 'images/sec', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'first_step': port.first,
     }
     print(json.dumps(line), flush=True)
 
@@ -276,13 +357,15 @@ def run_gpu_arm(args):
     else:
         opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, CURV_KW, **kw)
     B = args.batch
-    # a small pool of different synthetic batches, cycled: fresh data every step keeps the loss
-    # (and with it the curvature) stationary instead of memorising one batch
-    NB = 4
+    # A fresh synthetic batch for every step (rank r, step i: seed 1000*r + i), generated and pinned
+    # before anything is timed: one fixed batch is memorised within a few steps, the loss and with it
+    # the G factors collapse, and stale inverses then blow the loss up.
+    W = max(args.warmup, 3)
+    NB = 1 + W + 2 * args.steps
     pinned = [synthetic_batch(B, 1000, 1000 * rank + i, pin=True) for i in range(NB)]
-    resident = [(xp.to(dev).contiguous(memory_format=torch.channels_last), yp.to(dev)) for xp, yp in pinned]
     x_pin, y_pin = pinned[0]
-    state = {'step': 0}
+    resident = [(xp.to(dev), yp.to(dev)) for xp, yp in pinned[:1 + W + args.steps]]
+    state = {'step': 0, 'batch': 0}
 
     # The closure reads its batch from fixed device tensors so that it can be captured once into a
     # CUDA graph (forward, sampling backward, loss backward and all curvature kernels of the hooks)
@@ -290,14 +373,20 @@ def run_gpu_arm(args):
     x_static = torch.empty_like(resident[0][0])
     y_static = torch.empty_like(resident[0][1])
     x_static.copy_(resident[0][0]); y_static.copy_(resident[0][1])
+    state['batch'] = 1
     # autograd assigns fresh gradient tensors instead of accumulating into the optimizer's flat buffer
     # (one add kernel per parameter per backward pass); one multi-tensor copy harvests them
     opt.zero_grad_to_none = (args.grads == 'assign')
     closure = fisher_closure(torchsso, opt, model, x_static, y_static)
     eager_closure = closure
+    first = None
     if args.graph:
         opt.update_inv = True
-        opt.step(closure=closure)            # eager first step: builds pools, plans, scratch
+        loss0, _ = opt.step(closure=closure)            # eager first step: builds pools, plans, scratch
+        if world == 1:
+            kron_groups = [g for g in opt.param_groups if isinstance(g['curv'], torchsso.KronCurvature)]
+            first = {'loss': float(loss0), 'stem_A_norm': float(kron_groups[0]['curv'].ema[0].double().norm()),
+                     'layer1_conv1_A_norm': float(kron_groups[1]['curv'].ema[0].double().norm())}
         # the model has no in-place activations, so the hooks' kernels may run beside it
         torchsso.utils.set_curvature_stream(args.side_stream)
         closure = torchsso.utils.GraphedClosure(opt, closure)
@@ -316,6 +405,11 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def next_batch(pool):
+        b = pool[state['batch'] % len(pool)]
+        state['batch'] += 1
+        return b
+
     def timed(nsteps, e2e):
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -325,9 +419,9 @@ def run_gpu_arm(args):
         last = None
         for i in range(nsteps):
             if e2e:
-                last = one_step(*pinned[i % NB]).item()      # host -> device copy inside one_step
+                last = one_step(*next_batch(pinned)).item()      # host -> device copy inside one_step
             else:
-                last = one_step(*resident[i % NB])
+                last = one_step(*next_batch(resident))
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -338,11 +432,11 @@ def run_gpu_arm(args):
         launches = nat.launch_count() - l0
         if args.graph:      # kernels inside the replayed graph are not seen by the host-side counter
             launches += (closure.replays - r0) * closure.library_kernels_per_replay
-        return ms, launches, float(last)
+        return ms, launches, float(last.detach()) if torch.is_tensor(last) else float(last)
 
     # warm-up (also builds plans and cuDNN algorithm choices); first step inverts
-    for i in range(max(args.warmup, 3)):
-        one_step(*resident[i % NB])
+    for i in range(W):
+        one_step(*next_batch(resident))
     # align the inverse schedule so that every timed window of K steps sees K/10 inverses
     state['step'] = 1
     with ClockSampler(local_rank) as clocks:
@@ -385,7 +479,7 @@ def run_gpu_arm(args):
         # hold the stream back ~25 ms so that the host runs ahead and the step's kernels execute
         # back to back, as they do inside the replayed graph, instead of each starting on an idle GPU
         torch.cuda._sleep(int(5e7))
-        x_static.copy_(resident[i % NB][0]); y_static.copy_(resident[i % NB][1])
+        x_static.copy_(resident[i][0]); y_static.copy_(resident[i][1])
         opt.update_inv = False
         opt.step(closure=eager_closure)
     torch.cuda.synchronize()
@@ -395,6 +489,20 @@ def run_gpu_arm(args):
     f_flops = sum(f for _, _, f, _ in ft)
     f_bytes = sum(nb for _, _, _, nb in ft)
 
+    # data-parallel correctness bit: after the all-gather every rank must hold the same parameters
+    rank_diff = None
+    if world > 1:
+        flat_p = torch.cat([p.detach().flatten().float() for p in model.parameters()])
+        hi, lo = flat_p.clone(), flat_p.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        rank_diff = float((hi - lo).abs().max().item())
+        del flat_p, hi, lo
+    sgd = None
+    if not args.no_sgd_baseline:
+        del closure, eager_closure, opt
+        torch.cuda.empty_cache()
+        sgd = sgd_images_per_sec(B, dev, world, rank)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -428,25 +536,31 @@ def run_gpu_arm(args):
         'roofline': {'bound': 'tensor', 'kernel': 'factor construction (all Kron layers, A and G)',
                      'achieved': achieved_tf, 'peak': tf_peak, 'unit': 'TFLOP/s',
                      'frac': achieved_tf / tf_peak if tf_peak else None,
-                     # DRAM bytes per launch: algorithmic bytes (input once + d*d*4 output) averaged over
-                     # the factor launches, times the measured/algorithmic ratio of the ncu capture of one
-                     # launch (profiles/factor_tma_pair_kernel_*: 55.4 MB measured for 56.7 MB algorithmic)
-                     'traffic': (f_bytes / len(ft)) * (55.4 / 56.7) if ft else None,
-                     'traffic_unit': 'bytes per launch (average over the launches of a step)',
+                     # measured DRAM bytes exist per kernel and shape only (ncu captures summarised under
+                     # profiles/: they equal the algorithmic bytes, the input read once); a step's 108
+                     # launches are all different, so the line carries the algorithmic figure
+                     'traffic': None,
+                     'algorithmic_bytes_per_launch': (f_bytes / len(ft)) if ft else None,
                      'peak_source': peak_src + ' (bf16 dense, sustained)',
                      'launches': len(ft), 'total_ms': f_ms, 'measured_over_steps': probe_steps,
                      'flops_rule': '2*rows*d^2 per factor (what the reference einsum performs)'},
     }
-    if world == 1 and not args.no_sgd_baseline:
-        del closure, eager_closure, opt
-        sgd = sgd_images_per_sec(B, dev)
-        line['sgd_baseline'] = {'value': sgd, 'unit': 'images/sec', 'frac_of_sgd': ips / sgd,
-                                'note': 'stock torch SGD+momentum, same model / batch / bf16 autocast, '
-                                        'CUDA-graph replay, measured in this run'}
+    if rank_diff is not None:
+        line['config']['max_param_difference_across_ranks'] = rank_diff
+    if sgd is not None:
+        line['sgd_baseline'] = {'value': sgd, 'unit': 'images/sec', 'frac_of_sgd': ips / sgd, 'n_gpus': world,
+                                'note': 'stock torch SGD+momentum, same model / per-GPU batch / bf16 autocast, '
+                                        'CUDA-graph replay, flat-gradient all-reduce on N > 1, measured in this run'}
     if world == 1 and not args.no_cpu_baseline:
-        val, cores, sample, _ = cpu_port_images_per_sec(args.cpu_batch, 2)
+        val, cores, sample, cpu_first = cpu_port_sample(B)
         line['cpu_baseline'] = {'value': val, 'unit': 'images/sec', 'cores': cores, 'kind': 'port',
                                 'sample': sample}
+        if first is not None:
+            # same initial weights and first batch on both arms: the stem factor sees the fp32 image on
+            # both (1e-6 class agreement); the loss and the next layer go through bf16 activations here
+            line['parity'] = {'first_step_gpu': first, 'first_step_cpu_port': cpu_first,
+                              'rel_diff': {k: abs(first[k] - cpu_first[k]) / max(abs(cpu_first[k]), 1e-30)
+                                           for k in first}}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -470,7 +584,8 @@ def main():
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--batch', type=int, default=32, help='images per GPU')
-    ap.add_argument('--cpu-batch', type=int, default=16, help='batch of the bounded CPU sample')
+    ap.add_argument('--cpu-budget', type=float, default=240.0,
+                    help='wall-clock budget in seconds of the CPU arm (--impl reference)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-sgd-baseline', action='store_true')
     ap.add_argument('--weights', default='contiguous', choices=['channels_last', 'contiguous'],

@@ -58,7 +58,9 @@ class OracleKFAC:
     def __init__(self, model: nn.Module, curv_type: str = 'Fisher', ema_decay: float = 1.0,
                  damping: float = 1e-7, lr: float = 0.01, momentum: float = 0.0,
                  l2_reg: float = 0.0, weight_decay: float = 0.0, acc_steps: int = 1,
-                 diag: tuple = ()):
+                 diag: tuple = (), momentum_type: str = 'preconditioned', lars: bool = False,
+                 lars_type: str = 'preconditioned', normalizing_weights: bool = False,
+                 weight_scale: Optional[float] = None, use_max_ema: bool = False):
         """``diag``: class names ('Linear', 'Conv2d') that get the diagonal curvature of
         torchsso/curv/cov/linear.py:28-45 / cov/conv.py:15-42 instead of the Kronecker one."""
         assert curv_type in ('Cov', 'Fisher')
@@ -69,6 +71,9 @@ class OracleKFAC:
         self.lr, self.momentum = lr, momentum
         self.l2_reg, self.weight_decay = l2_reg, weight_decay
         self.acc_steps = acc_steps
+        self.momentum_type, self.lars, self.lars_type = momentum_type, lars, lars_type
+        self.normalizing_weights, self.weight_scale = normalizing_weights, weight_scale
+        self.use_max_ema = use_max_ema
         self.acc_step = 0
         self.steps = 0
         self.update_inv = True
@@ -199,19 +204,39 @@ class OracleKFAC:
             if layer_filter is not None and not layer_filter(idx):
                 continue
             with torch.no_grad():
-                if self.l2_reg != 0:
-                    for p in L.params:
-                        p.grad.add_(p.data, alpha=self.l2_reg)
-                    L.l2_reg = self.l2_reg
+                # secondorder.py:233-307: raw stage, curvature step, preconditioned stage, update
+                self._preprocess(L, 'raw')
                 self.curvature_step(L)
                 self.precondition(L)
-                for p, buf in zip(L.params, L.momentum_buf):
-                    if self.weight_decay != 0:
-                        p.grad.add_(p.data, alpha=self.weight_decay)
-                    if self.momentum != 0:
-                        buf.mul_(self.momentum).add_(p.grad)
-                        p.grad.copy_(buf)
+                self._preprocess(L, 'preconditioned')
+                for p in L.params:
                     p.data.add_(p.grad, alpha=-self.lr)
+                if self.normalizing_weights:
+                    # secondorder.py:309-330: the module's ``weight`` only, rescaled to a fixed norm
+                    w = getattr(L.module, 'weight', None)
+                    for p in L.params:
+                        if w is not None and p is w and p.data.norm() > 1e-2:
+                            scale = self.weight_scale
+                            if scale is None:
+                                scale = math.sqrt(2.0 * w.shape[0])
+                            p.data.div_(p.data.norm() + 1e-9).mul_(scale)
+
+    def _preprocess(self, L: _Layer, stage: str):
+        """secondorder.py:233-307 for one stage ('raw' before the curvature step, 'preconditioned'
+        after): l2 / weight decay, momentum, LARS, in the reference's order."""
+        for p, buf in zip(L.params, L.momentum_buf):
+            if stage == 'raw' and self.l2_reg != 0:
+                p.grad.add_(p.data, alpha=self.l2_reg)
+                L.l2_reg = self.l2_reg
+            if stage == 'preconditioned' and self.weight_decay != 0:
+                p.grad.add_(p.data, alpha=self.weight_decay)
+            if self.momentum_type == stage and self.momentum != 0:
+                buf.mul_(self.momentum).add_(p.grad)
+                p.grad.copy_(buf)
+            if self.lars and self.lars_type == stage:
+                d_norm = p.data.norm()
+                if d_norm > 1e-2:
+                    p.grad.mul_(d_norm / (p.grad.norm() + 1e-9))
 
     def curvature_step(self, L: _Layer):
         """curvature.py:166-191 (EMA incl. the l2 term) then :302-312 / :226-232."""
@@ -222,11 +247,19 @@ class OracleKFAC:
             L.l2_reg_ema = L.l2_reg
         else:
             L.l2_reg_ema = L.l2_reg * self.beta + L.l2_reg_ema * (1 - self.beta)
+        if self.use_max_ema:
+            # curvature.py:180-191: running element-wise maximum of the EMA
+            if getattr(L, 'ema_max', None) is None:
+                L.ema_max = [e.clone() for e in L.ema]
+            L.ema_max = [torch.maximum(e, m) for e, m in zip(L.ema, L.ema_max)]
         if not self.update_inv:
             return
         damping = self.damping + L.l2_reg_ema
         if L.is_diag:
-            L.inv = [ko.diag_inverse(e, damping) for e in L.ema]
+            # curvature.py:193-195: the diagonal classes invert the maximum when asked to; the
+            # Kronecker update_inv (:302-312) always reads the EMA itself
+            src = L.ema_max if self.use_max_ema else L.ema
+            L.inv = [ko.diag_inverse(e, damping) for e in src]
         else:
             L.inv = list(ko.kron_damped_inverse(L.ema[0], L.ema[1], damping))
 

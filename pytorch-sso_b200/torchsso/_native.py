@@ -213,15 +213,22 @@ def _timed_factor(fn, flops, nbytes):
 
 
 _workspaces = {}
+_retired_workspaces = []
 
 
 def workspace(device, nbytes: int) -> Optional[torch.Tensor]:
-    """Per-device scratch, grown on demand and reused (all launches are stream ordered)."""
+    """Per-device scratch, grown on demand and reused (all launches are stream ordered).  A buffer
+    that is outgrown is kept until the process ends: captured CUDA graphs hold its raw address."""
     if nbytes == 0:
         return None
     key = (device.type, device.index)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError('the factor scratch would have to grow during stream capture: run the '
+                                   'closure once eagerly before capturing it')
+            _retired_workspaces.append(buf)
         buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf

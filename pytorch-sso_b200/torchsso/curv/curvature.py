@@ -296,7 +296,10 @@ class KronCurvature(Curvature):
         self._update_ema_max()
 
     def update_inv(self):
-        self.pool.update_inv([self], with_std=False, use_max_ema=self.use_max_ema)
+        # always from the EMA: the reference's Kronecker update_inv ignores use_max_ema
+        # (torchsso/curv/curvature.py:302-312 reads self.ema; only the base / diagonal classes
+        # switch to ema_max, :193-195)
+        self.pool.update_inv([self], with_std=False)
         self._have.add('inv')
 
     def update_std(self):

@@ -65,6 +65,11 @@ def _weights(curv, n, device):
     w = curv.prob.detach().reshape(n)
     if w.dtype != torch.float32 or not w.is_contiguous():
         w = w.float().contiguous()
+    if nat.curvature_stream_enabled() and w.is_cuda:
+        # the hook's kernels run on the curvature stream while the closure, on its own stream, goes
+        # on to rebind ``prob`` for the next class: without this the caching allocator could hand the
+        # weight's block to the next allocation while a kernel here still reads it
+        w.record_stream(torch.cuda.current_stream(w.device))
     return w, 1.0
 
 
@@ -377,31 +382,64 @@ class DiagFisherConv2d(DiagCovConv2d, Fisher):
 
 
 # ---------------------------------------------------------------------------------------------
-# full-matrix placeholders (the reference ships them without a precondition step)
+# full-matrix curvatures: outside the accelerated path
 # ---------------------------------------------------------------------------------------------
-class _FullPlaceholder(Curvature):
+class CovLinear(Curvature):
+    """Full covariance of the per-sample gradients of a Linear layer, [(f_out (f_in+1))^2]
+    (torchsso/curv/cov/linear.py:5-25).  Not part of the accelerated path: built with plain torch
+    ops on the device, as the reference does; like the reference's, ``precondition_grad`` leaves
+    the gradient untouched."""
 
     def update_in_backward(self, grad_output):
-        pass
+        x = self._module.__dict__.get('data_input')
+        assert x is not None
+        n = x.shape[0]
+        x, g = x.float(), grad_output.float()
+        if self.bias:
+            x = torch.cat((x, x.new_ones((n, 1))), 1)
+        per_sample = torch.einsum('bi,bj->bij', g, x).reshape(n, -1)
+        self._generic['data'] = [per_sample.t() @ per_sample]
 
-    def step(self, update_std=False, update_inv=True):
-        pass
+    def update_ema(self):
+        first = self._ema_bookkeeping() or 'ema' not in self._generic
+        data, beta = self._generic['data'], self.ema_decay
+        if first:
+            self._generic['ema'] = [d.clone() for d in data]
+        else:
+            self._generic['ema'] = [d.mul(beta).add_(e, alpha=1 - beta) for d, e in zip(data, self._generic['ema'])]
+        self._have.add('ema')
+
+    def update_inv(self):
+        from ..utils import linalg
+        out = []
+        for e in self._generic['ema']:
+            m = e.clone()
+            m.diagonal().add_(self.damping)
+            out.append(linalg.inv(m))
+        self._generic['inv'] = out
 
     def precondition_grad(self, params):
         pass
 
 
-class CovLinear(_FullPlaceholder):
+class _NoFullCurvature(Curvature):
+    """The reference ships these classes as stubs (``update_in_backward`` is ``pass``,
+    torchsso/curv/cov/conv.py:6-13, torchsso/curv/cov/batchnorm.py:4-7,28-31) whose first ``step()``
+    fails on the missing data.  Fail at construction instead, with the reason."""
+
+    def __init__(self, module, *args, **kwargs):
+        raise NotImplementedError(
+            '%s: a full-matrix curvature for %s does not exist (a stub in the reference as well); '
+            "use the 'Kron' or 'Diag' shape for this module" % (type(self).__name__, type(module).__name__))
+
+
+class CovConv2d(_NoFullCurvature):
     pass
 
 
-class CovConv2d(_FullPlaceholder):
+class CovBatchNorm1d(_NoFullCurvature):
     pass
 
 
-class CovBatchNorm1d(_FullPlaceholder):
-    pass
-
-
-class CovBatchNorm2d(_FullPlaceholder):
+class CovBatchNorm2d(_NoFullCurvature):
     pass

@@ -90,10 +90,76 @@ class TinyVGG(nn.Module):
         return self.fc(x.reshape(x.shape[0], -1))
 
 
+class ConvNetB256(nn.Module):
+    """conv 3->64 5x5 p2, pool, conv 64->128 5x5 p2, pool, conv 128->256 3x3 p1, pool, fc 4096->512->10
+    (functional relu / max_pool2d; every layer has a bias): the single-GPU ConvNet configuration,
+    factor dimensions 76 / 1601 / 1153 / 4097 / 513."""
+    num_classes = 10
+
+    def __init__(self):
+        super().__init__()
+        self.c1 = nn.Conv2d(3, 64, 5, padding=2)
+        self.c2 = nn.Conv2d(64, 128, 5, padding=2)
+        self.c3 = nn.Conv2d(128, 256, 3, padding=1)
+        self.f1 = nn.Linear(4096, 512)
+        self.f2 = nn.Linear(512, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.c1(x)), 2)
+        x = F.max_pool2d(F.relu(self.c2(x)), 2)
+        x = F.max_pool2d(F.relu(self.c3(x)), 2)
+        return self.f2(F.relu(self.f1(x.reshape(x.shape[0], -1))))
+
+
+class VGG16Style(nn.Module):
+    """64-64-M-128-128-M-256x3-M-512x3-M-512x3-M conv stack (3x3, pad 1, bias, no norm layers)
+    then linear 512->100: the variational-inference configuration (factor dimensions up to 4609)."""
+    num_classes = 100
+    CFG = (64, 64, 'M', 128, 128, 'M', 256, 256, 256, 'M', 512, 512, 512, 'M', 512, 512, 512, 'M')
+
+    def __init__(self):
+        super().__init__()
+        convs, cin = [], 3
+        for v in self.CFG:
+            if v != 'M':
+                convs.append(nn.Conv2d(cin, v, 3, padding=1))
+                cin = v
+        self.convs = nn.ModuleList(convs)
+        self.fc = nn.Linear(512, 100)
+
+    def forward(self, x):
+        it = iter(self.convs)
+        for v in self.CFG:
+            x = F.max_pool2d(x, 2) if v == 'M' else F.relu(next(it)(x))
+        return self.fc(x.reshape(x.shape[0], -1))
+
+
 def make_model(name: str, seed: int = 0) -> nn.Module:
     cls = {'tiny_convnet': TinyConvNet, 'small_mlp': SmallMLP, 'mnist_mlp': MnistMLP,
-           'tiny_vgg': TinyVGG}[name]
-    return _fill_params(cls(), seed)
+           'tiny_vgg': TinyVGG, 'convnet_b256': ConvNetB256, 'vgg16_style': VGG16Style}[name]
+    return _fill_params(cls(), seed, scale=_INIT_SCALE.get(name, 1.0))
+
+
+# He-style gain for the deep ReLU stacks, so that activations neither vanish nor explode at depth
+_INIT_SCALE = {'vgg16_style': 2.0 ** 0.5}
+
+
+def summary_rows(d: int):
+    """Rows of a d x d (or length-d leading dimension) tensor kept by the large-model fixtures."""
+    return sorted({d // 2, d - 1})
+
+
+def summarize(t: torch.Tensor) -> dict:
+    """Compact fingerprint of a tensor too large to commit: Frobenius norm, sum, the diagonal of a
+    square matrix and a few full rows (a wrong scale, permutation or transpose changes them)."""
+    t = t.detach().cpu()
+    m = t.reshape(t.shape[0], -1) if t.dim() > 1 else t.reshape(1, -1)
+    out = {'norm': np.float64(m.double().norm().item()), 'sum': np.float64(m.double().sum().item())}
+    rows = summary_rows(m.shape[0])
+    out['rows'] = m[rows].numpy().astype(np.float32).copy()
+    if m.dim() == 2 and m.shape[0] == m.shape[1]:
+        out['diag'] = m.diagonal().numpy().astype(np.float32).copy()
+    return out
 
 
 def make_batch(shape, num_classes: int, seed: int):
@@ -111,3 +177,17 @@ def make_uniform(shape, seed: int) -> torch.Tensor:
 def make_normal(shape, seed: int) -> torch.Tensor:
     rng = np.random.default_rng(seed)
     return torch.from_numpy(rng.standard_normal(shape).astype(np.float32))
+
+
+def summary_error(gold, prefix: str, t: torch.Tensor) -> float:
+    """Worst relative deviation of tensor ``t`` from the fingerprint stored under ``prefix`` in a
+    fixture written with ``summarize``: Frobenius norm, the kept rows and the diagonal."""
+    got = summarize(t)
+    worst = abs(float(got['norm']) - float(gold[prefix + '/norm'])) / max(float(gold[prefix + '/norm']), 1e-30)
+    for key in ('rows', 'diag'):
+        if key in got:
+            a = np.asarray(got[key], dtype=np.float64)
+            b = np.asarray(gold[prefix + '/' + key], dtype=np.float64)
+            assert a.shape == b.shape, (prefix, key, a.shape, b.shape)
+            worst = max(worst, float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)))
+    return worst

@@ -237,6 +237,143 @@ def case_tiny_vgg_vi(torchsso):
     return out
 
 
+def dump_summary(out, tag, opt, with_std=False):
+    """Fingerprints (cases.summarize) instead of whole tensors, for the full-size models."""
+    for gi, group in enumerate(opt.param_groups):
+        curv = group['curv']
+        items = [('ema%d' % j, e) for j, e in enumerate(curv.ema)]
+        items += [('inv%d' % j, e) for j, e in enumerate(curv.inv)]
+        if with_std and curv.std is not None:
+            items += [('std%d' % j, e) for j, e in enumerate(curv.std)]
+        for j, p in enumerate(group['params']):
+            items += [('param%d' % j, p), ('grad%d' % j, p.grad)]
+        if 'mean' in group:
+            items += [('mean%d' % j, m) for j, m in enumerate(group['mean'])]
+        for name, t in items:
+            for k, v in cases.summarize(t).items():
+                out['%s/g%d/%s/%s' % (tag, gi, name, k)] = v
+
+
+def _convnet_b256_run(torchsso, dtype, out, prefix):
+    model = cases.make_model('convnet_b256', seed=11).to(dtype)
+    opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
+        model, 'Fisher', KRON, {'ema_decay': 0.95, 'damping': 1e-3}, lr=1e-2))
+    for t in range(3):
+        x, y = cases.make_batch((256, 3, 32, 32), 10, seed=1000 + t)
+        STATE['u'] = cases.make_uniform((1, 256), seed=2000 + t)
+        opt.update_inv = (t == 0)
+        closure = torchsso.get_closure_for_fisher(opt, model, x.to(dtype), y, approx_type='mc', num_mc=1)
+        loss, _ = opt.step(closure=closure)
+        out['%sstep%d/loss' % (prefix, t)] = np.float64(loss.item())
+        dump_summary(out, '%sstep%d' % (prefix, t), opt)
+
+
+def case_convnet_b256_fisher(torchsso):
+    """The single-GPU ConvNet configuration at its real shapes: batch 256 of 3x32x32, a fresh batch
+    every step (a fixed batch with stale inverses diverges in the reference itself), Fisher MC(1),
+    inverse on the first step only (the configuration inverts every 5th step).  The reference is
+    run twice: in fp32 as shipped (keys ``step*``) and with model and inputs in fp64 (keys
+    ``f64/step*``): the distance between the two is the reference's own rounding noise at these
+    sizes, the yardstick for any other fp32 implementation."""
+    out = {}
+    _convnet_b256_run(torchsso, torch.float32, out, '')
+    _convnet_b256_run(torchsso, torch.float64, out, 'f64/')
+    return out
+
+
+def case_vgg16_vi(torchsso):
+    """The variational-inference configuration at its real shapes: VGG-16-style stack, batch 128 of
+    3x32x32, dataset size 50000, prior variance 1, one weight sample per step, two steps (the
+    first step draws no noise because there is no posterior scale yet; the second one does)."""
+    model = cases.make_model('vgg16_style', seed=12).to(VGG_DTYPE)
+    opt = fix_hooks(torchsso.optim.VIOptimizer(
+        model, 50000, 'Cov', KRON, {'ema_decay': 0.95, 'damping': 1e-3}, lr=1e-3,
+        num_mc_samples=1, val_num_mc_samples=1, kl_weighting=VGG_KL, prior_variance=1))
+    real_randn_like = torch.randn_like
+    torch.randn_like = fake_randn_like
+    out = {}
+    try:
+        for t in range(2):
+            x, y = cases.make_batch((128, 3, 32, 32), 100, seed=3000 + t)
+            x = x.to(VGG_DTYPE)
+            STATE['noise_seed'], STATE['noise_count'] = 3100 + t, 0
+
+            def closure():
+                opt.zero_grad()
+                o = model(x)
+                loss = F.cross_entropy(o, y)
+                loss.backward()
+                return loss, o
+            loss, prob = opt.step(closure=closure)
+            out['step%d/loss' % t] = np.float64(loss.item())
+            out['step%d/prob_rows' % t] = prob.detach()[:4].numpy().copy()
+            dump_summary(out, 'step%d' % t, opt, with_std=True)
+    finally:
+        torch.randn_like = real_randn_like
+    return out
+
+
+# with 1.0 the posterior noise of the untrained network (its G factors are tiny, so their damped
+# inverses are huge) blows the second step's loss up to 1e6 in the reference itself
+VGG_KL = 0.01
+# fp64: in fp32 the reference's CPU inverse (LU) of the 4609-dimensional damped factors is not
+# numerically positive definite and its own update_std (Cholesky of that inverse) fails
+VGG_DTYPE = torch.float64
+
+
+def case_small_mlp_lars_wnorm(torchsso):
+    """LARS on the preconditioned gradient and weight normalisation after the update
+    (torchsso/optim/secondorder.py:282-330), then the same with LARS on the raw gradient."""
+    out = {}
+    for tag, kw in (('pre', dict(lars=True, lars_type='preconditioned', normalizing_weights=True)),
+                    ('raw', dict(lars=True, lars_type='raw', normalizing_weights=True, weight_scale=1.5,
+                                 momentum=0.9, momentum_type='raw'))):
+        model = cases.make_model('small_mlp', seed=6)
+        opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
+            model, 'Cov', KRON, {'ema_decay': 0.9, 'damping': 1e-2}, lr=5e-2, **kw))
+        for t in range(3):
+            x, y = cases.make_batch((8, 20), 4, seed=800 + t)
+
+            def closure():
+                opt.zero_grad()
+                o = model(x)
+                loss = F.cross_entropy(o, y)
+                loss.backward()
+                return loss, o
+            loss, _ = opt.step(closure=closure)
+            out['%s%d/loss' % (tag, t)] = np.float64(loss.item())
+            dump_groups(out, '%s%d' % (tag, t), opt)
+    return out
+
+
+def case_tiny_convnet_max_ema(torchsso):
+    """use_max_ema=True: the diagonal (BatchNorm) curvatures invert the running element-wise maximum
+    of the EMA, the Kronecker ones keep inverting the EMA itself (torchsso/curv/curvature.py:193-195
+    against :302-312)."""
+    model = cases.make_model('tiny_convnet', seed=7)
+    opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
+        model, 'Cov', KRON, {'ema_decay': 0.5, 'damping': 1e-3, 'use_max_ema': True}, lr=1e-2))
+    out = {}
+    for t in range(3):
+        x, y = cases.make_batch((6, 3, 8, 8), 5, seed=900 + t)
+        if t == 1:
+            x = x * 0.3        # smaller curvature on the middle step: EMA and its maximum part ways
+
+        def closure():
+            opt.zero_grad()
+            o = model(x)
+            loss = F.cross_entropy(o, y)
+            loss.backward()
+            return loss, o
+        loss, _ = opt.step(closure=closure)
+        out['step%d/loss' % t] = np.float64(loss.item())
+        dump_groups(out, 'step%d' % t, opt)
+        for gi, group in enumerate(opt.param_groups):
+            for j, e in enumerate(group['curv'].ema_max):
+                out['step%d/g%d/ema_max%d' % (t, gi, j)] = e.numpy().copy()
+    return out
+
+
 CASES = OrderedDict([
     ('tiny_convnet_fisher', case_tiny_convnet_fisher),
     ('tiny_convnet_fisher_exact', case_tiny_convnet_fisher_exact),
@@ -244,6 +381,10 @@ CASES = OrderedDict([
     ('tiny_convnet_diag', case_tiny_convnet_diag),
     ('tiny_vgg_vi', case_tiny_vgg_vi),
     ('mnist_mlp_fisher', case_mnist_mlp_fisher),
+    ('small_mlp_lars_wnorm', case_small_mlp_lars_wnorm),
+    ('tiny_convnet_max_ema', case_tiny_convnet_max_ema),
+    ('convnet_b256_fisher', case_convnet_b256_fisher),
+    ('vgg16_vi', case_vgg16_vi),
 ])
 
 

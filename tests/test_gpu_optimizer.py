@@ -137,6 +137,102 @@ def test_tiny_convnet_fisher_exact(torchsso_mod):
     check(gold, 'step0', opt, 1e-5, 1e-4)
 
 
+def test_tiny_convnet_fisher_exact_on_curvature_stream(torchsso_mod):
+    """Exact Fisher with the hooks' kernels on the side stream: the per-class weight vector is rebound
+    for every class while kernels of the previous class may still read the old one."""
+    torchsso = torchsso_mod
+    gold = load('tiny_convnet_fisher_exact')
+    model = cases.make_model('tiny_convnet', seed=2).cuda()
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON,
+                                              {'ema_decay': 1.0, 'damping': 1e-3}, lr=1e-2)
+    x, y = cases.make_batch((6, 3, 8, 8), 5, seed=300)
+    closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type=None)
+    torchsso.utils.set_curvature_stream(True)
+    try:
+        loss, _ = opt.step(closure=closure)
+    finally:
+        torchsso.utils.set_curvature_stream(False)
+    assert abs(loss.item() - float(gold['step0/loss'])) < 1e-4
+    check(gold, 'step0', opt, 1e-5, 1e-4)
+
+
+def test_small_mlp_lars_and_weight_normalisation(torchsso_mod):
+    """LARS (on the preconditioned and on the raw gradient) and weight normalisation
+    (torchsso/optim/secondorder.py:282-330) against the unmodified reference's vectors."""
+    torchsso = torchsso_mod
+    gold = load('small_mlp_lars_wnorm')
+    for tag, kw in (('pre', dict(lars=True, lars_type='preconditioned', normalizing_weights=True)),
+                    ('raw', dict(lars=True, lars_type='raw', normalizing_weights=True, weight_scale=1.5,
+                                 momentum=0.9, momentum_type='raw'))):
+        model = cases.make_model('small_mlp', seed=6).cuda()
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON, {'ema_decay': 0.9, 'damping': 1e-2},
+                                                  lr=5e-2, **kw)
+        for t in range(3):
+            x, y = cases.make_batch((8, 20), 4, seed=800 + t)
+            x, y = x.cuda(), y.cuda()
+
+            def closure():
+                opt.zero_grad()
+                o = model(x)
+                loss = F.cross_entropy(o, y)
+                loss.backward()
+                return loss, o
+            loss, _ = opt.step(closure=closure)
+            assert abs(loss.item() - float(gold['%s%d/loss' % (tag, t)])) < 1e-4
+            check(gold, '%s%d' % (tag, t), opt, 1e-5 * (1 + 3 * t), 1e-4 * (1 + 3 * t))
+
+
+def test_tiny_convnet_max_ema(torchsso_mod):
+    """use_max_ema: BatchNorm curvatures invert the running maximum of the EMA, Kronecker ones the
+    EMA itself, as the reference does (torchsso/curv/curvature.py:193-195 against :302-312)."""
+    torchsso = torchsso_mod
+    gold = load('tiny_convnet_max_ema')
+    model = cases.make_model('tiny_convnet', seed=7).cuda()
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON,
+                                              {'ema_decay': 0.5, 'damping': 1e-3, 'use_max_ema': True}, lr=1e-2)
+    for t in range(3):
+        x, y = cases.make_batch((6, 3, 8, 8), 5, seed=900 + t)
+        if t == 1:
+            x = x * 0.3
+        x, y = x.cuda(), y.cuda()
+
+        def closure():
+            opt.zero_grad()
+            o = model(x)
+            loss = F.cross_entropy(o, y)
+            loss.backward()
+            return loss, o
+        loss, _ = opt.step(closure=closure)
+        assert abs(loss.item() - float(gold['step%d/loss' % t])) < 1e-4
+        check(gold, 'step%d' % t, opt, 1e-5 * (1 + 3 * t), 1e-4 * (1 + 3 * t))
+        for gi, group in enumerate(opt.param_groups):
+            for j, e in enumerate(group['curv'].ema_max):
+                assert rel(e, gold['step%d/g%d/ema_max%d' % (t, gi, j)]) < 1e-5 * (1 + 3 * t)
+
+
+def test_full_matrix_curvature_classes(torchsso_mod):
+    """CovLinear builds the reference's full per-sample-gradient covariance with torch ops; the
+    classes the reference ships as empty stubs refuse construction with the reason."""
+    import torch.nn as nn
+    torchsso = torchsso_mod
+    lin = nn.Linear(5, 3).cuda()
+    curv = torchsso.CovLinear(lin, ema_decay=1.0, damping=1e-2)
+    x = cases.make_normal((7, 5), 3).cuda()
+    out = lin(x)
+    g = cases.make_normal((7, 3), 4).cuda()
+    out.backward(g)
+    xb = torch.cat([x, torch.ones(7, 1, device='cuda')], 1)
+    per = torch.einsum('bi,bj->bij', g, xb).reshape(7, -1)
+    assert rel(curv.data[0], (per.t() @ per).cpu().numpy()) < 1e-5
+    curv.step()
+    ref = torch.linalg.inv((per.t() @ per).double() + 1e-2 * torch.eye(18, device='cuda', dtype=torch.float64))
+    assert rel(curv.inv[0], ref.cpu().numpy()) < 1e-4
+    for cls, mod in ((torchsso.CovConv2d, nn.Conv2d(2, 2, 3)), (torchsso.CovBatchNorm2d, nn.BatchNorm2d(2)),
+                     (torchsso.CovBatchNorm1d, nn.BatchNorm1d(2))):
+        with pytest.raises(NotImplementedError, match='full-matrix curvature'):
+            cls(mod.cuda())
+
+
 def test_small_mlp_cov_momentum_l2_accsteps(torchsso_mod):
     torchsso = torchsso_mod
     gold = load('small_mlp_cov')
