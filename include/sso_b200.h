@@ -170,6 +170,29 @@ typedef struct {
 } sso_seg_rec;
 int sso_copy_segments(const sso_seg_rec* recs_dev, int n_recs, float scale, void* stream);
 
+/* 16-bit wire format of the exchange with per-array scaling.  A packed fp32 buffer is a sequence of
+ * arrays; the device table cuts it into runs of at most a few thousand elements of one array each.
+ *   sso_wire_absmax : maxima[array] <- max(maxima[array], max |x|) over the array's runs (clear
+ *                     `maxima` first); the caller sums the maxima over the ranks (one small all-reduce).
+ *   sso_wire_encode : out16[i] <- cast(buf[i] * 65000 / sums[array(i)])   (bf16 or fp16)
+ *   sso_wire_decode : out32[i] <- float(in16[i]) * sums[array(i)] / 65000
+ * An array whose summed maximum is zero or not finite travels unscaled.
+ * Replaces: torchsso/utils/chainer_communicators/pure_nccl_communicator.py:359-412
+ *           (_communication_scale / _rescale: per-array max-abs on side streams, all-reduce of the
+ *           maxima, scale to 65000 / sum before the cast, rescale after) and the cast kernels at
+ *           :415-429; here scaling is fused into the cast in both directions. */
+typedef struct {
+  int64_t offset;    /* first element of the run inside the packed buffer */
+  int64_t count;
+  int32_t array;     /* index into maxima / sums */
+  int32_t pad;
+} sso_wire_rec;
+int sso_wire_absmax(const float* buf, const sso_wire_rec* recs_dev, int n_recs, float* maxima, void* stream);
+int sso_wire_encode(const float* buf, const sso_wire_rec* recs_dev, int n_recs, const float* sums, void* out16,
+                    int dtype, void* stream);
+int sso_wire_decode(const void* in16, const sso_wire_rec* recs_dev, int n_recs, const float* sums, float* out32,
+                    int dtype, void* stream);
+
 /* Diagonal curvature of Linear / Conv2d layers: mean over samples of the squared per-sample weight
  * gradient (torchsso/curv/cov/linear.py:28-45, torchsso/curv/cov/conv.py:15-42; the reference builds
  * it from F.unfold + a batched matmul + elementwise squares):

@@ -9,9 +9,39 @@ thread_local std::string g_last_error;
 unsigned long long g_launches = 0;
 }  // namespace sso
 
+#include <map>
+#include <utility>
+
+namespace sso {
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> done;
+  int dev = -1;
+  SSO_CUDA_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(mu);
+  int& have = done[std::make_pair(kernel, dev)];
+  if (have >= bytes) return 0;
+  SSO_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  have = bytes;
+  return 0;
+}
+}  // namespace sso
+
 #include "factor_params.cuh"
 
 namespace sso {
+int factor_tma_set_wait_controls(long long cycles, int stall);
+int factor_tc_set_wait_controls(long long cycles, int stall);
+int engine_tc_set_wait_controls(long long cycles, int stall);
+static long long g_wait_kcycles = 0;   // 0 = default limit
+static int g_stall = 0;
+static int apply_wait_controls() {
+  const long long cycles = g_wait_kcycles * 1024;
+  int rc = factor_tma_set_wait_controls(cycles, g_stall);
+  if (!rc) rc = factor_tc_set_wait_controls(cycles, 0);
+  if (!rc) rc = engine_tc_set_wait_controls(cycles, g_stall);
+  return rc;
+}
 size_t factor_simt_workspace_bytes(int64_t rows, int64_t d);
 int factor_simt_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, cudaStream_t st);
 size_t factor_tc_workspace_bytes(int64_t rows, int64_t d);
@@ -30,7 +60,7 @@ static int g_tma_auto = 1;   // whether SSO_IMPL_AUTO may pick the TMA-fed tcgen
 
 using namespace sso;
 
-namespace sso { extern int g_kc_variant; extern int g_engine_tma; extern int g_chol_ksplit; extern int g_phase_lpt; }
+namespace sso { extern int g_engine_tma; extern int g_chol_ksplit; extern int g_phase_lpt; }
 
 extern "C" {
 
@@ -49,7 +79,11 @@ int sso_configure(const char* key, int value) {
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }
   if (k == "phase_lpt") { g_phase_lpt = value != 0; return 0; }
   if (k == "chol_ksplit") { g_chol_ksplit = (int)value; return 0; }
-  if (k == "kc_variant") { g_kc_variant = value; return 0; }
+  // failure-path controls, current device only: the limit of every bounded device-side wait in units of
+  // 1024 clocks (0 = the default of ~2 s), and a switch that makes the TMA producers of the factor and
+  // tile-task kernels issue no loads, so that the waits of their consumers run out
+  if (k == "wait_kcycles") { g_wait_kcycles = value < 0 ? 0 : value; return apply_wait_controls(); }
+  if (k == "inject_stall") { g_stall = value != 0; return apply_wait_controls(); }
   if (k == "tc_flush") { factor_tc_set_flush(value); return 0; }
   return fail(-1, "configure: unknown key %s", key);
 }

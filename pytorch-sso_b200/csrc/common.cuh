@@ -50,6 +50,15 @@ inline int fail(int code, const char* fmt, ...) {
       return ::sso::fail(-3, "launch of %s failed: %s", name, cudaGetErrorString(e__));     \
   } while (0)
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the device that is current when it is
+// called: remember per (kernel, device) what has been set (api.cu; thread safe).
+int ensure_dynamic_smem(const void* kernel, int bytes);
+#define SSO_ENSURE_SMEM(kernel, bytes)                                                   \
+  do {                                                                                   \
+    const int rc__ = ::sso::ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), (int)(bytes)); \
+    if (rc__) return rc__;                                                               \
+  } while (0)
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>

@@ -372,6 +372,58 @@ __global__ void __launch_bounds__(256) optimizer_tail_kernel(const sso_tail_rec*
 
 using namespace sso;
 
+// ---- 16-bit wire format of the exchange ---------------------------------------------------------
+// A packed fp32 buffer is a sequence of arrays; a chunk record names a run of elements of one array.
+// absmax: maxima[array] = max |x| (non-negative floats order like their bit patterns, so an integer
+// atomicMax gives a deterministic result).  encode: out16 = cast(x * 65000 / sums[array]).
+// decode: out32 = float(x16) * sums[array] / 65000.  `sums` holds the per-array maxima summed over
+// the ranks, so that the sum of the scaled values of all ranks stays inside the fp16 range.
+__global__ void __launch_bounds__(256) wire_absmax_kernel(const float* __restrict__ buf, const sso_wire_rec* __restrict__ recs,
+                                                          float* __restrict__ maxima) {
+  const sso_wire_rec r = recs[blockIdx.x];
+  const float* src = buf + r.offset;
+  float m = 0.f;
+  for (int64_t i = threadIdx.x; i < r.count; i += 256) m = fmaxf(m, fabsf(src[i]));
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float sm[8];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, sm[w]);
+    if (!(m == m)) m = __int_as_float(0x7f800000);     // a NaN in the array: scale by infinity's reciprocal
+    atomicMax(reinterpret_cast<int*>(maxima + r.array), __float_as_int(m));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ T wire_cast(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 wire_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half wire_cast<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) wire_encode_kernel(const float* __restrict__ buf, const sso_wire_rec* __restrict__ recs,
+                                                          const float* __restrict__ sums, T* __restrict__ out) {
+  const sso_wire_rec r = recs[blockIdx.x];
+  const float s = sums[r.array];
+  const float scale = (s > 0.f && s < __int_as_float(0x7f800000)) ? 65000.f / s : 1.f;
+  const float* src = buf + r.offset;
+  T* dst = out + r.offset;
+  for (int64_t i = threadIdx.x; i < r.count; i += 256) dst[i] = wire_cast<T>(src[i] * scale);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) wire_decode_kernel(const T* __restrict__ in, const sso_wire_rec* __restrict__ recs,
+                                                          const float* __restrict__ sums, float* __restrict__ out) {
+  const sso_wire_rec r = recs[blockIdx.x];
+  const float s = sums[r.array];
+  const float scale = (s > 0.f && s < __int_as_float(0x7f800000)) ? s / 65000.f : 1.f;
+  const T* src = in + r.offset;
+  float* dst = out + r.offset;
+  for (int64_t i = threadIdx.x; i < r.count; i += 256) dst[i] = to_f32<T>(src[i]) * scale;
+}
+
 extern "C" {
 
 int sso_optimizer_tail(const sso_tail_rec* recs_dev, int n_recs, void* stream) {
@@ -463,6 +515,42 @@ int sso_copy_segments(const sso_seg_rec* recs_dev, int n_recs, float scale, void
   if (n_recs == 0) return 0;
   copy_segments_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale);
   SSO_LAUNCH_OK("copy_segments_kernel");
+  return 0;
+}
+
+int sso_wire_absmax(const float* buf, const sso_wire_rec* recs_dev, int n_recs, float* maxima, void* stream) {
+  SSO_CHECK_ARG(buf && recs_dev && maxima && n_recs >= 0, "wire_absmax: bad argument");
+  if (n_recs == 0) return 0;
+  wire_absmax_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(buf, recs_dev, maxima);
+  SSO_LAUNCH_OK("wire_absmax_kernel");
+  return 0;
+}
+
+int sso_wire_encode(const float* buf, const sso_wire_rec* recs_dev, int n_recs, const float* sums, void* out16,
+                    int dtype, void* stream) {
+  SSO_CHECK_ARG(buf && recs_dev && sums && out16 && n_recs >= 0, "wire_encode: bad argument");
+  SSO_CHECK_ARG(dtype == SSO_BF16 || dtype == SSO_F16, "wire_encode: the wire type must be bf16 or fp16");
+  if (n_recs == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == SSO_BF16)
+    wire_encode_kernel<__nv_bfloat16><<<n_recs, 256, 0, st>>>(buf, recs_dev, sums, static_cast<__nv_bfloat16*>(out16));
+  else
+    wire_encode_kernel<__half><<<n_recs, 256, 0, st>>>(buf, recs_dev, sums, static_cast<__half*>(out16));
+  SSO_LAUNCH_OK("wire_encode_kernel");
+  return 0;
+}
+
+int sso_wire_decode(const void* in16, const sso_wire_rec* recs_dev, int n_recs, const float* sums, float* out32,
+                    int dtype, void* stream) {
+  SSO_CHECK_ARG(in16 && recs_dev && sums && out32 && n_recs >= 0, "wire_decode: bad argument");
+  SSO_CHECK_ARG(dtype == SSO_BF16 || dtype == SSO_F16, "wire_decode: the wire type must be bf16 or fp16");
+  if (n_recs == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == SSO_BF16)
+    wire_decode_kernel<__nv_bfloat16><<<n_recs, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in16), recs_dev, sums, out32);
+  else
+    wire_decode_kernel<__half><<<n_recs, 256, 0, st>>>(static_cast<const __half*>(in16), recs_dev, sums, out32);
+  SSO_LAUNCH_OK("wire_decode_kernel");
   return 0;
 }
 

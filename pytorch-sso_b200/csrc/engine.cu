@@ -652,6 +652,13 @@ static int upload(Plan& p, void* dev_mem, size_t dev_bytes) {
   return 0;
 }
 
+// A tensor-core tile task whose bounded wait gave up has set the plan's status word (and written NaN
+// tiles); surface it through the LAPACK-style info array the caller already reads: info[0] = -(1000 + code).
+__global__ void fold_status_kernel(const int* __restrict__ status, int* __restrict__ info) {
+  const int s = *status;
+  if (s != 0) info[0] = -(1000 + s);
+}
+
 static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* info, cudaStream_t st) {
   for (const sso_phase& ph : phases) {
     switch (ph.kind) {
@@ -861,6 +868,10 @@ int sso_kron_plan_run(int64_t plan, const float* damp_r_dev, int* info_dev, int 
     SSO_CHECK_ARG(!p->std_phases.empty(), "plan %lld has no std program", (long long)plan);
     const int rc = run_phases(*p, p->std_phases, info_dev, st);
     if (rc) return rc;
+  }
+  if (info_dev && p->d_status) {
+    fold_status_kernel<<<1, 1, 0, st>>>(p->d_status, info_dev);
+    SSO_LAUNCH_OK("fold_status_kernel");
   }
   return 0;
 }

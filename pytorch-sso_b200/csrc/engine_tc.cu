@@ -145,13 +145,17 @@ __device__ __forceinline__ void accumulate_and_store(const sso_tile_task& t, uin
   // The operand buffers are free now (the last commit has fired, so every MMA has read them):
   // stage the tile there, row r at r*129 floats, and write C (and its mirror) with whole
   // warps per row so that global accesses are coalesced.
+  // A wait that gave up leaves the accumulator incomplete: the tile is written all the same, as NaN, so
+  // that nothing downstream can mistake a stale or partial result for a valid one.
   const int r = q * 32 + lane;
-  if (ok) {
+  if (!ok) {
 #pragma unroll
-    for (int i = 0; i < 64; ++i) ct[r * CT_LD + half * 64 + i] = t.alpha * acc[i];
+    for (int i = 0; i < 64; ++i) acc[i] = __int_as_float(0x7fc00000);
   }
+#pragma unroll
+  for (int i = 0; i < 64; ++i) ct[r * CT_LD + half * 64 + i] = t.alpha * acc[i];
   asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
-  if (ok) {
+  {
     const bool sym = (t.flags & 4u) != 0;
     for (int rr = warp; rr < t.m; rr += EPI_WARPS) {
       float* crow = t.C + (int64_t)rr * t.ldc;
@@ -165,7 +169,7 @@ __device__ __forceinline__ void accumulate_and_store(const sso_tile_task& t, uin
   }
   // the mirror of an updated tile (beta != 0) reads back what other warps have just written
   if (t.C2 && t.beta != 0.f) asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
-  if (ok && t.C2) {
+  if (t.C2) {
     for (int c = warp; c < t.n; c += EPI_WARPS) {
       float* orow = t.C2 + (int64_t)c * t.ldc2;
       for (int rr = lane; rr < t.m; rr += 32)
@@ -575,10 +579,11 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tma_kernel(const sso_til
       asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                    ::"r"(dst + OPB), "l"(map_b), "r"(s * KS), "r"(0), "r"(fb) : "memory");
     };
-    if (lt == 0)
+    const bool producer = (lt == 0) && !g_inject_stall;     // stalled: nothing is ever loaded
+    if (producer)
       for (int s = 0; s < PREFETCH && s < nstages; ++s) issue(s);
     for (int s = 0; s < nstages; ++s) {
-      if (lt == 0 && s + PREFETCH < nstages) issue(s + PREFETCH);
+      if (producer && s + PREFETCH < nstages) issue(s + PREFETCH);
       const int rs = s % RAW_SLOTS, ls = s % LO_SLOTS;
       if (!mbar_wait(rawfull_bar(rs), (s / RAW_SLOTS) & 1, status, 46)) break;
       if (s >= LO_SLOTS && !mbar_wait(lofree_bar(ls), ((s / LO_SLOTS) - 1) & 1, status, 45)) break;
@@ -614,15 +619,11 @@ __global__ void __launch_bounds__(THREADS, 1) tile_task_tma_kernel(const sso_til
 
 }  // namespace etc
 
-int g_kc_variant = 0;
+int engine_tc_set_wait_controls(long long cycles, int stall) { return tc::set_wait_controls(cycles, stall); }
 
 int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, int count, int* status_dev, cudaStream_t st) {
   const size_t smem = (size_t)etc::KC_SMEM + 1024;
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_tma_kernel<5, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  SSO_ENSURE_SMEM((etc::tile_task_tma_kernel<5, 2, 3>), smem);
   etc::tile_task_tma_kernel<5, 2, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, reinterpret_cast<const etc::TaskMaps*>(maps_dev), status_dev);
   SSO_LAUNCH_OK("tile_task_tma_kernel");
   return 0;
@@ -630,27 +631,15 @@ int launch_tile_tasks_tma(const sso_tile_task* tasks_dev, const void* maps_dev, 
 
 int launch_tile_tasks_kc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st) {
   const size_t smem = (size_t)etc::KC_SMEM + 1024;
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel<5, 2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel<4, 3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_kc_kernel<4, 3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
-  if (g_kc_variant == 1) etc::tile_task_kc_kernel<4, 3, 2><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
-  else if (g_kc_variant == 2) etc::tile_task_kc_kernel<4, 3, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
-  else etc::tile_task_kc_kernel<5, 2, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
+  SSO_ENSURE_SMEM((etc::tile_task_kc_kernel<5, 2, 3>), smem);
+  etc::tile_task_kc_kernel<5, 2, 3><<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
   SSO_LAUNCH_OK("tile_task_kc_kernel");
   return 0;
 }
 
 int launch_tile_tasks_tc(const sso_tile_task* tasks_dev, int count, int* status_dev, cudaStream_t st) {
   const size_t smem = (size_t)etc::STAGES * etc::STAGE_BYTES + 1024;
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(etc::tile_task_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  SSO_ENSURE_SMEM(etc::tile_task_tc_kernel, (int)smem);
   etc::tile_task_tc_kernel<<<count, etc::THREADS, smem, st>>>(tasks_dev, status_dev);
   SSO_LAUNCH_OK("tile_task_tc_kernel");
   return 0;

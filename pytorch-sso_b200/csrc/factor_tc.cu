@@ -562,11 +562,7 @@ static int tc_launch_typed(FactorParams p, int tiles, cudaStream_t st) {
   using C = tc::Cfg<T>;
   tc::choose_splits(p.rows, tiles, C::KS, p.splits, p.rows_per_split);
   const size_t smem = (size_t)C::STAGES * 2 * C::PARTS * C::OPB + 128;
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(tc::factor_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  SSO_ENSURE_SMEM((tc::factor_tc_kernel<T>), smem);
   tc::factor_tc_kernel<T><<<dim3(tiles, p.splits), tc::THREADS, smem, st>>>(
       p, g_flush_stages > 0 ? g_flush_stages : C::FLUSH);
   SSO_LAUNCH_OK("factor_tc_kernel");
@@ -613,15 +609,13 @@ int factor_tc_run_reduce(const FactorParams& p, int tiles, cudaStream_t st) {
   const int pitch = width | 1;
   const size_t smem = (size_t)tc::RED_ROWS * pitch * sizeof(float);
   SSO_CHECK_ARG(smem <= 200 * 1024, "factor: kernel window too large for the finishing kernel");
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(tc::factor_tc_reduce, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    configured = true;
-  }
+  SSO_ENSURE_SMEM(tc::factor_tc_reduce, 200 * 1024);
   tc::factor_tc_reduce<<<dim3(ceil_div(p.d, tc::RED_ROWS), perm_groups + plain_groups), 256, smem, st>>>(p, perm_groups, pitch);
   SSO_LAUNCH_OK("factor_tc_reduce");
   return 0;
 }
+
+int factor_tc_set_wait_controls(long long cycles, int stall) { return tc::set_wait_controls(cycles, stall); }
 
 int factor_tc_flush_setting() { return g_flush_stages & 0xFFFF; }
 

@@ -181,7 +181,7 @@ factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CU
       }
       const uint32_t box_bytes = (uint32_t)g.kstage * 128u;
       const uint64_t tmap_ptr = reinterpret_cast<uint64_t>(&tmap);
-      bool ok = true;
+      bool ok = !g_inject_stall;       // stalled: nothing is ever loaded and the consumers' waits run out
       for (int s = 0; s < nstages && ok; ++s) {
         const int slot = s % STAGES;
         if (s >= STAGES) ok = mbar_wait(empty_bar(slot), ((s / STAGES) - 1) & 1, status, 4);
@@ -400,7 +400,7 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
       }
       const uint32_t box_bytes = (uint32_t)g.kstage * 128u;
       const uint64_t tmap_ptr = reinterpret_cast<uint64_t>(&tmap);
-      bool ok = true;
+      bool ok = !g_inject_stall;
       for (int s = 0; s < nstages && ok; ++s) {
         const int slot = s % STAGES;
         if (s >= STAGES) ok = mbar_wait(empty_bar(slot), ((s / STAGES) - 1) & 1, status, 34);
@@ -791,6 +791,8 @@ static bool choose_box(const FactorParams& p, GeomF& g) {
 
 }  // namespace tmaf
 
+int factor_tma_set_wait_controls(long long cycles, int stall) { return tc::set_wait_controls(cycles, stall); }
+
 static int g_tma_f32 = 0;     // fp32 inputs may use the TMA-fed 3xTF32 kernel
 void factor_tma_set_f32(int on) { g_tma_f32 = on != 0; }
 
@@ -838,11 +840,7 @@ static int factor_tma_f32_launch(FactorParams p, void* workspace, size_t workspa
   if (cr != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
 
   const size_t smem = (size_t)(RAW_SLOTS + LO_SLOTS) * STAGE_BYTES + 1024;
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  SSO_ENSURE_SMEM(factor_tma_f32_kernel, (int)smem);
   factor_tma_f32_kernel<<<dim3(tiles, p.splits), THREADS, smem, st>>>(p, g, tmap);
   SSO_LAUNCH_OK("factor_tma_f32_kernel");
   return factor_tc_run_reduce(p, tiles, st);
@@ -906,17 +904,9 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   if (cr != CUDA_SUCCESS) return fail(-5, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
 
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-  static bool configured = false;
-  if (!configured) {
-    SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
-  }
+  SSO_ENSURE_SMEM(factor_tma_kernel, (int)smem);
   if (pair) {
-    static bool configured2 = false;
-    if (!configured2) {
-      SSO_CUDA_OK(cudaFuncSetAttribute(factor_tma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      configured2 = true;
-    }
+    SSO_ENSURE_SMEM(factor_tma_pair_kernel, (int)smem);
     factor_tma_pair_kernel<<<dim3(2 * pair_blocks, p.splits), THREADS, smem, st>>>(p, g, tmap);
     SSO_LAUNCH_OK("factor_tma_pair_kernel");
     return factor_tc_run_reduce(p, tiles, st);

@@ -6,7 +6,22 @@
 namespace sso {
 namespace tc {
 
-constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s: a wait that lasts longer gives up
+// Every wait on an mbarrier is bounded: after g_wait_cycles clocks (~2 s by default) it gives up, records a
+// code in the kernel's status word and the kernel winds down normally.  The limit and the stall switch
+// below are per translation unit (each .cu that includes this header has its own copy, set through
+// set_wait_controls) and exist so that the give-up path can be exercised: with g_inject_stall set, the
+// TMA producers issue no loads, so every consumer wait runs out.
+constexpr long long WAIT_CYCLES_DEFAULT = 4000000000LL;
+static __device__ long long g_wait_cycles = WAIT_CYCLES_DEFAULT;
+static __device__ int g_inject_stall = 0;
+
+// Host side, current device: cycles <= 0 restores the default limit.
+static inline int set_wait_controls(long long cycles, int stall) {
+  if (cycles <= 0) cycles = WAIT_CYCLES_DEFAULT;
+  SSO_CUDA_OK(cudaMemcpyToSymbol(g_wait_cycles, &cycles, sizeof(cycles)));
+  SSO_CUDA_OK(cudaMemcpyToSymbol(g_inject_stall, &stall, sizeof(stall)));
+  return 0;
+}
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -32,8 +47,9 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = g_wait_cycles;
   while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > WAIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       if (status) atomicCAS(status, 0, code);
       return false;
     }

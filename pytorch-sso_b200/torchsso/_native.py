@@ -74,6 +74,9 @@ SIGNATURES = {
     'sso_tri_pack': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
     'sso_tri_unpack': (c_i32, [c_vp, c_i32, c_f32, c_i32, c_vp]),
     'sso_copy_segments': (c_i32, [c_vp, c_i32, c_f32, c_vp]),
+    'sso_wire_absmax': (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp]),
+    'sso_wire_encode': (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_vp]),
+    'sso_wire_decode': (c_i32, [c_vp, c_vp, c_i32, c_vp, c_vp, c_i32, c_vp]),
     'sso_kron_plan_dev_bytes': (c_sz, [c_i32, c_vp, c_i32]),
     'sso_kron_plan_create': (c_i64, [c_i32, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_i32, c_vp]),
     'sso_kron_plan_run': (c_i32, [c_i64, c_vp, c_vp, c_i32, c_i32, c_vp]),
@@ -123,6 +126,12 @@ def _check(rc):
     if rc < 0:
         raise RuntimeError('sso_b200: %s (code %d)' % (lib().sso_last_error().decode(), rc))
     return rc
+
+
+def _check_status(v):
+    if v < 0:
+        _check(v)
+    return int(v)
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -488,6 +497,35 @@ def copy_segments(table: torch.Tensor, scale: float = 1.0):
     _check(lib().sso_copy_segments(table.data_ptr(), table.numel() // SEG_REC_DTYPE.itemsize, scale, _stream()))
 
 
+WIRE_REC_DTYPE = np.dtype([('offset', np.int64), ('count', np.int64), ('array', np.int32), ('pad', np.int32)])
+
+
+def wire_records(offsets, counts, device, ids=None, chunk: int = 1 << 13) -> torch.Tensor:
+    """Device table for the sso_wire_* kernels: array ids[i] (default i) occupies
+    [offsets[i], offsets[i] + counts[i]) of the packed buffer."""
+    recs = []
+    for i, (off, n) in enumerate(zip(offsets, counts)):
+        for o in range(0, n, chunk):
+            recs.append((off + o, min(chunk, n - o), i if ids is None else ids[i], 0))
+    arr = np.array(recs, dtype=WIRE_REC_DTYPE)
+    return torch.from_numpy(arr.view(np.uint8).copy()).to(device)
+
+
+def wire_absmax(buf: torch.Tensor, table: torch.Tensor, maxima: torch.Tensor):
+    _check(lib().sso_wire_absmax(buf.data_ptr(), table.data_ptr(), table.numel() // WIRE_REC_DTYPE.itemsize,
+                                 maxima.data_ptr(), _stream()))
+
+
+def wire_encode(buf: torch.Tensor, table: torch.Tensor, sums: torch.Tensor, out16: torch.Tensor):
+    _check(lib().sso_wire_encode(buf.data_ptr(), table.data_ptr(), table.numel() // WIRE_REC_DTYPE.itemsize,
+                                 sums.data_ptr(), out16.data_ptr(), _dtype_code(out16), _stream()))
+
+
+def wire_decode(in16: torch.Tensor, table: torch.Tensor, sums: torch.Tensor, out32: torch.Tensor):
+    _check(lib().sso_wire_decode(in16.data_ptr(), table.data_ptr(), table.numel() // WIRE_REC_DTYPE.itemsize,
+                                 sums.data_ptr(), out32.data_ptr(), _dtype_code(in16), _stream()))
+
+
 def _i64(vals):
     return (c_i64 * len(vals))(*[int(v) for v in vals])
 
@@ -517,6 +555,11 @@ class Plan:
                 _lib.sso_plan_destroy(self.handle)
         except Exception:
             pass
+
+    def status(self) -> int:
+        """0, or the code of the first device-side wait of a tensor-core tile task that gave up in any
+        run of this plan so far (synchronises; the tiles of such a task were written as NaN)."""
+        return _check_status(lib().sso_plan_status(self.handle))
 
     # introspection (host side)
     def phases(self):

@@ -199,14 +199,25 @@ class FactorPool:
                 del self._plans[k]
 
     def check_info(self):
-        """Raise if the last factorisation met a non-positive pivot (synchronises)."""
+        """Raise if the last factorisation met a non-positive pivot, or if a bounded device-side wait of
+        any engine plan of this pool ever gave up (its tiles were written as NaN).  Synchronises."""
+        for key, ent in self._plans.items():
+            plan = ent[0] if isinstance(ent, tuple) else ent
+            code = plan.status()
+            if code:
+                raise RuntimeError('a device-side wait of the %s plan gave up (code %d): its results are NaN'
+                                   % ({'inv': 'inverse', 'pre': 'precondition', 'smp': 'sampling'}[key[0]], code))
         if self.last_info is None:
             return
-        bad = torch.nonzero(self.last_info).flatten()
+        info = self.last_info.cpu()
+        if int(info[0]) <= -1000:
+            raise RuntimeError('a device-side wait of the inverse plan gave up (code %d): its results are NaN'
+                               % (-int(info[0]) - 1000))
+        bad = torch.nonzero(info).flatten()
         if bad.numel():
             i = int(bad[0])
             raise RuntimeError('curvature matrix %d (%s pass) is not positive definite at row %d'
-                               % (i // 2, 'inverse' if i % 2 == 0 else 'cholesky', int(self.last_info[i])))
+                               % (i // 2, 'inverse' if i % 2 == 0 else 'cholesky', int(info[i])))
 
     def precondition(self, curvs: Sequence, grads: Sequence[Sequence[torch.Tensor]]):
         """grads[i] = [dW (, db)] of layer i, fp32 contiguous; replaced by G^-1 [dW|db] A^-1."""

@@ -82,11 +82,28 @@ class DevicePacker:
                 off += k
             seg_tab = nat.seg_records(flat_pairs, buf.device) if flat_pairs else None
             tri_tab = nat.tri_records(tri_mats, buf, tri_offs) if tri_mats else None
-            if len(self._tables) > 64:
-                self._tables.clear()
+            while len(self._tables) >= 256:      # oldest first; one model needs 2 x world entries
+                self._tables.pop(next(iter(self._tables)))
             ent = (seg_tab, tri_tab, strided)
             self._tables[key] = ent
         return ent
+
+    # ---- 16-bit wire format (per-array scaling fused into the casts) ---------------------------
+    def wire_table(self, offsets, counts, ids, device):
+        from torchsso import _native as nat
+        return nat.wire_records(offsets, counts, device, ids=ids)
+
+    def wire_absmax(self, buf, table, maxima):
+        from torchsso import _native as nat
+        nat.wire_absmax(buf, table, maxima)
+
+    def wire_encode(self, buf, table, sums, out16):
+        from torchsso import _native as nat
+        nat.wire_encode(buf, table, sums, out16)
+
+    def wire_decode(self, in16, table, sums, out32):
+        from torchsso import _native as nat
+        nat.wire_decode(in16, table, sums, out32)
 
     def pack(self, arrays, buf, offset, scale):
         from torchsso import _native as nat
@@ -113,11 +130,16 @@ class DevicePacker:
 
 class KFACCommunicator:
 
-    def __init__(self, group=None, packer=None, wire_dtype=None):
+    def __init__(self, group=None, packer=None, wire_dtype=None, wire_scaling=True):
         """``wire_dtype`` (torch.bfloat16 / torch.float16, default None = fp32): the packed buffers
         cross the links in that type (half the bytes), as the reference's ``allreduce_grad_dtype``
-        option does (pure_nccl_communicator.py:359-412).  It rounds factors and gradients to 8 / 11
-        mantissa bits, so it is off in every parity configuration."""
+        option does, with its per-array scaling (pure_nccl_communicator.py:359-412): the maximum
+        magnitude of every array is taken on each rank, the maxima are summed over the ranks (one small
+        all-reduce), every array is scaled to 65000 / sum on the way into the 16-bit buffer and scaled
+        back on the way out, so arrays of very different magnitude (G factors carry an n^2, late-layer
+        gradients are tiny) neither overflow nor underflow.  ``wire_scaling=False`` is the plain cast.
+        It still rounds factors and gradients to 8 / 11 mantissa bits, so it is off in every parity
+        configuration."""
         if not dist.is_initialized():
             raise RuntimeError('torch.distributed is not initialised')
         self.group = group
@@ -127,6 +149,9 @@ class KFACCommunicator:
         if wire_dtype not in (None, torch.float32, torch.bfloat16, torch.float16):
             raise ValueError('wire_dtype must be None, torch.bfloat16 or torch.float16')
         self.wire_dtype = None if wire_dtype == torch.float32 else wire_dtype
+        self.wire_scaling = bool(wire_scaling)
+        self._wire_layouts = {}
+        self._extract_cache = {}
         self.indices = None
         self._optimizer = None
         self._bufs = {}
@@ -163,7 +188,7 @@ class KFACCommunicator:
             if local:
                 self.packer.pack(local, send, r * seg, 1.0 / self.size)
         if self.size > 1:
-            self._reduce_scatter(recv, send, seg)
+            self._reduce_scatter(recv, send, seg, arrays)
         else:
             recv = send[:seg]
         if arrays[self.rank]:
@@ -181,7 +206,7 @@ class KFACCommunicator:
         if arrays[self.rank]:
             self.packer.pack(arrays[self.rank], send, 0, 1.0)
         if self.size > 1:
-            self._all_gather(recv, send, seg)
+            self._all_gather(recv, send, seg, arrays)
         else:
             recv = send
         for r, local in enumerate(arrays):
@@ -192,27 +217,75 @@ class KFACCommunicator:
     def _wire(self, name, like):
         b = self._bufs.get(name)
         if b is None or b.numel() < like.numel() or b.device != like.device or b.dtype != self.wire_dtype:
-            b = torch.empty(like.numel(), dtype=self.wire_dtype, device=like.device)
+            b = torch.zeros(like.numel(), dtype=self.wire_dtype, device=like.device)
             self._bufs[name] = b
         return b[:like.numel()]
 
-    def _reduce_scatter(self, recv, send, seg):
-        if self.wire_dtype is not None:
-            send16, recv16 = self._wire('rsv_send16', send), self._wire('rsv_recv16', recv)
-            send16.copy_(send)
-            self._reduce_scatter_raw(recv16, send16, seg)
-            recv.copy_(recv16)
-            return
-        self._reduce_scatter_raw(recv, send, seg)
+    def _wire_layout(self, arrays: Arrays, seg: int, device):
+        """(table over the whole [world x seg] buffer, table over this rank's segment alone, maxima
+        vector): array i of the flattened per-owner lists has index i in the maxima."""
+        key = (seg, tuple((t.data_ptr(), tri) for local in arrays for t, tri in local))
+        ent = self._wire_layouts.get(key)
+        if ent is None:
+            offs, cnts, ids, l_offs, l_cnts, l_ids = [], [], [], [], [], []
+            i = 0
+            for r, local in enumerate(arrays):
+                off = 0
+                for t, tri in local:
+                    k = packed_numel(t, tri)
+                    offs.append(r * seg + off); cnts.append(k); ids.append(i)
+                    if r == self.rank:
+                        l_offs.append(off); l_cnts.append(k); l_ids.append(i)
+                    off += k
+                    i += 1
+            whole = self.packer.wire_table(offs, cnts, ids, device)
+            own = self.packer.wire_table(l_offs, l_cnts, l_ids, device) if l_ids else None
+            maxima = torch.zeros(max(i, 1), dtype=torch.float32, device=device)
+            while len(self._wire_layouts) >= 8:
+                self._wire_layouts.pop(next(iter(self._wire_layouts)))
+            ent = (whole, own, maxima)
+            self._wire_layouts[key] = ent
+        return ent
 
-    def _all_gather(self, recv, send, seg):
-        if self.wire_dtype is not None:
-            send16, recv16 = self._wire('agv_send16', send), self._wire('agv_recv16', recv)
-            send16.copy_(send)
-            self._all_gather_raw(recv16, send16, seg)
-            recv.copy_(recv16)
+    def _reduce_scatter(self, recv, send, seg, arrays=None):
+        if self.wire_dtype is None:
+            self._reduce_scatter_raw(recv, send, seg)
             return
-        self._all_gather_raw(recv, send, seg)
+        send16, recv16 = self._wire('rsv_send16', send), self._wire('rsv_recv16', recv)
+        if self.wire_scaling and arrays is not None:
+            whole, own, maxima = self._wire_layout(arrays, seg, send.device)
+            maxima.zero_()
+            self.packer.wire_absmax(send, whole, maxima)
+            dist.all_reduce(maxima, op=dist.ReduceOp.SUM, group=self.group)
+            self.packer.wire_encode(send, whole, maxima, send16)
+            self._reduce_scatter_raw(recv16, send16, seg)
+            if own is not None:
+                self.packer.wire_decode(recv16, own, maxima, recv)
+            return
+        send16.copy_(send)
+        self._reduce_scatter_raw(recv16, send16, seg)
+        recv.copy_(recv16)
+
+    def _all_gather(self, recv, send, seg, arrays=None):
+        if self.wire_dtype is None:
+            self._all_gather_raw(recv, send, seg)
+            return
+        send16, recv16 = self._wire('agv_send16', send), self._wire('agv_recv16', recv)
+        if self.wire_scaling and arrays is not None:
+            whole, own, maxima = self._wire_layout(arrays, seg, send.device)
+            maxima.zero_()
+            if own is not None:
+                self.packer.wire_absmax(send, own, maxima)
+            # only the owner contributes a non-zero maximum for an array, so the sum is the owner's value
+            dist.all_reduce(maxima, op=dist.ReduceOp.SUM, group=self.group)
+            if own is not None:
+                self.packer.wire_encode(send, own, maxima, send16)
+            self._all_gather_raw(recv16, send16, seg)
+            self.packer.wire_decode(recv16, whole, maxima, recv)
+            return
+        send16.copy_(send)
+        self._all_gather_raw(recv16, send16, seg)
+        recv.copy_(recv16)
 
     def _reduce_scatter_raw(self, recv, send, seg):
         backend = dist.get_backend(self.group)
@@ -235,6 +308,14 @@ class KFACCommunicator:
         """Arrays per owner rank: for every owned group, in order, what each extractor names:
         'grad' (flat-pool gradient views), 'param.data', 'mean.data', 'curv.data', 'curv.std'."""
         opt = self._optimizer
+        # the lists depend on which tensors exist, not on their values: rebuild only when the groups'
+        # storage changes (the pools and the flat gradient buffer are allocated once)
+        # (lists that name parameter storage are rebuilt every time: a caller may swap ``p.data``)
+        cacheable = not any(ex in ('param.data', 'mean.data', 'curv.std') for ex in extractors)
+        key = (id(param_groups), tuple(extractors), id(getattr(opt, 'pool', None)), id(getattr(opt, '_grad_flat', None)))
+        hit = self._extract_cache.get(key) if cacheable else None
+        if hit is not None and hit[0] is param_groups:
+            return hit[1]
         arrays = []
         for local_indices in self.indices:
             local = []
@@ -260,6 +341,10 @@ class KFACCommunicator:
                     else:
                         raise ValueError('unknown extractor %r' % (ex,))
             arrays.append(local)
+        if cacheable:
+            while len(self._extract_cache) >= 16:
+                self._extract_cache.pop(next(iter(self._extract_cache)))
+            self._extract_cache[key] = (param_groups, arrays)
         return arrays
 
     def reduce_scatterv_data(self, param_groups, extractors):
@@ -280,6 +365,6 @@ class KFACCommunicator:
                     curv._have.add('std')
 
 
-def create_communicator(group=None, packer=None, wire_dtype=None, **unused):
+def create_communicator(group=None, packer=None, wire_dtype=None, wire_scaling=True, **unused):
     """Communicator over the default (or given) process group; one process per GPU, NCCL backend."""
-    return KFACCommunicator(group=group, packer=packer, wire_dtype=wire_dtype)
+    return KFACCommunicator(group=group, packer=packer, wire_dtype=wire_dtype, wire_scaling=wire_scaling)

@@ -134,14 +134,48 @@ class VGG16Style(nn.Module):
         return self.fc(x.reshape(x.shape[0], -1))
 
 
+class UnevenNet(nn.Module):
+    """Nine convolutions and four linear layers of very different sizes (factor dimensions 19 ... 361),
+    with and without bias, three BatchNorm layers: owner assignment by inverse cost and by contiguous
+    ranges give different, unbalanced partitions on 2, 4 and 8 ranks."""
+    num_classes = 7
+    WIDTHS = (6, 24, 8, 40, 12, 12, 32, 6, 16)
+
+    def __init__(self):
+        super().__init__()
+        convs, bns, cin = [], {}, 2
+        for i, w in enumerate(self.WIDTHS):
+            convs.append(nn.Conv2d(cin, w, 3 if i % 3 else 1, padding=1 if i % 3 else 0, bias=(i % 2 == 0)))
+            if i in (1, 4, 7):
+                bns[str(i)] = nn.BatchNorm2d(w)
+            cin = w
+        self.convs = nn.ModuleList(convs)
+        self.bns = nn.ModuleDict(bns)
+        self.f1 = nn.Linear(cin * 4, 48)
+        self.f2 = nn.Linear(48, 20, bias=False)
+        self.f3 = nn.Linear(20, 30)
+        self.f4 = nn.Linear(30, 7)
+
+    def forward(self, x):
+        for i, conv in enumerate(self.convs):
+            x = conv(x)
+            if str(i) in self.bns:
+                x = self.bns[str(i)](x)
+            x = F.relu(x)
+            if i in (2, 5):
+                x = F.max_pool2d(x, 2)
+        x = x.reshape(x.shape[0], -1)
+        return self.f4(F.relu(self.f3(F.relu(self.f2(F.relu(self.f1(x)))))))
+
+
 def make_model(name: str, seed: int = 0) -> nn.Module:
     cls = {'tiny_convnet': TinyConvNet, 'small_mlp': SmallMLP, 'mnist_mlp': MnistMLP,
-           'tiny_vgg': TinyVGG, 'convnet_b256': ConvNetB256, 'vgg16_style': VGG16Style}[name]
+           'tiny_vgg': TinyVGG, 'convnet_b256': ConvNetB256, 'vgg16_style': VGG16Style, 'uneven_net': UnevenNet}[name]
     return _fill_params(cls(), seed, scale=_INIT_SCALE.get(name, 1.0))
 
 
 # He-style gain for the deep ReLU stacks, so that activations neither vanish nor explode at depth
-_INIT_SCALE = {'vgg16_style': 2.0 ** 0.5}
+_INIT_SCALE = {'vgg16_style': 2.0 ** 0.5, 'uneven_net': 2.0 ** 0.5}
 
 
 def summary_rows(d: int):

@@ -1,8 +1,10 @@
-"""Two-GPU data-parallel K-FAC against its single-process equivalent.
+"""Data-parallel K-FAC on 2, 4 and 8 GPUs against its single-process equivalent.
 
 Grads and curvature data are averaged over ranks with equal weights, so N-rank data parallel
 training equals one process with ``acc_steps = N`` fed the N shards in rank order (batch-norm
-statistics are per shard in both).  Needs two GPUs; skipped otherwise."""
+statistics are per shard in both).  Each case needs as many GPUs as ranks and is skipped
+otherwise.  The model has 13 Kronecker layers of very different sizes, so the two ownership
+rules give different, unbalanced partitions with padded segments."""
 import os
 import socket
 
@@ -29,20 +31,20 @@ def _free_port():
 
 
 def _shard(step, rank):
-    x, y = cases.make_batch((6, 3, 8, 8), 5, seed=900 + 10 * step + rank)
+    x, y = cases.make_batch((6, 2, 8, 8), 7, seed=900 + 10 * step + rank)
     u = cases.make_uniform((1, 6), seed=950 + 10 * step + rank)
     return x, y, u
 
 
-def _run_single(device):
+def _run_single(device, world):
     import torchsso
-    model = cases.make_model('tiny_convnet', seed=1).to(device)
-    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=1e-2, acc_steps=2)
+    model = cases.make_model('uneven_net', seed=1).to(device)
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=1e-2, acc_steps=world)
     state = {}
     torchsso.curv.fisher.sample_targets = \
         lambda prob, num_mc: inverse_cdf_targets(prob.detach().float().cpu(), state['u']).to(prob.device)
     for step in range(STEPS):
-        for rank in range(2):
+        for rank in range(world):
             x, y, state['u'] = _shard(step, rank)
             closure = torchsso.get_closure_for_fisher(opt, model, x.to(device), y.to(device),
                                                       approx_type='mc', num_mc=1)
@@ -50,7 +52,7 @@ def _run_single(device):
     return [p.detach().cpu().clone() for p in model.parameters()]
 
 
-def _worker(rank, world, port, balance, ret):
+def _worker(rank, world, port, balance, ret, wire=None, scaling=True):
     import torch.distributed as dist
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
@@ -60,9 +62,10 @@ def _worker(rank, world, port, balance, ret):
     dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
     try:
         import torchsso
-        model = cases.make_model('tiny_convnet', seed=1).to(device)
+        model = cases.make_model('uneven_net', seed=1).to(device)
+        comm = torchsso.utils.create_communicator(wire_dtype=wire, wire_scaling=scaling)
         opt = torchsso.optim.DistributedSecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=1e-2,
-                                                             balance=balance)
+                                                             balance=balance, comm=comm)
         state = {}
         torchsso.curv.fisher.sample_targets = \
             lambda prob, num_mc: inverse_cdf_targets(prob.detach().float().cpu(), state['u']).to(prob.device)
@@ -74,24 +77,50 @@ def _worker(rank, world, port, balance, ret):
         opt.pool.check_info()
         assert sorted(i for part in opt.indices for i in part) == list(range(len(opt.param_groups)))
         ret[rank] = [p.detach().cpu().clone() for p in model.parameters()]
+        ret['indices'] = [list(p) for p in opt.indices]
     finally:
         dist.destroy_process_group()
 
 
+def _worst(got, ref):
+    return max(((g - e).norm() / e.norm().clamp_min(1e-12)).item() for g, e in zip(got, ref))
+
+
+@pytest.mark.parametrize('world', [2, 4, 8])
 @pytest.mark.parametrize('balance', ['inverse_cost', 'contiguous'])
-def test_two_gpu_data_parallel_equals_accumulation(balance):
-    if torch.cuda.device_count() < 2:
-        pytest.skip('needs two GPUs')
-    ref = _run_single(torch.device('cuda', 0))
+def test_data_parallel_equals_accumulation(world, balance):
+    if torch.cuda.device_count() < world:
+        pytest.skip('needs %d GPUs' % world)
+    ref = _run_single(torch.device('cuda', 0), world)
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(2, _free_port(), balance, ret), nprocs=2, join=True)
-    for rank in range(2):
-        for got, exp in zip(ret[rank], ref):
-            err = ((got - exp).norm() / exp.norm().clamp_min(1e-12)).item()
-            assert err < 2e-5, (rank, err)
-    for a, b in zip(ret[0], ret[1]):
-        assert torch.equal(a, b), 'ranks disagree after the all-gather'
+    mp.spawn(_worker, args=(world, _free_port(), balance, ret), nprocs=world, join=True)
+    sizes = [len(p) for p in ret['indices']]
+    assert sum(sizes) == 16
+    for rank in range(world):
+        assert _worst(ret[rank], ref) < 2e-5, (rank, _worst(ret[rank], ref))
+    for rank in range(1, world):
+        for a, b in zip(ret[0], ret[rank]):
+            assert torch.equal(a, b), 'ranks disagree after the all-gather'
+
+
+def test_two_gpu_half_precision_wire_with_scaling():
+    """fp16 on the wire: the gradients of this network (~1e-3) and its G factors (carrying n^2) span
+    orders of magnitude; with per-array scaling the update stays within fp16 rounding of the fp32
+    exchange, and it is closer than the plain cast."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    ref = _run_single(torch.device('cuda', 0), 2)
+    mgr = mp.Manager()
+    errs = {}
+    for scaling in (True, False):
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(2, _free_port(), 'inverse_cost', ret, torch.float16, scaling), nprocs=2, join=True)
+        errs[scaling] = _worst(ret[0], ref)
+        for a, b in zip(ret[0], ret[1]):
+            assert torch.equal(a, b)
+    assert errs[True] < 2e-2, errs
+    assert errs[True] <= errs[False] or not (errs[False] == errs[False]), errs
 
 
 # ---------------------------------------------------------------------------------------------

@@ -24,25 +24,38 @@ def _both(nat, x, bias, alpha, beta, impl, seed_out):
     nat._check(L.sso_factor_syrk(x.data_ptr(), nat._dtype_code(x), rows, cols, x.stride(0), x.stride(1),
                                  int(bias), None, alpha, beta, ref.data_ptr(), d, ws.data_ptr(), nbytes,
                                  impl, stream))
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]     # sees allocations made behind torch's back as well
     nat._check(L.sso_factor_syrk_noalloc(x.data_ptr(), nat._dtype_code(x), rows, cols, x.stride(0),
                                          x.stride(1), int(bias), None, alpha, beta, got.data_ptr(), d,
                                          impl, stream))
     assert torch.cuda.memory_allocated() == before
     torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before, 'the call took device memory'
+    # and against the CPU oracle, so that two wrong-but-equal results cannot pass
+    from oracle import kfac_oracle as ko
+    exact = ko.linear_factor_A(x.double().cpu(), bias) * (alpha * rows) + beta * init.double().cpu()
+    err = ((got.double().cpu() - exact).norm() / exact.norm()).item()
+    assert err < 1e-5, err
     return ref, got
 
 
-@pytest.mark.parametrize('impl_name', ['IMPL_SIMT', 'IMPL_TCGEN05'])
+@pytest.mark.parametrize('impl_name', ['IMPL_SIMT', 'IMPL_TCGEN05', 'IMPL_AUTO', 'IMPL_TMA'])
 def test_noalloc_entry_matches_regular_entry_twice(impl_name):
     from torchsso import _native as nat
     impl = getattr(nat, impl_name)
     g = torch.Generator(device='cuda').manual_seed(11)
     # first problem: many row splits, so the shared scratch is left full of partial tiles
     x1 = torch.randn((20000, 96), device='cuda', generator=g)
-    ref1, got1 = _both(nat, x1, True, 1.0 / 20000, 0.0, impl, 1)
-    # second problem, different shape and an accumulate (beta = 1) on top of existing contents
-    x2 = (torch.randn((3000, 200), device='cuda', generator=g) + 0.5).bfloat16()
+    bias1 = True
+    if impl == nat.IMPL_TMA:      # the TMA-fed kernel takes 16-bit rows of a multiple of 64 columns, no ones column
+        x1, bias1 = torch.randn((20000, 128), device='cuda', generator=g).bfloat16(), False
+    ref1, got1 = _both(nat, x1, bias1, 1.0 / 20000, 0.0, impl, 1)
+    # second problem, different shape and an accumulate (beta = 1) on top of existing contents; 192 bf16
+    # columns take the automatic choice to the TMA-fed kernel
+    cols2 = 200 if impl in (nat.IMPL_SIMT, nat.IMPL_TCGEN05) else 192
+    x2 = (torch.randn((3000, cols2), device='cuda', generator=g) + 0.5).bfloat16()
     ref2, got2 = _both(nat, x2, False, 1.0 / 3000, 1.0, impl, 2)
     for ref, got in ((ref1, got1), (ref2, got2)):
         assert torch.isfinite(got).all()
