@@ -382,10 +382,13 @@ def run_gpu_arm(args):
     first = None
     if args.graph:
         opt.update_inv = True
-        loss0, _ = opt.step(closure=closure)            # eager first step: builds pools, plans, scratch
+        # eager first step: builds pools, plans, scratch.  Only the value of the loss is kept: a live loss
+        # tensor would pin this step's autograd graph, whose gradient-accumulation nodes belong to the
+        # default stream and would then break the capture below
+        loss0 = float(opt.step(closure=closure)[0].detach())
         if world == 1:
             kron_groups = [g for g in opt.param_groups if isinstance(g['curv'], torchsso.KronCurvature)]
-            first = {'loss': float(loss0), 'stem_A_norm': float(kron_groups[0]['curv'].ema[0].double().norm()),
+            first = {'loss': loss0, 'stem_A_norm': float(kron_groups[0]['curv'].ema[0].double().norm()),
                      'layer1_conv1_A_norm': float(kron_groups[1]['curv'].ema[0].double().norm())}
         # the model has no in-place activations, so the hooks' kernels may run beside it
         torchsso.utils.set_curvature_stream(args.side_stream)

@@ -90,7 +90,9 @@ int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols,
  * The split-partial scratch is a 16 MiB array inside the library image: every GPU that loads the
  * library holds it until the process exits.  Shapes whose scratch need (sso_factor_workspace_bytes)
  * is larger are rejected with an error and nothing is launched.  The first call on a device
- * resolves the array's device address; make it before any stream capture begins.  All calls on a
+ * resolves the array's device address; make it before any stream capture begins.  Where the CUDA
+ * driver loads modules lazily, that first call is also when it sets the 16 MiB aside on the device
+ * (free device memory drops by that amount, once; no later call changes it).  All calls on a
  * device share the array: calls whose GPU work can overlap (other streams or threads) race and
  * must be serialised by the caller; calls on one stream are safe.  Nothing on this path calls
  * cudaMalloc / cudaFree or an allocating library routine. */

@@ -162,7 +162,10 @@ int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols, int64_
 //  * Problems whose scratch need (sso_factor_workspace_bytes) exceeds it are rejected with an
 //    error; nothing is launched.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
-//    with that device current).  Make that first call before starting any stream capture.
+//    with that device current).  Make that first call before starting any stream capture.  With
+//    CUDA's lazy module loading that look-up is also the moment the driver sets the array's 16 MiB
+//    aside on that device (free device memory drops by that much, once); no later call changes the
+//    amount of free device memory.
 //  * All calls on a device share the one array and it keeps the previous call's contents.  The
 //    kernels overwrite every partial tile before reading it and the status word is cleared on the
 //    stream at the start of each call, so back-to-back calls on ONE stream are safe; calls whose

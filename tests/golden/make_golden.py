@@ -352,7 +352,7 @@ def case_tiny_convnet_max_ema(torchsso):
     against :302-312)."""
     model = cases.make_model('tiny_convnet', seed=7)
     opt = fix_hooks(torchsso.optim.SecondOrderOptimizer(
-        model, 'Cov', KRON, {'ema_decay': 0.5, 'damping': 1e-3, 'use_max_ema': True}, lr=1e-2))
+        model, 'Cov', KRON, {'ema_decay': 0.5, 'damping': 1e-2, 'use_max_ema': True}, lr=1e-2))
     out = {}
     for t in range(3):
         x, y = cases.make_batch((6, 3, 8, 8), 5, seed=900 + t)

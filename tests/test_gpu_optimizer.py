@@ -189,7 +189,7 @@ def test_tiny_convnet_max_ema(torchsso_mod):
     gold = load('tiny_convnet_max_ema')
     model = cases.make_model('tiny_convnet', seed=7).cuda()
     opt = torchsso.optim.SecondOrderOptimizer(model, 'Cov', KRON,
-                                              {'ema_decay': 0.5, 'damping': 1e-3, 'use_max_ema': True}, lr=1e-2)
+                                              {'ema_decay': 0.5, 'damping': 1e-2, 'use_max_ema': True}, lr=1e-2)
     for t in range(3):
         x, y = cases.make_batch((6, 3, 8, 8), 5, seed=900 + t)
         if t == 1:
