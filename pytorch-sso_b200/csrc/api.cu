@@ -52,6 +52,7 @@ int factor_tc_flush_setting();
 bool factor_tma_supported(const FactorParams& p, int dtype);
 void factor_tma_set_pair_min_d(int d);
 void factor_tma_set_f32(int on);
+void factor_tma_set_fused_finish(int on);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
 extern int g_engine_tc;
 static int g_tc_auto = 1;    // whether SSO_IMPL_AUTO may pick the tcgen05 kernels
@@ -75,6 +76,7 @@ int sso_configure(const char* key, int value) {
   if (k == "tma_auto") { g_tma_auto = value != 0; return 0; }
   if (k == "engine_tc") { g_engine_tc = value != 0; return 0; }
   if (k == "tma_f32") { factor_tma_set_f32(value); return 0; }
+  if (k == "fused_finish") { factor_tma_set_fused_finish(value); return 0; }
   if (k == "tma_pair_min_d") { factor_tma_set_pair_min_d(value); return 0; }
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }
   if (k == "phase_lpt") { g_phase_lpt = value != 0; return 0; }

@@ -23,7 +23,16 @@ struct FactorParams {
   int* status;      // device word: 0 ok, else the code of the wait that gave up
   int perm_c;       // > 0: kernel columns are ordered (kh, kw, c) with c < perm_c; 0: natural order
   int perm_kk;      // kh*kw
+  // finishing inside the producing kernel (factor_finish.cuh); tickets == nullptr: separate kernel
+  int* tickets;     // [ticket_tiles] per-tile counters, then [ticket_tiles][16] per-group counters
+  int ticket_tiles;
 };
+
+// Scratch layout of the tensor-core factor kernels: [status word, 256 bytes][ticket counters]
+// [partial tiles].  The header is cleared on the stream by every launch.
+inline size_t factor_header_bytes(int tiles) {
+  return 256 + (((size_t)tiles * 17 * sizeof(int) + 255) / 256) * 256;
+}
 
 struct RowInfo {   // one im2col row (n, ho, wo)
   int64_t base;    // n*sn

@@ -541,7 +541,7 @@ size_t factor_tc_workspace_bytes(int64_t rows, int64_t d) {
   // below 12 MB of partial tiles for them
   const int64_t wide = std::min<int64_t>(std::min<int64_t>(148, 192 / tiles), std::max<int64_t>(1, rows / 512));
   if (wide > splits) splits = (int)wide;
-  return 256 + (size_t)tiles * splits * 128 * 128 * sizeof(float);
+  return factor_header_bytes(tiles) + (size_t)tiles * splits * 128 * 128 * sizeof(float);
 }
 
 bool factor_tc_supported(const FactorParams& p, int dtype) {
@@ -576,7 +576,8 @@ int factor_tc_launch(FactorParams p, int dtype, void* workspace, size_t workspac
   SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= need,
                 "factor workspace too small: need %zu bytes, got %zu", need, workspace_bytes);
   p.status = reinterpret_cast<int*>(workspace);
-  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + factor_header_bytes(tiles));
+  p.tickets = nullptr;
   SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), st));
   // internal column order (kh, kw, c); identity when there is a single kernel position
   p.perm_c = (p.kh * p.kw > 1) ? p.c : 0;

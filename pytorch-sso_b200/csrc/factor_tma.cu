@@ -18,6 +18,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "factor_finish.cuh"
 #include "factor_params.cuh"
 #include "tc_common.cuh"
 
@@ -60,11 +61,13 @@ factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CU
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int fin_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int bi, bj;
   tri_decode(blockIdx.x, bi, bj);
   const bool share = (bi == bj);
+  const bool fused = p.tickets != nullptr;
   const int split = blockIdx.y;
   const int s_begin = split * g.stages_per_split;
   const int s_end = min(g.total_stages, s_begin + g.stages_per_split);
@@ -91,17 +94,26 @@ factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CU
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // zero the operand buffers once: padding rows (kstage..kpad) and blocks past the matrix edge
-  // are never written by TMA and must read as zeros
-  for (uint32_t o = tid * 16u; o < STAGES * STAGE_BYTES; o += THREADS * 16u)
-    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(smem0 + o), "r"(0u) : "memory");
+  // What TMA never writes must read as zeros: the padding rows kstage..kpad of every block, and
+  // whole blocks past the matrix edge.  A row of a 64-column block is 128 bytes (the swizzle only
+  // permutes 16-byte chunks inside a row), so both are plain byte ranges; nothing else is touched.
+  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
+  for (int sb = 0; sb < 4 * STAGES; ++sb) {
+    const int e = sb & 3, op = e >> 1;
+    const int j0 = (op == 0 ? bi : bj) * TILE + (e & 1) * 64;
+    const bool valid = (j0 < p.dcols) && !(share && op == 1);
+    if (share && op == 1) continue;                         // never read on a diagonal tile
+    const uint32_t base = smem0 + (sb >> 2) * STAGE_BYTES + op * 2 * BLOCK_BYTES_MAX + (e & 1) * blk_bytes;
+    const uint32_t lo = valid ? (uint32_t)g.kstage * 128u : 0u;
+    for (uint32_t o = lo + tid * 16u; o < blk_bytes; o += THREADS * 16u)
+      asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(base + o), "r"(0u) : "memory");
+  }
   fence_async_smem();
   if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
 
   if (warp < EPI_WARPS) {
     // ------------------------------------------------------------------ accumulate warps
@@ -127,11 +139,20 @@ factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CU
         acc[32 + i] += __uint_as_float(v1[i]);
       }
     }
-    float* dst = p.partial + ((int64_t)blockIdx.x * p.splits + split) * (TILE * TILE) +
-                 (q * 32 + lane) * TILE + half * 64;
+    if (fused && p.splits == 1) {
+      // one split: the accumulator is the result; it goes to the output through the staging tile
+      // (the operand buffers are free: the last commit has fired, so every MMA has read them)
+      float* ct = reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw))) + (q * 32 + lane) * fin::CT_LD + half * 64;
 #pragma unroll
-    for (int i = 0; i < 64; i += 4)
-      *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+      for (int i = 0; i < 64; ++i) ct[i] = acc[i];
+    } else {
+      float* dst = p.partial + ((int64_t)blockIdx.x * p.splits + split) * (TILE * TILE) +
+                   (q * 32 + lane) * TILE + half * 64;
+#pragma unroll
+      for (int i = 0; i < 64; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+      if (fused) __threadfence();
+    }
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -211,6 +232,9 @@ factor_tma_kernel(const FactorParams p, const Geom g, const __grid_constant__ CU
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (fused)
+    fin::finish_tile<THREADS>(p, blockIdx.x, bi, bj, split,
+                              reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw))), &fin_flag, tid);
 }
 
 // ---- CTA-pair variant ----------------------------------------------------------------------------
@@ -275,8 +299,10 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int fin_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool fused = p.tickets != nullptr;
   const uint32_t rank = cluster_ctarank();
   int bI, bJ;
   tri_decode(blockIdx.x >> 1, bI, bJ);        // 256-wide block row / column of the pair
@@ -307,19 +333,25 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (uint32_t o = tid * 16u; o < STAGES * STAGE_BYTES; o += THREADS * 16u)
-    asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(smem0 + o), "r"(0u) : "memory");
+  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
+  // valid 64-column blocks of a CTA of rank rr: A0 A1 (rows of the block), B0 B1 (its half of the columns)
+  auto block_col = [&](uint32_t rr, int e) { return ((e >> 1) == 0 ? bI : bJ) * 256 + (int)rr * TILE + (e & 1) * 64; };
+  auto block_valid = [&](uint32_t rr, int e) { return block_col(rr, e) < p.dcols && !(share && (e >> 1) == 1); };
+  // zero what TMA never writes (see the single-CTA kernel): padding rows and blocks past the edge
+  for (int sb = 0; sb < 4 * STAGES; ++sb) {
+    const int e = sb & 3, op = e >> 1;
+    if (share && op == 1) continue;
+    const uint32_t base = smem0 + (sb >> 2) * STAGE_BYTES + op * 2 * BLOCK_BYTES_MAX + (e & 1) * blk_bytes;
+    const uint32_t lo = block_valid(rank, e) ? (uint32_t)g.kstage * 128u : 0u;
+    for (uint32_t o = lo + tid * 16u; o < blk_bytes; o += THREADS * 16u)
+      asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(base + o), "r"(0u) : "memory");
+  }
   fence_async_smem();
   if (warp == MMA_WARP) tmem_alloc2(smem_u32(&tmem_base_slot), TMEM_COLS2);
   tc_fence_before();
   cluster_sync_all();          // barriers of both CTAs are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t blk_bytes = (uint32_t)g.kpad * 128u;
-
-  // valid 64-column blocks of a CTA of rank rr: A0 A1 (rows of the block), B0 B1 (its half of the columns)
-  auto block_col = [&](uint32_t rr, int e) { return ((e >> 1) == 0 ? bI : bJ) * 256 + (int)rr * TILE + (e & 1) * 64; };
-  auto block_valid = [&](uint32_t rr, int e) { return block_col(rr, e) < p.dcols && !(share && (e >> 1) == 1); };
 
   if (warp < EPI_WARPS) {
     // ------------------------------------------------------------------ accumulate warps
@@ -349,11 +381,20 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
     const int ti = 2 * bI + (int)rank, tj = 2 * bJ + half;
     const int nb = ceil_div(p.d, TILE);
     if (ti < nb && tj <= ti) {
-      float* dst = p.partial + ((int64_t)(ti * (ti + 1) / 2 + tj) * p.splits + split) * (TILE * TILE) +
-                   (q * 32 + lane) * TILE;
+      if (fused && p.splits == 1) {
+        // one staging tile per half, behind each other in the (now free) operand buffers
+        float* ct = reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw))) + half * (TILE * fin::CT_LD) +
+                    (q * 32 + lane) * fin::CT_LD;
 #pragma unroll
-      for (int i = 0; i < 128; i += 4)
-        *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+        for (int i = 0; i < 128; ++i) ct[i] = acc[i];
+      } else {
+        float* dst = p.partial + ((int64_t)(ti * (ti + 1) / 2 + tj) * p.splits + split) * (TILE * TILE) +
+                     (q * 32 + lane) * TILE;
+#pragma unroll
+        for (int i = 0; i < 128; i += 4)
+          *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+        if (fused) __threadfence();
+      }
     }
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -430,6 +471,19 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
   if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc2(tmem_base, TMEM_COLS2);
+  }
+  if (fused) {
+    // this CTA's two tiles of the block: rows [128*rank, +128) x columns [128*h, +128), h = 0, 1
+    const int nb = ceil_div(p.d, TILE);
+    const int ti = 2 * bI + (int)rank;
+    float* ct0 = reinterpret_cast<float*>(smem_raw + (smem0 - smem_u32(smem_raw)));
+    for (int h = 0; h < 2; ++h) {
+      const int tj = 2 * bJ + h;
+      if (ti < nb && tj <= ti)
+        fin::finish_tile<THREADS>(p, ti * (ti + 1) / 2 + tj, ti, tj, split,
+                                  ct0 + (p.splits == 1 ? h * (TILE * fin::CT_LD) : 0), &fin_flag, tid);
+      __syncthreads();
+    }
   }
 }
 
@@ -814,16 +868,18 @@ static int factor_tma_f32_launch(FactorParams p, void* workspace, size_t workspa
   const int nb = ceil_div(p.d, 128);
   const int tiles = nb * (nb + 1) / 2;
   tma::choose_splits(g.total_stages, tiles, p.splits, g.stages_per_split);
-  SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= 256 + (size_t)tiles * 65536,
+  const size_t hdr = factor_header_bytes(tiles);
+  SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= hdr + (size_t)tiles * 65536,
                 "factor workspace too small for the tensor-core path");
-  const int max_splits = (int)((workspace_bytes - 256) / ((size_t)tiles * 65536));
+  const int max_splits = (int)((workspace_bytes - hdr) / ((size_t)tiles * 65536));
   if (p.splits > max_splits) {
     g.stages_per_split = ceil_div(g.total_stages, max_splits);
     p.splits = ceil_div(g.total_stages, g.stages_per_split);
   }
   p.rows_per_split = 0;
   p.status = reinterpret_cast<int*>(workspace);
-  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + hdr);
+  p.tickets = nullptr;
   SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), st));
   p.perm_c = (p.kh * p.kw > 1) ? p.c : 0;
   p.perm_kk = p.kh * p.kw;
@@ -858,6 +914,9 @@ bool factor_tma_supported(const FactorParams& p, int dtype) {
   return tma::encode_fn() != nullptr;
 }
 
+static int g_fused_finish = 1;  // unpermuted factors are finished by the producing kernel
+void factor_tma_set_fused_finish(int on) { g_fused_finish = on != 0; }
+
 static int g_pair_min_d = 512;  // factors at least this wide use the CTA-pair kernel; 0 = never
 void factor_tma_set_pair_min_d(int d) { g_pair_min_d = d < 0 ? 0 : d; }
 
@@ -874,9 +933,10 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   const int pair_blocks = nb2 * (nb2 + 1) / 2;
   choose_splits(g.total_stages, pair ? 2 * pair_blocks : tiles, p.splits, g.stages_per_split);
   // fit the partial tiles into the scratch the caller sized with sso_factor_workspace_bytes
-  SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= 256 + (size_t)tiles * 65536,
+  const size_t hdr = factor_header_bytes(tiles);
+  SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= hdr + (size_t)tiles * 65536,
                 "factor workspace too small for the tensor-core path");
-  const int max_splits = (int)((workspace_bytes - 256) / ((size_t)tiles * 65536));
+  const int max_splits = (int)((workspace_bytes - hdr) / ((size_t)tiles * 65536));
   if (p.splits > max_splits) {
     g.stages_per_split = ceil_div(g.total_stages, max_splits);
     p.splits = ceil_div(g.total_stages, g.stages_per_split);
@@ -885,10 +945,14 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   g.flush = flush > 0 ? flush : 4;
   g.fmt = (dtype == SSO_BF16) ? 1u : 0u;
   p.status = reinterpret_cast<int*>(workspace);
-  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 256);
-  SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, sizeof(int), st));
+  p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + hdr);
   p.perm_c = (p.kh * p.kw > 1) ? p.c : 0;
   p.perm_kk = p.kh * p.kw;
+  // columns in their public order already: the last CTA of every tile finishes it (factor_finish.cuh)
+  const bool fused = g_fused_finish && p.perm_c == 0;
+  p.tickets = fused ? reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 256) : nullptr;
+  p.ticket_tiles = tiles;
+  SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, fused ? hdr : sizeof(int), st));
 
   // NHWC view of the input: dims {C, W, H, N}
   CUtensorMap tmap;
@@ -909,11 +973,11 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
     SSO_ENSURE_SMEM(factor_tma_pair_kernel, (int)smem);
     factor_tma_pair_kernel<<<dim3(2 * pair_blocks, p.splits), THREADS, smem, st>>>(p, g, tmap);
     SSO_LAUNCH_OK("factor_tma_pair_kernel");
-    return factor_tc_run_reduce(p, tiles, st);
+    return fused ? 0 : factor_tc_run_reduce(p, tiles, st);
   }
   factor_tma_kernel<<<dim3(tiles, p.splits), THREADS, smem, st>>>(p, g, tmap);
   SSO_LAUNCH_OK("factor_tma_kernel");
-  return factor_tc_run_reduce(p, tiles, st);
+  return fused ? 0 : factor_tc_run_reduce(p, tiles, st);
 }
 
 }  // namespace sso
