@@ -377,6 +377,12 @@ def run_gpu_arm(args):
     # autograd assigns fresh gradient tensors instead of accumulating into the optimizer's flat buffer
     # (one add kernel per parameter per backward pass); one multi-tensor copy harvests them
     opt.zero_grad_to_none = (args.grads == 'assign')
+    # all factors of a pass go to the device in one persistent launch instead of one launch pair per layer
+    torchsso.utils.set_factor_batching(args.batching)
+    if args.fuse_ema and world == 1:
+        # the kernels that build the curvature write the running average in their epilogue
+        # (one closure call per step, which is how this loop drives the optimizer)
+        opt.fuse_ema = True
     closure = fisher_closure(torchsso, opt, model, x_static, y_static)
     eager_closure = closure
     first = None
@@ -523,6 +529,8 @@ def run_gpu_arm(args):
                    'factors_every': 1, 'inverse_every': INV_INTERVAL,
                    'closure': 'CUDA graph replay' if args.graph else 'eager',
                    'curvature_stream': bool(args.graph and args.side_stream),
+                   'factor_launches': 'batched per pass' if args.batching else 'per layer',
+                   'ema': 'fused into the factor / BatchNorm epilogues' if (args.fuse_ema and world == 1) else 'separate pass',
                    'parallelism': 'dp%d, factors reduce-scattered to owners' % world if world > 1 else 'single',
                    'l2_policy': 'per-step inputs (%.0f MB activations + 615 MB factor pools) exceed the 126 MB L2'
                                 % (B * 3 * 224 * 224 * 2 / 1e6),
@@ -598,6 +606,10 @@ def main():
                          "'accumulate' binds .grad to the flat buffer (autograd adds in place)")
     ap.add_argument('--no-side-stream', dest='side_stream', action='store_false',
                     help='launch the curvature kernels of the hooks on the main stream')
+    ap.add_argument('--no-batching', dest='batching', action='store_false',
+                    help='one factor launch per layer and pass instead of one batched launch per pass')
+    ap.add_argument('--no-fuse-ema', dest='fuse_ema', action='store_false',
+                    help='keep curv.data and the separate data -> ema pass (single GPU only; N > 1 always does)')
     ap.add_argument('--no-graph', dest='graph', action='store_false',
                     help='issue the closure eagerly instead of replaying a captured CUDA graph')
     args = ap.parse_args()

@@ -83,6 +83,28 @@ int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols,
                     float alpha, float beta, float* out, int64_t ldo,
                     void* workspace, size_t workspace_bytes, int impl, void* stream);
 
+/* Many factors in one call: every problem is what one sso_factor_syrk_im2col call describes (a plain
+ * [rows, cols] matrix is n = rows, c = cols, h = w = 1 with a 1x1 window).  Problems with 16-bit
+ * channels-contiguous inputs whose channel count is a multiple of 64 (no ones column, no per-sample
+ * weights) are cut into equally long work items and processed by ONE persistent tcgen05 kernel plus
+ * one finishing kernel; the others run one by one behind them.  The outputs must be distinct
+ * matrices.  Scratch: sso_factor_batch_workspace_bytes bytes, contents irrelevant on entry.
+ * Replaces: the per-layer loop of curvature updates that the hooks of
+ *           torchsso/curv/curvature.py:118-155 run one layer at a time (each a full launch sequence
+ *           of torchsso/curv/cov/conv.py:47-74 or torchsso/curv/cov/linear.py:50-67). */
+typedef struct {
+  const void* x;
+  int32_t dtype, append_ones;
+  int64_t n, c, h, w, sn, sc, sh, sw;
+  int32_t kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  const float* sample_weight;
+  float alpha, beta;
+  float* out;
+  int64_t ldo;
+} sso_factor_desc;
+size_t sso_factor_batch_workspace_bytes(int n, const sso_factor_desc* descs);
+int sso_factor_batch(int n, const sso_factor_desc* descs, void* workspace, size_t workspace_bytes, void* stream);
+
 /* sso_factor_syrk for callers that are not allowed to allocate device memory when they need a
  * factor (all device memory already given to their own pool, a fixed memory budget after start-up,
  * or no tolerance for the implicit synchronisation of an allocation).  It has no counterpart in

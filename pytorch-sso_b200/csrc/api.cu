@@ -9,8 +9,10 @@ thread_local std::string g_last_error;
 unsigned long long g_launches = 0;
 }  // namespace sso
 
+#include <algorithm>
 #include <map>
 #include <utility>
+#include <vector>
 
 namespace sso {
 int ensure_dynamic_smem(const void* kernel, int bytes) {
@@ -54,6 +56,9 @@ void factor_tma_set_pair_min_d(int d);
 void factor_tma_set_f32(int on);
 void factor_tma_set_fused_finish(int on);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
+size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int n);
+int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsigned char* done, void* workspace,
+                        size_t workspace_bytes, int flush, cudaStream_t st);
 extern int g_engine_tc;
 static int g_tc_auto = 1;    // whether SSO_IMPL_AUTO may pick the tcgen05 kernels
 static int g_tma_auto = 1;   // whether SSO_IMPL_AUTO may pick the TMA-fed tcgen05 kernel
@@ -98,12 +103,11 @@ size_t sso_factor_workspace_bytes(int64_t rows, int64_t d, int impl) {
   return a > b ? a : b;
 }
 
-int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64_t h, int64_t w,
-                           int64_t sn, int64_t sc, int64_t sh, int64_t sw, int kh, int kw,
-                           int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
-                           int append_ones, const float* sample_weight, float alpha, float beta,
-                           float* out, int64_t ldo, void* workspace, size_t workspace_bytes, int impl,
-                           void* stream) {
+// Argument checks and launch parameters shared by the single-problem and the batched entry points.
+static int make_factor_params(const void* x, int64_t n, int64_t c, int64_t h, int64_t w, int64_t sn, int64_t sc,
+                              int64_t sh, int64_t sw, int kh, int kw, int stride_h, int stride_w, int pad_h, int pad_w,
+                              int dil_h, int dil_w, int append_ones, const float* sample_weight, float alpha,
+                              float beta, float* out, int64_t ldo, FactorParams& p) {
   SSO_CHECK_ARG(x != nullptr && out != nullptr, "factor: null pointer");
   SSO_CHECK_ARG(n > 0 && c > 0 && h > 0 && w > 0, "factor: bad input dims");
   SSO_CHECK_ARG(kh > 0 && kw > 0 && stride_h > 0 && stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 &&
@@ -115,7 +119,7 @@ int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64
   const int64_t d = dcols + (append_ones ? 1 : 0);
   SSO_CHECK_ARG(d <= 65536 && n < ((int64_t)1 << 31) && ho * wo < ((int64_t)1 << 31), "factor: shape too large");
   SSO_CHECK_ARG(ldo >= d, "factor: ldo < d");
-  FactorParams p{};
+  p = FactorParams{};
   p.x = x; p.weight = sample_weight; p.out = out; p.partial = nullptr;
   p.sn = sn; p.sc = sc; p.sh = sh; p.sw = sw; p.ldo = ldo;
   p.rows = n * ho * wo;
@@ -124,7 +128,11 @@ int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64
   p.pad_h = pad_h; p.pad_w = pad_w; p.dil_h = dil_h; p.dil_w = dil_w;
   p.d = (int)d; p.dcols = (int)dcols;
   p.alpha = alpha; p.beta = beta;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return 0;
+}
+
+static int launch_one_factor(const FactorParams& p, int dtype, void* workspace, size_t workspace_bytes, int impl,
+                             cudaStream_t st) {
   if (impl == SSO_IMPL_TMA) {
     SSO_CHECK_ARG(factor_tma_supported(p, dtype), "factor: shape not supported by the TMA-fed tcgen05 path");
     return factor_tma_launch(p, dtype, workspace, workspace_bytes, factor_tc_flush_setting(), st);
@@ -138,6 +146,78 @@ int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64
   if (impl == SSO_IMPL_AUTO && g_tc_auto && factor_tc_supported(p, dtype))
     return factor_tc_launch(p, dtype, workspace, workspace_bytes, st);
   return factor_simt_launch(p, dtype, workspace, workspace_bytes, st);
+}
+
+int sso_factor_syrk_im2col(const void* x, int dtype, int64_t n, int64_t c, int64_t h, int64_t w,
+                           int64_t sn, int64_t sc, int64_t sh, int64_t sw, int kh, int kw,
+                           int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w,
+                           int append_ones, const float* sample_weight, float alpha, float beta,
+                           float* out, int64_t ldo, void* workspace, size_t workspace_bytes, int impl,
+                           void* stream) {
+  FactorParams p;
+  const int rc = make_factor_params(x, n, c, h, w, sn, sc, sh, sw, kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h,
+                                    dil_w, append_ones, sample_weight, alpha, beta, out, ldo, p);
+  if (rc) return rc;
+  return launch_one_factor(p, dtype, workspace, workspace_bytes, impl, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// ---- many factors in one call ----------------------------------------------------------------
+static int batch_params(int n, const sso_factor_desc* descs, std::vector<FactorParams>& ps, std::vector<int>& dts) {
+  SSO_CHECK_ARG(n >= 0 && (n == 0 || descs != nullptr), "factor batch: bad argument");
+  ps.resize(n);
+  dts.resize(n);
+  for (int i = 0; i < n; ++i) {
+    const sso_factor_desc& q = descs[i];
+    const int rc = make_factor_params(q.x, q.n, q.c, q.h, q.w, q.sn, q.sc, q.sh, q.sw, q.kh, q.kw, q.stride_h, q.stride_w,
+                                      q.pad_h, q.pad_w, q.dil_h, q.dil_w, q.append_ones, q.sample_weight, q.alpha, q.beta,
+                                      q.out, q.ldo, ps[i]);
+    if (rc) return rc;
+    dts[i] = q.dtype;
+  }
+  return 0;
+}
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+size_t sso_factor_batch_workspace_bytes(int n, const sso_factor_desc* descs) {
+  std::vector<FactorParams> ps;
+  std::vector<int> dts;
+  if (batch_params(n, descs, ps, dts) != 0) return 0;
+  size_t single = 0;
+  for (int i = 0; i < n; ++i) single = std::max(single, sso_factor_workspace_bytes(ps[i].rows, ps[i].d, SSO_IMPL_AUTO));
+  const size_t batched = (g_tc_auto && g_tma_auto) ? factor_batch_scratch_bytes(ps.data(), dts.data(), n) : 256;
+  return align256(batched) + align256(single);
+}
+
+int sso_factor_batch(int n, const sso_factor_desc* descs, void* workspace, size_t workspace_bytes, void* stream) {
+  std::vector<FactorParams> ps;
+  std::vector<int> dts;
+  const int rc = batch_params(n, descs, ps, dts);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  for (int i = 0; i < n; ++i)
+    for (int j = 0; j < i; ++j)
+      SSO_CHECK_ARG(ps[i].out != ps[j].out, "factor batch: problems %d and %d write the same matrix", j, i);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  std::vector<unsigned char> done(n, 0);
+  size_t batched = 256;
+  if (g_tc_auto && g_tma_auto) {
+    batched = factor_batch_scratch_bytes(ps.data(), dts.data(), n);
+    SSO_CHECK_ARG(workspace != nullptr && workspace_bytes >= batched, "factor batch: workspace too small: need %zu bytes, got %zu",
+                  batched, workspace_bytes);
+    const int rb = factor_batch_launch(ps.data(), dts.data(), n, done.data(), workspace, batched, factor_tc_flush_setting(), st);
+    if (rb) return rb;
+  }
+  // whatever the batched kernel does not take (fp32 inputs, odd channel counts, a ones column, per-sample
+  // weights) runs through the single-problem path behind the batch's scratch
+  char* tail = workspace ? reinterpret_cast<char*>(workspace) + align256(batched) : nullptr;
+  const size_t tail_bytes = workspace_bytes > align256(batched) ? workspace_bytes - align256(batched) : 0;
+  for (int i = 0; i < n; ++i) {
+    if (done[i]) continue;
+    const int r1 = launch_one_factor(ps[i], dts[i], tail, tail_bytes, SSO_IMPL_AUTO, st);
+    if (r1) return r1;
+  }
+  return 0;
 }
 
 int sso_factor_syrk(const void* x, int dtype, int64_t rows, int64_t cols, int64_t row_stride,

@@ -16,6 +16,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <vector>
 
 #include "common.cuh"
 #include "factor_finish.cuh"
@@ -949,7 +950,7 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   p.perm_c = (p.kh * p.kw > 1) ? p.c : 0;
   p.perm_kk = p.kh * p.kw;
   // columns in their public order already: the last CTA of every tile finishes it (factor_finish.cuh)
-  const bool fused = g_fused_finish && p.perm_c == 0;
+  const bool fused = g_fused_finish && p.perm_c == 0 && p.splits <= 4;
   p.tickets = fused ? reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + 256) : nullptr;
   p.ticket_tiles = tiles;
   SSO_CUDA_OK(cudaMemsetAsync(p.status, 0, fused ? hdr : sizeof(int), st));
@@ -978,6 +979,16 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
   factor_tma_kernel<<<dim3(tiles, p.splits), THREADS, smem, st>>>(p, g, tmap);
   SSO_LAUNCH_OK("factor_tma_kernel");
   return fused ? 0 : factor_tc_run_reduce(p, tiles, st);
+}
+
+#include "factor_batch.cuh"
+
+size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int n) {
+  return batch::factor_batch_scratch_bytes(ps, dtypes, n);
+}
+int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsigned char* done, void* workspace,
+                        size_t workspace_bytes, int flush, cudaStream_t st) {
+  return batch::factor_batch_launch(ps, dtypes, n, done, workspace, workspace_bytes, flush, st);
 }
 
 }  // namespace sso

@@ -369,6 +369,23 @@ def suite_collective(args):
              ms=round(ms_rs, 4), bus_gbs=round(4.0 * seg * world * f / ms_rs / 1e6, 1), nominal_gbs=900)
         emit(suite='collective', op='all_gather(updates)', world=world, bytes=4 * pseg * world,
              ms=round(ms_ag, 4), bus_gbs=round(4.0 * pseg * world * f / ms_ag / 1e6, 1), nominal_gbs=900)
+    # sweep over the distinct (d_A, d_G) pairs of the model: the exchange of ONE layer (packed A and G
+    # plus the gradient), cut into `world` equal segments, reduce-scattered and all-gathered; bus
+    # bandwidth against bytes shows where the collectives leave the latency-bound regime
+    for a, g in sorted(set(layers), key=lambda ag: tri(ag[0]) + tri(ag[1]) + ag[0] * ag[1]):
+        n = tri(a) + tri(g) + a * g
+        sg = (n + world - 1) // world
+        sg = (sg + 63) // 64 * 64
+        s_buf = torch.randn(sg * world, device='cuda')
+        r_buf = torch.empty(sg, device='cuda')
+        t_rs = timed(lambda: dist.reduce_scatter_tensor(r_buf, s_buf, op=dist.ReduceOp.SUM))
+        t_ag = timed(lambda: dist.all_gather_into_tensor(s_buf, r_buf))
+        if rank == 0:
+            f = (world - 1) / world
+            emit(suite='collective_sweep', dA=a, dG=g, world=world, bytes=4 * sg * world,
+                 reduce_scatter_ms=round(t_rs, 4), reduce_scatter_bus_gbs=round(4.0 * sg * world * f / t_rs / 1e6, 1),
+                 all_gather_ms=round(t_ag, 4), all_gather_bus_gbs=round(4.0 * sg * world * f / t_ag / 1e6, 1),
+                 nominal_gbs=900)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -49,6 +49,15 @@ class Phase(C.Structure):
     _fields_ = [('kind', C.c_int32), ('first', C.c_int32), ('count', C.c_int32), ('reserved', C.c_int32)]
 
 
+class FactorDesc(C.Structure):
+    _fields_ = [('x', c_vp), ('dtype', C.c_int32), ('append_ones', C.c_int32),
+                ('n', c_i64), ('c', c_i64), ('h', c_i64), ('w', c_i64),
+                ('sn', c_i64), ('sc', c_i64), ('sh', c_i64), ('sw', c_i64),
+                ('kh', C.c_int32), ('kw', C.c_int32), ('stride_h', C.c_int32), ('stride_w', C.c_int32),
+                ('pad_h', C.c_int32), ('pad_w', C.c_int32), ('dil_h', C.c_int32), ('dil_w', C.c_int32),
+                ('sample_weight', c_vp), ('alpha', c_f32), ('beta', c_f32), ('out', c_vp), ('ldo', c_i64)]
+
+
 TRI_REC_DTYPE = np.dtype([('m', np.uint64), ('packed', np.uint64), ('n', np.int32), ('ld', np.int32),
                           ('row0', np.int32), ('nrows', np.int32)])
 
@@ -65,6 +74,8 @@ SIGNATURES = {
                                 c_vp, c_i64, c_vp, c_sz, c_i32, c_vp]),
     'sso_factor_syrk_noalloc': (c_i32, [c_vp, c_i32, c_i64, c_i64, c_i64, c_i64, c_i32, c_vp, c_f32, c_f32,
                                         c_vp, c_i64, c_i32, c_vp]),
+    'sso_factor_batch_workspace_bytes': (c_sz, [c_i32, c_vp]),
+    'sso_factor_batch': (c_i32, [c_i32, c_vp, c_vp, c_sz, c_vp]),
     'sso_bn_plane_splits': (c_i32, [c_i32, c_i64, c_i64, c_i64, c_i64]),
     'sso_bn_plane_sums': (c_i32, [c_vp, c_vp, c_i32] + [c_i64] * 9 + [c_vp] * 4 + [c_i32, c_vp]),
     'sso_bn_diag_finish': (c_i32, [c_vp, c_vp, c_vp, c_i64, c_i64, c_i32, c_i32, c_f32, c_f32, c_vp, c_vp, c_vp]),
@@ -180,7 +191,10 @@ def run_on_curvature_stream(fn, tensor: torch.Tensor):
 
 
 def join_curvature_stream(device=None):
-    """Make the current stream wait for the curvature kernels queued so far."""
+    """Make the current stream wait for the curvature kernels queued so far (factor problems that
+    are still waiting for their batch are launched first)."""
+    if _pending:
+        flush_factors()
     if not _curv_dirty:
         return
     if device is None or device.index is None:
@@ -225,12 +239,13 @@ _workspaces = {}
 _retired_workspaces = []
 
 
-def workspace(device, nbytes: int) -> Optional[torch.Tensor]:
+def workspace(device, nbytes: int, which: str = '') -> Optional[torch.Tensor]:
     """Per-device scratch, grown on demand and reused (all launches are stream ordered).  A buffer
-    that is outgrown is kept until the process ends: captured CUDA graphs hold its raw address."""
+    that is outgrown is kept until the process ends: captured CUDA graphs hold its raw address.
+    `which` names a separate buffer (the batched factor launches have their own)."""
     if nbytes == 0:
         return None
-    key = (device.type, device.index)
+    key = (device.type, device.index) if not which else (device.type, device.index, which)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         if buf is not None:
@@ -320,7 +335,14 @@ class FactorOp:
         self.flops = 2.0 * rows * d * d
         self.bytes = x.numel() * x.element_size() + 4 * d * d
 
-    def run(self, x: torch.Tensor, weight: Optional[torch.Tensor], alpha: float, beta: float):
+    def run(self, x: torch.Tensor, weight: Optional[torch.Tensor], alpha: float, beta: float, defer: bool = True):
+        if _batching and defer and weight is None:
+            # wait for the other factors of this pass and go to the device with them in one launch
+            if self.out_ptr in _pending_outs:
+                flush_factors()
+            _pending.append((self, x, alpha, beta))
+            _pending_outs.add(self.out_ptr)
+            return
         ws = workspace(self.device, self.nbytes)
         if FACTOR_TIMING is not None:
             a = torch.cuda.Event(enable_timing=True)
@@ -334,6 +356,92 @@ class FactorOp:
         if FACTOR_TIMING is not None:
             b.record()
             FACTOR_TIMING.append((a, b, self.flops, self.bytes))
+
+
+# ---- batched factor construction -------------------------------------------------------------
+# With batching on, the hooks only note their factor problems; flush_factors() sends everything that
+# has been noted to the device as ONE call of sso_factor_batch (a persistent tcgen05 kernel over all
+# problems plus one finishing kernel).  Flush points: the end of the forward pass and of every backward
+# pass inside the Fisher closure, the first backward hook after a forward pass, and any consumer of
+# curvature data (join_curvature_stream).  Inputs are kept alive until their batch has been issued; as
+# with the curvature stream, the model must not modify a hooked layer's input or output in place.
+_batching = False
+_pending = []
+_pending_outs = set()
+_pending_phase = [None]
+_batch_cache = {}
+
+
+def set_factor_batching(enabled: bool):
+    global _batching
+    if not enabled and _pending:
+        flush_factors()
+    _batching = bool(enabled)
+
+
+def factor_batching_enabled() -> bool:
+    return _batching
+
+
+def note_phase(phase: str):
+    """Called by the hooks: a backward hook while forward-pass problems are still waiting means the
+    forward pass is over, so they are sent off before this pass adds its own."""
+    if _pending and _pending_phase[0] != phase:
+        flush_factors()
+    _pending_phase[0] = phase
+
+
+def flush_factors():
+    if not _pending:
+        return
+    items = list(_pending)
+    _pending.clear()
+    _pending_outs.clear()
+    L = lib()
+    key = tuple(id(op) for op, _, _, _ in items)
+    ent = _batch_cache.get(key)
+    if ent is None:
+        arr = (FactorDesc * len(items))()
+        for d, (op, x, alpha, beta) in zip(arr, items):
+            (d.dtype, d.n, d.c, d.h, d.w, d.sn, d.sc, d.sh, d.sw, d.kh, d.kw, d.stride_h, d.stride_w,
+             d.pad_h, d.pad_w, d.dil_h, d.dil_w, d.append_ones) = op.mid
+            d.x, d.sample_weight, d.alpha, d.beta, d.out, d.ldo = x.data_ptr(), None, alpha, beta, op.out_ptr, op.ldo
+        nbytes = L.sso_factor_batch_workspace_bytes(len(items), arr)
+        if nbytes == 0:
+            _check(-1)
+        if len(_batch_cache) > 32:
+            _batch_cache.pop(next(iter(_batch_cache)))
+        ent = (arr, nbytes, [op for op, _, _, _ in items])       # the ops stay alive with their ids
+        _batch_cache[key] = ent
+    arr, nbytes = ent[0], ent[1]
+    for d, (op, x, alpha, beta) in zip(arr, items):
+        d.x, d.alpha, d.beta = x.data_ptr(), alpha, beta
+    device = items[0][0].device
+
+    def launch(_):
+        ws = workspace(device, nbytes, 'batch')
+        if FACTOR_TIMING is not None:
+            a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            a.record()
+        _check(L.sso_factor_batch(len(items), arr, ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
+        if FACTOR_TIMING is not None:
+            b.record()
+            FACTOR_TIMING.append((a, b, sum(op.flops for op, _, _, _ in items), sum(op.bytes for op, _, _, _ in items)))
+
+    if _curv_enabled:
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        side = _curv_streams.get(idx)
+        if side is None:
+            side = _curv_streams[idx] = torch.cuda.Stream(device=idx)
+        side.wait_stream(torch.cuda.current_stream(idx))
+        for _, x, _, _ in items:
+            x.record_stream(side)
+        _curv_dirty.add(idx)
+        with torch.cuda.stream(side):
+            launch(None)
+    else:
+        launch(None)
 
 
 def _plane_strides(t: torch.Tensor):

@@ -44,6 +44,7 @@ class Curvature(object):
         self.use_max_ema = use_max_ema
         self.pi_type = pi_type
         self._pool = None
+        self._fuse_ema = False      # hooks write the running average themselves (optimizer.fuse_ema)
         self._have = set()          # which of data / ema / inv / std hold values
         self._generic = {}          # storage for curvature shapes the pool does not manage
         self._is_norm = isinstance(module, _NORM_TYPES)
@@ -129,6 +130,10 @@ class Curvature(object):
         d['data_input'] = x
         d['data_output'] = output.detach()   # detached: keeping the graph alive between steps would
                                              # pin last step's activations and autograd nodes
+        if self._fuse_ema and not (output.requires_grad and torch.is_grad_enabled()):
+            return      # an evaluation forward must not advance a running average the hooks own
+        if nat._batching:
+            nat.note_phase('forward')
         nat.run_on_curvature_stream(self.update_in_forward, output.detach() if self._is_norm else x)
         d.pop('output_edge', None)
         if output.requires_grad and torch.is_grad_enabled():
@@ -146,6 +151,8 @@ class Curvature(object):
     def backward_postprocess(self, module, grad_input, grad_output):
         g = grad_output[0].detach()
         module.__dict__['grad_output'] = g
+        if nat._batching:
+            nat.note_phase('backward')
         # the n^2 rescale that undoes the mean reduction of the loss
         # (torchsso/curv/curvature.py:151-155) is folded into the kernels' alpha
         nat.run_on_curvature_stream(self.update_in_backward, g)

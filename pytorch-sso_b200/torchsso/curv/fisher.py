@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
+from .. import _native as nat
 from .layers import Fisher
 
 _APPROX_TYPE_MC = 'mc'
@@ -51,6 +52,9 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
             torch.autograd.grad(loss, edges, retain_graph=True, allow_unused=True)
         else:
             loss.backward(retain_graph=True)
+        # with batched factor construction: this pass's G factors go to the device now, in one launch,
+        # beside whatever the closure does next (the next pass accumulates onto them)
+        nat.flush_factors()
 
     def closure():
         for group in optimizer.param_groups:
@@ -60,6 +64,7 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
 
         optimizer.zero_grad()
         output = model(data)
+        nat.flush_factors()          # batched factor construction: all A factors of the forward pass
         prob = F.softmax(output, dim=1)
 
         edges = []

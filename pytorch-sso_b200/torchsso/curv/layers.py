@@ -73,6 +73,16 @@ def _weights(curv, n, device):
     return w, 1.0
 
 
+def _fused_ema_coefficients(curv):
+    """(scale of the new estimate, weight of the old average) when a hook writes the running
+    average itself (torchsso/curv/curvature.py:174-191: ema <- data on first use or with decay 1,
+    else decay * data + (1 - decay) * ema)."""
+    b = curv.ema_decay
+    if 'ema' not in curv._have or b == 1:
+        return 1.0, 0.0
+    return float(b), float(1.0 - b)
+
+
 # ---------------------------------------------------------------------------------------------
 # Kronecker-factored
 # ---------------------------------------------------------------------------------------------
@@ -92,7 +102,7 @@ class _KronFactors(KronCurvature):
     """Shared driver: A in the forward hook, G (optionally prob-weighted and accumulated over
     sampling passes) in the backward hook, both by the fused factor kernel."""
 
-    def _factor_A(self, x, out):
+    def _factor_A(self, x, out, scale=1.0, beta=0.0):
         raise NotImplementedError
 
     def _factor_G(self, g, weight, alpha_scale, beta, out):
@@ -117,23 +127,40 @@ class _KronFactors(KronCurvature):
             self.__dict__['_dv'] = v
         return v[1]
 
+    def _ema_views(self):
+        v = self.__dict__.get('_ev')
+        if v is None or v[0] is not self._pool:
+            v = (self._pool if self._pool is not None else self.pool, self._views('ema'))
+            self.__dict__['_ev'] = v
+        return v[1]
+
     def update_in_forward(self, x):
-        self._factor_A(x, self._data_views()[0])
+        if self._fuse_ema:
+            # the kernel's epilogue is the running average: ema <- b * A + (1 - b) * ema
+            scale, beta = _fused_ema_coefficients(self)
+            self._factor_A(x, self._ema_views()[0], scale, beta)
+        else:
+            self._factor_A(x, self._data_views()[0])
 
     def update_in_backward(self, g):
         fisher = isinstance(self, Fisher)
         if fisher and not self.do_backward:
             # real backward: the sampling passes already left  n^2 * sum_pass G_pass  in place
             self._g_passes = 0
-            self._have.add('data')
+            if not self._fuse_ema:
+                self._have.add('data')
             return
         n = g.shape[0]
-        beta = 1.0 if (fisher and self._g_passes > 0) else 0.0
+        later_pass = fisher and self._g_passes > 0
         w, ws = _weights(self, n, g.device)
-        self._factor_G(g, w, ws * float(n) * float(n), beta, self._data_views()[1])
+        if self._fuse_ema:
+            scale, beta = _fused_ema_coefficients(self)
+            self._factor_G(g, w, scale * ws * float(n) * float(n), 1.0 if later_pass else beta, self._ema_views()[1])
+        else:
+            self._factor_G(g, w, ws * float(n) * float(n), 1.0 if later_pass else 0.0, self._data_views()[1])
+            self._have.add('data')
         if fisher:
             self._g_passes += 1
-        self._have.add('data')
 
 
 class KronCovLinear(_KronFactors):
@@ -146,9 +173,9 @@ class KronCovLinear(_KronFactors):
 
     _PLAIN = ((1, 1), (1, 1), (0, 0), (1, 1))
 
-    def _factor_A(self, x, out):
+    def _factor_A(self, x, out, scale=1.0, beta=0.0):
         x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
-        self._op(x2, self._PLAIN, self.bias, out).run(x2, None, 1.0 / x2.shape[0], 0.0)
+        self._op(x2, self._PLAIN, self.bias, out).run(x2, None, scale / x2.shape[0], beta)
 
     def _factor_G(self, g, weight, scale, beta, out):
         g2 = g if g.dim() == 2 else g.reshape(-1, g.shape[-1])
@@ -164,7 +191,7 @@ class KronCovConv2d(_KronFactors):
         da = c_in * kh * kw + (1 if self.bias else 0)
         return (da, da), (c_out, c_out)
 
-    def _factor_A(self, x, out):
+    def _factor_A(self, x, out, scale=1.0, beta=0.0):
         m = self._module
         if m.groups != 1 or isinstance(m.padding, str):
             raise NotImplementedError('grouped / string-padded convolutions have no Kronecker curvature here')
@@ -186,16 +213,22 @@ class KronCovConv2d(_KronFactors):
             if getattr(self, '_pad_buf', None) is None or self._pad_buf.shape[0] != dp:
                 self._pad_buf = torch.empty((dp, dp), dtype=torch.float32, device=x.device)
             self._op(xp, (m.kernel_size, m.stride, m.padding, m.dilation), self.bias,
-                     self._pad_buf).run(xp, None, 1.0 / n, 0.0)
+                     self._pad_buf).run(xp, None, 1.0 / n, 0.0, defer=False)      # read back right below
             d = c * kk
-            out[:d, :d].copy_(self._pad_buf[:d, :d])
+
+            def merge(dst, src):
+                if beta == 0.0 and scale == 1.0:
+                    dst.copy_(src)
+                else:
+                    dst.mul_(beta).add_(src, alpha=scale)
+            merge(out[:d, :d], self._pad_buf[:d, :d])
             if self.bias:
-                out[:d, d].copy_(self._pad_buf[:d, dp - 1])
-                out[d, :d].copy_(self._pad_buf[dp - 1, :d])
-                out[d, d].copy_(self._pad_buf[dp - 1, dp - 1])
+                merge(out[:d, d], self._pad_buf[:d, dp - 1])
+                merge(out[d, :d], self._pad_buf[dp - 1, :d])
+                merge(out[d, d], self._pad_buf[dp - 1, dp - 1])
             return
         geometry = (m.kernel_size, m.stride, m.padding, m.dilation)
-        self._op(x, geometry, self.bias, out).run(x, None, 1.0 / n, 0.0)
+        self._op(x, geometry, self.bias, out).run(x, None, scale / n, beta)
 
     _PLAIN = ((1, 1), (1, 1), (0, 0), (1, 1))
 
@@ -277,24 +310,28 @@ class _DiagBatchNorm(DiagCurvature):
         fisher = isinstance(self, Fisher)
         if fisher and not self.do_backward:
             self._passes = 0
-            self._have.add('data')
+            if not self._fuse_ema:
+                self._have.add('data')
             return
         n, c = g.shape[0], g.shape[1]
         layout = self._layout(g)
         self._sg = self._buffer(self._sg, n * layout[2] * c, g.device)
         splits_g = nat.bn_plane_sums(layout[0], False, None, None, self._sg, layout)
-        beta = 1.0 if (fisher and self._passes > 0) else 0.0
+        later_pass = fisher and self._passes > 0
+        role = 'ema' if self._fuse_ema else 'data'
         views = self.__dict__.get('_bnv')
-        if views is None or views[0] is not self._pool:
-            views = (self._pool if self._pool is not None else self.pool, self._views('data'))
+        if views is None or views[0] is not self._pool or views[2] != role:
+            views = (self._pool if self._pool is not None else self.pool, self._views(role), role)
             self.__dict__['_bnv'] = views
         views = views[1]
         w, ws = _weights(self, n, g.device)
-        nat.bn_diag_finish(self._sx, self._sg, w, n, c, self._splits_x, splits_g, ws * float(n) * float(n), beta,
-                           views[0], views[1] if len(views) > 1 else None)
+        scale, beta = _fused_ema_coefficients(self) if self._fuse_ema else (1.0, 0.0)
+        nat.bn_diag_finish(self._sx, self._sg, w, n, c, self._splits_x, splits_g, scale * ws * float(n) * float(n),
+                           1.0 if later_pass else beta, views[0], views[1] if len(views) > 1 else None)
         if fisher:
             self._passes += 1
-        self._have.add('data')
+        if not self._fuse_ema:
+            self._have.add('data')
 
 
 class DiagCovBatchNorm1d(_DiagBatchNorm):

@@ -169,6 +169,34 @@ class SecondOrderOptimizer(Optimizer):
     def local_param_groups(self):
         return self.param_groups
 
+    @property
+    def fuse_ema(self):
+        """Write ``ema <- decay * new + (1 - decay) * ema`` in the epilogue of the kernels that build
+        the curvature (factor, BatchNorm), instead of storing ``data`` and streaming ``data -> ema``
+        over all factors once per step (torchsso/curv/curvature.py:174-191).  Off by default because
+        it changes the hooks' contract: ``curv.data`` is no longer produced, and every closure call
+        that runs a backward pass must be followed by exactly one ``step()`` (evaluation forwards under
+        ``no_grad`` are ignored).  Needs ``acc_steps == 1``, a single process, and curvatures that
+        share one ``ema_decay``."""
+        return self.__dict__.get('_fuse_ema', False)
+
+    @fuse_ema.setter
+    def fuse_ema(self, on):
+        curvs = [g['curv'] for g in self.param_groups]
+        if on:
+            if self.defaults['acc_steps'] != 1 or type(self).backward_postprocess is not SecondOrderOptimizer.backward_postprocess:
+                raise ValueError('fuse_ema needs acc_steps == 1 and a single process: accumulation and the '
+                                 'owner-rank exchange carry curv.data')
+            if not all(c is not None and _is_pooled(c) for c in curvs) or len({c.ema_decay for c in curvs}) > 1:
+                raise ValueError('fuse_ema needs Kronecker / BatchNorm curvatures with one common ema_decay')
+        nat.join_curvature_stream(None)
+        for c in curvs:
+            if c is not None:
+                c._fuse_ema = bool(on)
+                if on:
+                    c._have.discard('data')
+        self.__dict__['_fuse_ema'] = bool(on)
+
     #: what ``zero_grad()`` does when called without an argument (as the closures do).  True (torch's
     #: own default): set every ``p.grad`` to None, autograd assigns its own tensors and one
     #: multi-tensor copy after the closure brings them into the flat buffer (100 MB more memory for
@@ -344,8 +372,9 @@ class SecondOrderOptimizer(Optimizer):
         uniform = len({(c.ema_decay, 'ema' in c._have) for c in curvs}) <= 1
         if pooled and uniform:
             firsts = [c._ema_bookkeeping() for c in curvs]
-            self.pool.update_ema(curvs[0].ema_decay, firsts[0], [g['curv'] for g in kron],
-                                 [g['curv'] for g in diag])
+            if not self.fuse_ema:        # else the hooks' kernels have already written the average
+                self.pool.update_ema(curvs[0].ema_decay, firsts[0], [g['curv'] for g in kron],
+                                     [g['curv'] for g in diag])
             for c in curvs:
                 c._have.add('ema')
         else:

@@ -32,6 +32,12 @@ class GraphedClosure:
         side = torch.cuda.Stream(priority=-1)
         side.wait_stream(torch.cuda.current_stream())
         from torchsso import _native as nat
+        # with optimizer.fuse_ema the hooks advance the running averages: the executions below (warm-up
+        # and the capture itself) are not optimisation steps, so the averages are put back afterwards
+        saved = []
+        if getattr(optimizer, 'fuse_ema', False):
+            pool = optimizer.pool
+            saved = [(pool.buf('ema', k), pool.buf('ema', k).clone()) for k in ('k', 'd') if pool.has('ema', k)]
         with torch.cuda.stream(side):
             for _ in range(max(1, warmup)):
                 closure()
@@ -43,6 +49,9 @@ class GraphedClosure:
         with torch.cuda.graph(self.graph, stream=side):
             self.result = closure()
             nat.join_curvature_stream(None)      # forked curvature kernels rejoin inside the capture
+        torch.cuda.synchronize()
+        for buf, copy in saved:
+            buf.copy_(copy)
         #: kernels of libsso_b200 inside the graph, i.e. launched by every replay
         self.library_kernels_per_replay = nat.launch_count() - before
         self.replays = 0

@@ -58,6 +58,7 @@ def torchsso_mod():
     import torchsso
     yield torchsso
     torchsso.utils.set_curvature_stream(False)
+    torchsso.utils.set_factor_batching(False)
 
 
 @pytest.fixture
@@ -236,13 +237,16 @@ def test_resnet50_step_through_graph_and_side_stream(torchsso_mod, monkeypatch, 
     assert not fails, fails[:10]
 
 
-def test_resnet50_bf16_factors_at_benchmark_shapes(torchsso_mod):
+@pytest.mark.parametrize('batching', [False, True])
+def test_resnet50_bf16_factors_at_benchmark_shapes(torchsso_mod, batching):
     """The benchmark's own numerics: ResNet-50 at batch 32 under bf16 autocast, channels_last.  For
     one layer of every distinct (d_A, d_G, rows) shape - d from 64 to 4608, rows from 32 to 401408,
     the 7x7 stride-2 stem, stride-2 3x3 and 1x1 convolutions, the biased Linear layer - the A and G
-    factors the hooks produced (TMA-fed and CTA-pair kernels) are compared with an fp64 evaluation
-    of the oracle on exactly the bf16 tensors the hooks saw."""
+    factors the hooks produced (TMA-fed and CTA-pair kernels; with `batching` all factors of a pass in
+    one persistent launch) are compared with an fp64 evaluation of the oracle on exactly the bf16
+    tensors the hooks saw."""
     torchsso = torchsso_mod
+    torchsso.utils.set_factor_batching(batching)
     bench = _resnet50()
     n = 32
     torch.manual_seed(0)
@@ -264,6 +268,7 @@ def test_resnet50_bf16_factors_at_benchmark_shapes(torchsso_mod):
     xs, ys = x.cuda().contiguous(memory_format=torch.channels_last), y.cuda()
     closure = bench.fisher_closure(torchsso, opt, model, xs, ys)
     closure()
+    torchsso.utils.set_factor_batching(False)      # flushes whatever is still waiting
     torch.cuda.synchronize()
 
     done, worst = set(), {'A': [0.0, None], 'G': [0.0, None]}
@@ -294,7 +299,7 @@ def test_resnet50_bf16_factors_at_benchmark_shapes(torchsso_mod):
                 worst[tag] = [e, str(key)]
         assert ea < F_TOL and eg < F_TOL, (key, ea, eg)
         assert torch.equal(A, A.t()) and torch.equal(G, G.t())
-    report(test='resnet50_bf16_factors_b32', shapes=len(done), worst=worst)
+    report(test='resnet50_bf16_factors_b32', batching=batching, shapes=len(done), worst=worst)
     assert len(done) >= 20
 
 

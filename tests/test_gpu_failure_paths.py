@@ -51,6 +51,39 @@ def test_factor_kernel_wait_runs_out(nat, channels):
     assert int(ws[:4].view(torch.int32).item()) == 0
 
 
+def test_batched_factor_kernel_wait_runs_out(nat):
+    """The persistent kernel of sso_factor_batch: with its producers stalled, every role's wait runs out,
+    the kernel returns, and the finishing kernel writes NaN for every problem of the batch."""
+    xs = [cases.make_normal((4, c, 6, 6), 5 + c).cuda().to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+          for c in (64, 320)]
+    outs = [torch.zeros((x.shape[1], x.shape[1]), device='cuda') for x in xs]
+    arr = (nat.FactorDesc * 2)()
+    for d, x, out in zip(arr, xs, outs):
+        d.x, d.dtype, d.append_ones = x.data_ptr(), nat._dtype_code(x), 0
+        d.n, d.c, d.h, d.w = x.shape
+        d.sn, d.sc, d.sh, d.sw = x.stride()
+        d.kh = d.kw = d.stride_h = d.stride_w = d.dil_h = d.dil_w = 1
+        d.pad_h = d.pad_w = 0
+        d.sample_weight, d.alpha, d.beta, d.out, d.ldo = None, 0.25, 0.0, out.data_ptr(), out.stride(0)
+    L = nat.lib()
+    nbytes = L.sso_factor_batch_workspace_bytes(2, arr)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device='cuda')
+    stream = torch.cuda.current_stream().cuda_stream
+    nat.configure('wait_kcycles', 2000)
+    nat.configure('inject_stall', 1)
+    nat._check(L.sso_factor_batch(2, arr, ws.data_ptr(), nbytes, stream))
+    torch.cuda.synchronize()
+    assert int(ws[:4].view(torch.int32).item()) != 0
+    assert all(bool(torch.isnan(o).all()) for o in outs)
+    nat.configure('inject_stall', 0)
+    nat.configure('wait_kcycles', 0)
+    nat._check(L.sso_factor_batch(2, arr, ws.data_ptr(), nbytes, stream))
+    for x, out in zip(xs, outs):
+        ref = ko.conv_factor_A(x.double().cpu(), (1, 1), (1, 1), (0, 0), (1, 1), False)
+        assert _rel(out, ref) < 1e-5
+    assert int(ws[:4].view(torch.int32).item()) == 0
+
+
 def test_engine_tile_task_wait_runs_out(nat):
     d = 384
     xa = cases.make_normal((4 * d, d), 7)

@@ -608,3 +608,57 @@ def test_diag_sq_conv_matches_oracle(nat, cfg, channels_last, dtype):
     out_b = torch.full((oc,), float('nan'), device='cuda')
     nat.diag_sq(xd, gd, k, s, p, d, dev(prob), 1.0 / n, 0.0, out_w, out_b)
     assert rel(out_w, rw) < FACTOR_TOL and rel(out_b, rb) < FACTOR_TOL
+
+
+# ------------------------------------------------------------------------------------ batched factors
+def _desc_array(nat, items):
+    arr = (nat.FactorDesc * len(items))()
+    for d, (x, geo, alpha, beta, out) in zip(arr, items):
+        n, c, h, w = x.shape
+        (kh, kw), (sh, sw), (ph, pw), (dh, dw) = geo
+        d.x, d.dtype, d.append_ones = x.data_ptr(), nat._dtype_code(x), 0
+        d.n, d.c, d.h, d.w = n, c, h, w
+        d.sn, d.sc, d.sh, d.sw = x.stride()
+        d.kh, d.kw, d.stride_h, d.stride_w, d.pad_h, d.pad_w, d.dil_h, d.dil_w = kh, kw, sh, sw, ph, pw, dh, dw
+        d.sample_weight, d.alpha, d.beta, d.out, d.ldo = None, alpha, beta, out.data_ptr(), out.stride(0)
+    return arr
+
+
+def test_factor_batch_matches_oracle(nat):
+    """Several factor problems of different geometry in ONE call (persistent CTA-pair kernel over all
+    of them + one finishing launch): 3x3 / 1x1 / strided windows, channel counts 64 ... 384, a single
+    image plane smaller than a stage, accumulation onto existing contents, and one fp32 problem that
+    the batched kernel does not take (it runs behind the batch through the single-problem path)."""
+    cl = torch.channels_last
+    specs = [  # (n, c, h, w), geometry, dtype, alpha, beta
+        ((6, 64, 12, 12), ((3, 3), (1, 1), (1, 1), (1, 1)), torch.bfloat16, 1.0 / 6, 0.0),
+        ((5, 128, 14, 14), ((1, 1), (1, 1), (0, 0), (1, 1)), torch.bfloat16, 0.5, 1.0),
+        ((4, 256, 7, 7), ((3, 3), (1, 1), (1, 1), (1, 1)), torch.float16, 0.25, 0.0),
+        ((3, 64, 16, 16), ((3, 3), (2, 2), (1, 1), (1, 1)), torch.bfloat16, 1.0, 0.0),
+        ((9, 384, 5, 5), ((1, 1), (1, 1), (0, 0), (1, 1)), torch.bfloat16, 2.0, 0.5),
+        ((40, 64, 28, 28), ((1, 1), (1, 1), (0, 0), (1, 1)), torch.bfloat16, 1.0 / 40, 0.0),
+        ((2, 8, 9, 9), ((3, 3), (1, 1), (1, 1), (1, 1)), torch.float32, 1.0, 0.0),
+    ]
+    items, news = [], []
+    for i, (shape, geo, dt, alpha, beta) in enumerate(specs):
+        x = cases.make_normal(shape, 300 + i).to(dt).cuda().contiguous(memory_format=cl)
+        d = shape[1] * geo[0][0] * geo[0][1]
+        init = cases.make_normal((d, d), 400 + i)
+        out = (init + init.t()).cuda()
+        items.append((x, geo, alpha, beta, out))
+        news.append(alpha * ko.conv_factor_A(x.double().cpu(), *geo, False) * shape[0])    # alpha * sum_r u u^T
+    arr = _desc_array(nat, items)
+    L = nat.lib()
+    nbytes = L.sso_factor_batch_workspace_bytes(len(items), arr)
+    assert nbytes > 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+    for rep in range(2):     # twice on the same scratch: stale partial tiles must not leak
+        before = [it[4].double().cpu() for it in items]
+        nat._check(L.sso_factor_batch(len(items), arr, ws.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        for (x, geo, alpha, beta, out), new, old in zip(items, news, before):
+            assert rel(out, new + beta * old) < 1e-5, (rep, tuple(x.shape), geo)
+            assert torch.equal(out, out.t())
+    with pytest.raises(RuntimeError, match='write the same matrix'):
+        bad = _desc_array(nat, [items[0], items[0]])
+        nat._check(L.sso_factor_batch(2, bad, ws.data_ptr(), nbytes, torch.cuda.current_stream().cuda_stream))

@@ -415,6 +415,51 @@ def test_graphed_closure_equals_eager(torchsso_mod, side_stream):
         assert rel(b, a.cpu().numpy()) < 1e-5
 
 
+@pytest.mark.parametrize('graphed', [False, True])
+def test_fused_ema_equals_separate_pass(torchsso_mod, monkeypatch, graphed):
+    """optimizer.fuse_ema: the running average written by the epilogue of the factor / BatchNorm
+    kernels equals the separate data -> ema pass (eagerly and from a replayed graph, whose warm-up
+    executions must leave the averages untouched)."""
+    torchsso = torchsso_mod
+    state = {}
+    patch_targets(monkeypatch, torchsso, state)
+
+    def run(fuse):
+        model = cases.make_model('tiny_convnet', seed=1).cuda()
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, {'ema_decay': 0.9, 'damping': 1e-3}, lr=1e-2)
+        xs = torch.empty((6, 3, 8, 8), device='cuda')
+        ys = torch.empty((6,), dtype=torch.int64, device='cuda')
+        closure = torchsso.get_closure_for_fisher(opt, model, xs, ys, approx_type='mc', num_mc=2)
+        step_closure = closure
+        for t in range(4):
+            x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100 + t)
+            xs.copy_(x); ys.copy_(y)
+            state['u'] = cases.make_uniform((2, 6), seed=200 + t)
+            if t == 1:
+                opt.fuse_ema = fuse
+                if graphed:
+                    with torch.no_grad():
+                        fixed = inverse_cdf_targets(torch.softmax(model(xs), dim=1).float().cpu(), state['u']).cuda()
+                    monkeypatch.setattr(torchsso.curv.fisher, 'sample_targets', lambda prob, num_mc: fixed)
+                    bn = {k: v.clone() for k, v in model.state_dict().items()}
+                    step_closure = torchsso.utils.GraphedClosure(opt, closure)
+                    model.load_state_dict(bn)
+            if graphed and t >= 1:      # the captured targets are those of step 1: keep its batch too
+                x, y = cases.make_batch((6, 3, 8, 8), 5, seed=101)
+                xs.copy_(x); ys.copy_(y)
+            opt.update_inv = (t != 2)
+            opt.step(closure=step_closure)
+        emas = [e.clone() for g in opt.param_groups for e in g['curv'].ema]
+        if fuse:
+            assert all(g['curv'].data is None for g in opt.param_groups)
+        return emas, [p.detach().clone() for p in model.parameters()]
+
+    e0, p0 = run(False)
+    e1, p1 = run(True)
+    for a, b in zip(e0 + p0, e1 + p1):
+        assert rel(b, a.cpu().numpy()) < 2e-6
+
+
 def test_fisher_sampling_survives_nan_probabilities(torchsso_mod):
     """NaN / zero rows in the predictive distribution (a diverged model) must not reach the
     sampling kernel's device-side assertion."""
