@@ -1,6 +1,7 @@
 """Operator-level microbenchmarks of libsso_b200 (one JSON line per case).
 
     python pytorch-sso_b200/microbench.py factor   [--dtype bf16|fp32] [--case I] [--iters K]
+    python pytorch-sso_b200/microbench.py batch    [--case 0|1]    all ResNet-50 A / G factors: one batched call vs one call each
     python pytorch-sso_b200/microbench.py rows     [--case I]      fp32 X^T X, d in 64..4608
     python pytorch-sso_b200/microbench.py inverse  [--case I]      damped SPD inverse, d in 64..4608
     python pytorch-sso_b200/microbench.py precond  [--case I]      G^-1 dW A^-1
@@ -390,7 +391,78 @@ def suite_collective(args):
     dist.destroy_process_group()
 
 
-SUITES = {'diag': suite_diag, 'peaks': suite_peaks, 'steps': suite_steps, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
+def r50_convs(batch):
+    """(c_in, h, w, kernel, stride, pad, c_out, h_out, w_out) of every convolution of the benchmark's
+    ResNet-50 at 224x224, taken from a shape-only forward pass of the model itself."""
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), '..')
+    if root not in sys.path:
+        sys.path.insert(0, root)
+    import bench
+    with torch.device('meta'):
+        model = bench.ResNet50()
+    out = []
+
+    def hook(m, inp, res):
+        x = inp[0]
+        out.append((x.shape[1], x.shape[2], x.shape[3], m.kernel_size[0], m.stride[0], m.padding[0],
+                    res.shape[1], res.shape[2], res.shape[3]))
+    for m in model.modules():
+        if isinstance(m, torch.nn.Conv2d):
+            m.register_forward_hook(hook)
+    model(torch.empty((batch, 3, 224, 224), device='meta'))
+    return out
+
+
+def suite_batch(args):
+    """All A factors (or all G factors) of ResNet-50's convolutions, bf16, as ONE sso_factor_batch call,
+    against the same problems issued one sso_factor_syrk_im2col call at a time (the 3-channel stem is
+    left out of both: its input is the fp32 image)."""
+    n = args.batch
+    convs = [c for c in r50_convs(n) if c[0] % 64 == 0]
+    cl = torch.channels_last
+    g = torch.Generator(device='cuda').manual_seed(0)
+    for which in ('A', 'G'):
+        items, flops, nbytes_in = [], 0.0, 0
+        for (cin, h, w, k, st, pad, cout, ho, wo) in convs:
+            if which == 'A':
+                x = torch.randn((n, cin, h, w), device='cuda', generator=g).bfloat16().contiguous(memory_format=cl)
+                geo, d, rows = ((k, k), (st, st), (pad, pad), (1, 1)), cin * k * k, n * ho * wo
+            else:
+                x = torch.randn((n, cout, ho, wo), device='cuda', generator=g).bfloat16().contiguous(memory_format=cl)
+                geo, d, rows = ((1, 1), (1, 1), (0, 0), (1, 1)), cout, n * ho * wo
+            items.append((x, geo, torch.empty((d, d), device='cuda')))
+            flops += 2.0 * rows * d * d
+            nbytes_in += x.numel() * 2
+        arr = (nat.FactorDesc * len(items))()
+        for dsc, (x, geo, out) in zip(arr, items):
+            dsc.x, dsc.dtype, dsc.append_ones = x.data_ptr(), nat.BF16, 0
+            dsc.n, dsc.c, dsc.h, dsc.w = x.shape
+            dsc.sn, dsc.sc, dsc.sh, dsc.sw = x.stride()
+            (dsc.kh, dsc.kw), (dsc.stride_h, dsc.stride_w), (dsc.pad_h, dsc.pad_w), (dsc.dil_h, dsc.dil_w) = geo
+            dsc.sample_weight, dsc.alpha, dsc.beta, dsc.out, dsc.ldo = None, 1.0 / n, 0.0, out.data_ptr(), out.stride(0)
+        L = nat.lib()
+        nb = L.sso_factor_batch_workspace_bytes(len(items), arr)
+        ws = torch.empty(nb, dtype=torch.uint8, device='cuda')
+
+        def batched():
+            nat._check(L.sso_factor_batch(len(items), arr, ws.data_ptr(), nb, torch.cuda.current_stream().cuda_stream))
+
+        def one_by_one():
+            for x, geo, out in items:
+                nat.factor_im2col(x, *geo, False, None, 1.0 / n, 0.0, out)
+        if args.case in (None, 0):
+            ms_b = timeit(batched, args.iters)
+            emit(suite='batch', which=which, mode='one sso_factor_batch call', problems=len(items), ms=round(ms_b, 4),
+                 tflops_algorithmic=round(flops / ms_b / 1e9, 1), input_mb=round(nbytes_in / 1e6, 1),
+                 scratch_mb=round(nb / 1e6, 1))
+        if args.case in (None, 1):
+            ms_s = timeit(one_by_one, args.iters)
+            emit(suite='batch', which=which, mode='one call per problem', problems=len(items), ms=round(ms_s, 4),
+                 tflops_algorithmic=round(flops / ms_s / 1e9, 1))
+        del items, ws
+
+
+SUITES = {'batch': suite_batch, 'diag': suite_diag, 'peaks': suite_peaks, 'steps': suite_steps, 'factor': suite_factor, 'rows': suite_rows, 'inverse': suite_inverse, 'precond': suite_precond,
           'stream': suite_stream, 'collective': suite_collective}
 
 
