@@ -366,8 +366,8 @@ def test_resnet50_bf16_factors_at_benchmark_shapes(torchsso_mod, batching):
 
 
 # ------------------------------------------------------------------------------------ rank-deficient inverse
-@pytest.mark.parametrize('rows,da,dg', [(1568, 4608, 512), (6272, 2304, 256)])
-def test_rank_deficient_damped_inverse(rows, da, dg):
+@pytest.mark.parametrize('rows,da,dg,decay', [(1568, 4608, 512, 0.0), (6272, 2304, 256, 0.0), (1568, 4608, 512, 3.0)])
+def test_rank_deficient_damped_inverse(rows, da, dg, decay):
     """A = X^T X / 32 from `rows` rows (rank <= rows < d_A for the last stage: most of the spectrum of
     the damped matrix IS the damping), G small.  The 3xTF32 Cholesky-based inverse is compared with
     the fp64 oracle on the same fp32 input; fp32 LAPACK (what the reference's CPU branch calls,
@@ -377,6 +377,11 @@ def test_rank_deficient_damped_inverse(rows, da, dg):
     g = torch.Generator().manual_seed(rows + da)
     X = torch.randn((rows, da), generator=g)
     Y = torch.randn((rows, dg), generator=g) * 1e-2
+    if decay:
+        # column scales falling by `decay` orders of magnitude, as the channels of a trained layer do: the
+        # spectrum then spans six orders above the damping floor instead of sitting on one plateau
+        X = X * torch.logspace(0, -decay, da)
+        Y = Y * torch.logspace(0, -decay, dg)
     A = ((X.t() @ X) / 32.0).cuda()
     G = ((Y.t() @ Y) / rows * 1024.0).cuda()
     src = [A, G]
@@ -399,6 +404,6 @@ def test_rank_deficient_damped_inverse(rows, da, dg):
         ev = torch.linalg.eigvalsh(Md)
         out[name] = {'ours': rel(got, ref), 'fp32_lapack': rel(lapack32, ref), 'cond': (ev[-1] / ev[0]).item()}
         assert torch.equal(got, got.t())
-    report(test='rank_deficient_inverse', rows=rows, dA=da, dG=dg, **out)
+    report(test='rank_deficient_inverse', rows=rows, dA=da, dG=dg, decay=decay, **out)
     for name, e in out.items():
         assert e['ours'] <= max(I_TOL, 3 * e['fp32_lapack']), (name, e)
