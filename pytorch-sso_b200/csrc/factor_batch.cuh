@@ -83,7 +83,12 @@ factor_batch_kernel(const __grid_constant__ Params bp) {
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      // "full" takes two arrivals per stage: the leader's (which also announces the bytes of both
+      // CTAs) and one from the peer's producer once it has dealt with the stage.  Without the second
+      // a peer that has nothing to load for a stretch of stages (its half of the block lies past the
+      // matrix edge) could fall two phases behind its "empty" barrier, whose parity it would then
+      // misread; it also orders the peer's zero filling before the MMAs that read its shared memory.
+      mbar_init(full_bar(s), 2);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -243,6 +248,7 @@ factor_batch_kernel(const __grid_constant__ Params bp) {
                 ::"r"(dst), "l"(tmap_ptr), "r"(bc0[e]), "r"(bx[e]), "r"(oy0 * P.stride_h + by[e]), "r"(n0), "r"(fb)
                 : "memory");
           }
+          if (rank != 0) mbar_arrive_cluster(fb);       // the peer's arrival for this stage
         }
         __syncwarp();
       }

@@ -325,7 +325,10 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      // two arrivals per stage: the leader's (with the byte count of both CTAs) and the peer's, so
+      // that a peer with nothing to load (its columns lie past the matrix edge) stays in step with
+      // the stages instead of being lapped by its "empty" barrier
+      mbar_init(full_bar(s), 2);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -464,6 +467,7 @@ factor_tma_pair_kernel(const FactorParams p, const Geom g, const __grid_constant
               ::"r"(dst), "l"(tmap_ptr), "r"(bc0[e]), "r"(bx[e]), "r"(oy0 * p.stride_h + by[e]), "r"(n0), "r"(fb)
               : "memory");
         }
+        if (rank != 0) mbar_arrive_cluster(fb);
       }
     }
   }
