@@ -379,6 +379,8 @@ def run_gpu_arm(args):
     opt.zero_grad_to_none = (args.grads == 'assign')
     # all factors of a pass go to the device in one persistent launch instead of one launch pair per layer
     torchsso.utils.set_factor_batching(args.batching)
+    if args.batch_pairs:
+        nat.configure('batch_pairs', args.batch_pairs)
     if args.fuse_ema and world == 1:
         # the kernels that build the curvature write the running average in their epilogue
         # (one closure call per step, which is how this loop drives the optimizer)
@@ -608,6 +610,9 @@ def main():
                     help='launch the curvature kernels of the hooks on the main stream')
     ap.add_argument('--no-batching', dest='batching', action='store_false',
                     help='one factor launch per layer and pass instead of one batched launch per pass')
+    ap.add_argument('--batch-pairs', type=int, default=0,
+                    help='CTA pairs of the batched factor kernel (0 = one per two SMs); fewer leave SMs to the '
+                         'model kernels that run beside it')
     ap.add_argument('--no-fuse-ema', dest='fuse_ema', action='store_false',
                     help='keep curv.data and the separate data -> ema pass (single GPU only; N > 1 always does)')
     ap.add_argument('--no-graph', dest='graph', action='store_false',

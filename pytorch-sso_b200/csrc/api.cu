@@ -55,6 +55,7 @@ bool factor_tma_supported(const FactorParams& p, int dtype);
 void factor_tma_set_pair_min_d(int d);
 void factor_tma_set_f32(int on);
 void factor_tma_set_fused_finish(int on);
+void factor_batch_set_pairs(int pairs);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
 size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int n);
 int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsigned char* done, void* workspace,
@@ -81,6 +82,7 @@ int sso_configure(const char* key, int value) {
   if (k == "tma_auto") { g_tma_auto = value != 0; return 0; }
   if (k == "engine_tc") { g_engine_tc = value != 0; return 0; }
   if (k == "tma_f32") { factor_tma_set_f32(value); return 0; }
+  if (k == "batch_pairs") { factor_batch_set_pairs(value); return 0; }
   if (k == "fused_finish") { factor_tma_set_fused_finish(value); return 0; }
   if (k == "tma_pair_min_d") { factor_tma_set_pair_min_d(value); return 0; }
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }

@@ -370,6 +370,8 @@ __global__ void __launch_bounds__(256) factor_batch_finish_kernel(const __grid_c
 }
 
 // ---- host side -----------------------------------------------------------------------------------
+static int g_batch_pairs = 0;        // CTA pairs of the persistent kernel; 0 = one per two SMs
+
 struct Planned {
   FactorParams p;
   Geom g;
@@ -499,7 +501,10 @@ int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsign
     }
     bp.nitems = items;
     SSO_CHECK_ARG(fin_smem <= 200 * 1024, "factor batch: kernel window too large for the finishing kernel");
-    const int pairs = std::max(1, std::min(sm_count / 2, items));
+    // all SM pairs by default; fewer leave SMs to kernels of other streams that run beside the batch
+    int pairs = sm_count / 2;
+    if (g_batch_pairs > 0) pairs = std::min(pairs, g_batch_pairs);
+    pairs = std::max(1, std::min(pairs, items));
     factor_batch_kernel<<<2 * pairs, THREADS, smem, st>>>(bp);
     SSO_LAUNCH_OK("factor_batch_kernel");
     SSO_ENSURE_SMEM(factor_batch_finish_kernel, 200 * 1024);

@@ -987,6 +987,7 @@ int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspa
 
 #include "factor_batch.cuh"
 
+void factor_batch_set_pairs(int pairs) { batch::g_batch_pairs = pairs < 0 ? 0 : pairs; }
 size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int n) {
   return batch::factor_batch_scratch_bytes(ps, dtypes, n);
 }

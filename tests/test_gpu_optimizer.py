@@ -422,9 +422,9 @@ def test_fused_ema_equals_separate_pass(torchsso_mod, monkeypatch, graphed):
     executions must leave the averages untouched)."""
     torchsso = torchsso_mod
     state = {}
-    patch_targets(monkeypatch, torchsso, state)
 
     def run(fuse):
+        patch_targets(monkeypatch, torchsso, state)      # (the graphed variant swaps in fixed targets below)
         model = cases.make_model('tiny_convnet', seed=1).cuda()
         opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, {'ema_decay': 0.9, 'damping': 1e-3}, lr=1e-2)
         xs = torch.empty((6, 3, 8, 8), device='cuda')
@@ -457,7 +457,7 @@ def test_fused_ema_equals_separate_pass(torchsso_mod, monkeypatch, graphed):
     e0, p0 = run(False)
     e1, p1 = run(True)
     for a, b in zip(e0 + p0, e1 + p1):
-        assert rel(b, a.cpu().numpy()) < 2e-6
+        assert rel(b, a.cpu().numpy()) < 1e-5        # one fused multiply-add instead of two rounded steps
 
 
 def test_fisher_sampling_survives_nan_probabilities(torchsso_mod):
