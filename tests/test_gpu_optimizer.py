@@ -457,7 +457,7 @@ def test_fused_ema_equals_separate_pass(torchsso_mod, monkeypatch, graphed):
     e0, p0 = run(False)
     e1, p1 = run(True)
     for a, b in zip(e0 + p0, e1 + p1):
-        assert rel(b, a.cpu().numpy()) < 1e-5        # one fused multiply-add instead of two rounded steps
+        assert rel(b, a.cpu().numpy()) < 3e-5        # one fused multiply-add instead of two rounded steps, over four updates
 
 
 def test_fisher_sampling_survives_nan_probabilities(torchsso_mod):
