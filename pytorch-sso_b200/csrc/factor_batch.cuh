@@ -22,7 +22,7 @@ using namespace tc;
 using namespace tma;
 
 constexpr int MAX_PROBLEMS = 96;
-constexpr int ITEM_STAGES = 32;          // target length of a work item, in pipeline stages
+constexpr int ITEM_STAGES_MIN = 32, ITEM_STAGES_MAX = 128;   // bounds of a work item's length, in pipeline stages
 
 struct alignas(64) Prob {
   CUtensorMap tmap;          // NHWC view of the input, box {64, bw*stride_w, bh*stride_h, bn}
@@ -385,15 +385,30 @@ static bool batchable(const FactorParams& p, int dtype) {
   return (dtype == SSO_BF16 || dtype == SSO_F16) && factor_tma_supported(p, dtype);
 }
 
-static void plan_problem(const FactorParams& p, int dtype, Planned& out) {
+// Length of a work item for a set of problems: long enough that the partial tiles (one per item and
+// tile, written and read back once) stay a small part of the traffic, short enough that every CTA pair
+// gets several items (about six) and the round-robin walk ends evenly.
+static int item_stages_for(const FactorParams* ps, const int* dtypes, int n, int pairs) {
+  double work = 0;
+  for (int i = 0; i < n; ++i) {
+    if (!batchable(ps[i], dtypes[i])) continue;
+    Geom g;
+    choose_box(ps[i], g);
+    const int nb2 = ceil_div(ps[i].d, 256);
+    work += (double)(nb2 * (nb2 + 1) / 2) * g.total_stages;
+  }
+  const int want = (int)(work / (6.0 * std::max(1, pairs)));
+  return std::max(ITEM_STAGES_MIN, std::min(ITEM_STAGES_MAX, want));
+}
+
+static void plan_problem(const FactorParams& p, int dtype, int item_stages, Planned& out) {
   out.p = p;
   out.dtype = dtype;
   choose_box(p, out.g);
   const int nb = ceil_div(p.d, 128), nb2 = ceil_div(p.d, 256);
   out.tiles = nb * (nb + 1) / 2;
   out.nblk = nb2 * (nb2 + 1) / 2;
-  // items of about ITEM_STAGES stages each; never more splits than the single launch would use
-  int splits = std::max(1, (out.g.total_stages + ITEM_STAGES - 1) / ITEM_STAGES);
+  int splits = std::max(1, (out.g.total_stages + item_stages - 1) / item_stages);
   splits = std::min(splits, 64);
   out.g.stages_per_split = ceil_div(out.g.total_stages, splits);
   out.p.splits = ceil_div(out.g.total_stages, out.g.stages_per_split);
@@ -403,11 +418,12 @@ static void plan_problem(const FactorParams& p, int dtype, Planned& out) {
 }
 
 size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int n) {
+  // sized for the shortest items (most splits), so that it holds for any grid size chosen later
   size_t total = 256;
   for (int i = 0; i < n; ++i) {
     if (!batchable(ps[i], dtypes[i])) continue;
     Planned pl;
-    plan_problem(ps[i], dtypes[i], pl);
+    plan_problem(ps[i], dtypes[i], ITEM_STAGES_MIN, pl);
     total += pl.partial_bytes;
   }
   return total;
@@ -416,12 +432,26 @@ size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int
 // Launches the batchable problems of ps[0..n) (marks them in done[]); the caller runs the rest one by one.
 int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsigned char* done, void* workspace,
                         size_t workspace_bytes, int flush, cudaStream_t st) {
+  int sm_count = 148;
+  {
+    int dev = 0;
+    SSO_CUDA_OK(cudaGetDevice(&dev));
+    static int cached[64] = {};
+    if (dev >= 0 && dev < 64) {
+      if (!cached[dev]) SSO_CUDA_OK(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+      sm_count = cached[dev];
+    }
+  }
+  // all SM pairs by default; fewer leave SMs to kernels of other streams that run beside the batch
+  int max_pairs = sm_count / 2;
+  if (g_batch_pairs > 0) max_pairs = std::min(max_pairs, g_batch_pairs);
+  const int item_stages = item_stages_for(ps, dtypes, n, max_pairs);
   std::vector<Planned> plans;
   for (int i = 0; i < n; ++i) {
     done[i] = 0;
     if (!batchable(ps[i], dtypes[i])) continue;
     Planned pl;
-    plan_problem(ps[i], dtypes[i], pl);
+    plan_problem(ps[i], dtypes[i], item_stages, pl);
     plans.push_back(pl);
     done[i] = 1;
   }
@@ -438,16 +468,6 @@ int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsign
 
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
   SSO_ENSURE_SMEM(factor_batch_kernel, smem);
-  int sm_count = 148;
-  {
-    int dev = 0;
-    SSO_CUDA_OK(cudaGetDevice(&dev));
-    static int cached[64] = {};
-    if (dev >= 0 && dev < 64) {
-      if (!cached[dev]) SSO_CUDA_OK(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
-      sm_count = cached[dev];
-    }
-  }
   size_t at = 0;
   while (at < plans.size()) {
     const size_t cnt = std::min<size_t>(MAX_PROBLEMS, plans.size() - at);
@@ -501,10 +521,7 @@ int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsign
     }
     bp.nitems = items;
     SSO_CHECK_ARG(fin_smem <= 200 * 1024, "factor batch: kernel window too large for the finishing kernel");
-    // all SM pairs by default; fewer leave SMs to kernels of other streams that run beside the batch
-    int pairs = sm_count / 2;
-    if (g_batch_pairs > 0) pairs = std::min(pairs, g_batch_pairs);
-    pairs = std::max(1, std::min(pairs, items));
+    const int pairs = std::max(1, std::min(max_pairs, items));
     factor_batch_kernel<<<2 * pairs, THREADS, smem, st>>>(bp);
     SSO_LAUNCH_OK("factor_batch_kernel");
     SSO_ENSURE_SMEM(factor_batch_finish_kernel, 200 * 1024);
