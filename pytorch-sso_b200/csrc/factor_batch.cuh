@@ -285,10 +285,10 @@ struct FinParams {
   FinProb prob[MAX_PROBLEMS];
 };
 
-__device__ __forceinline__ float batch_fetch(const float* __restrict__ partial, int nsplit, int r, int c) {
-  const int bi = r >> 7, bj = c >> 7;
-  const float* src = partial + ((int64_t)(bi * (bi + 1) / 2 + bj) * nsplit) * (TILE * TILE) + (r & 127) * TILE + (c & 127);
+// sum over the splits of one element; `src` points at the element inside the first split's tile
+__device__ __forceinline__ float sum_splits(const float* __restrict__ src, int nsplit) {
   constexpr int64_t S = TILE * TILE;
+  if (nsplit == 1) return src[0];
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   int sp = 0;
   for (; sp + 4 <= nsplit; sp += 4) {
@@ -315,28 +315,44 @@ __global__ void __launch_bounds__(256) factor_batch_finish_kernel(const __grid_c
     }
     pi = lo;
   }
-  const FinProb& P = fp.prob[pi];
+  // the record is read once into registers: every later use would be another indexed load from
+  // parameter space
+  const FinProb P = fp.prob[pi];
+  const float* __restrict__ partial = P.partial;
   const int local = blockIdx.x - P.block0;
   const int rb = local / P.groups, grp = local - rb * P.groups;
   const int gi0 = rb * FIN_ROWS;
   const int kk = P.perm_kk, C = P.perm_c, d = P.d, pitch = P.pitch, nsplit = P.splits;
+  const int64_t tile_floats = (int64_t)nsplit * (TILE * TILE);
+  // element (r, c), r >= c, of the lower-triangle partial tiles (first split)
+  auto at = [&](int r, int c) {
+    const int bi = r >> 7, bj = c >> 7;
+    return partial + (int64_t)(bi * (bi + 1) / 2 + bj) * tile_floats + ((r & 127) * TILE + (c & 127));
+  };
   int ext0, n_ext;
   if (grp < P.perm_groups) {
     const int c0 = grp * FIN_CB, len = min(FIN_CB, C - c0);
     ext0 = c0 * kk;
     n_ext = len * kk;
+    // below / on the diagonal: 4 rows x 8 columns per warp (lanes along the run of 8 channels);
+    // above: 32 rows x 1 column per warp, read from the mirrored position (lanes along its columns)
     const int rrA = warp * 4 + (lane >> 3), eA = lane & 7, giA = gi0 + rrA;
     const int rrB = lane, eB = warp, giB = gi0 + rrB;
     const bool okA = eA < len && giA < d, okB = eB < len && giB < d;
+    // fixed parts of the two addresses: A walks along its own row, B down a column of the mirrored tile
+    const int biA = giA >> 7;
+    const float* rowA = partial + (int64_t)(biA * (biA + 1) / 2) * tile_floats + (giA & 127) * TILE;
+    const int bjB = giB >> 7, cjB = giB & 127;
+    float* dstA = rs + rrA * pitch + eA * kk;
+    float* dstB = rs + rrB * pitch + eB * kk;
 #pragma unroll 3
     for (int run = 0; run < kk; ++run) {
       const int gjA = run * C + c0 + eA, gjB = run * C + c0 + eB;
-      float vA = 0.f, vB = 0.f;
-      const bool doA = okA && gjA <= giA, doB = okB && gjB > giB;
-      if (doA) vA = batch_fetch(P.partial, nsplit, giA, gjA);
-      if (doB) vB = batch_fetch(P.partial, nsplit, gjB, giB);
-      if (doA) rs[rrA * pitch + eA * kk + run] = vA;
-      if (doB) rs[rrB * pitch + eB * kk + run] = vB;
+      if (okA && gjA <= giA) dstA[run] = sum_splits(rowA + (int64_t)(gjA >> 7) * tile_floats + (gjA & 127), nsplit);
+      if (okB && gjB > giB) {
+        const int biB = gjB >> 7;
+        dstB[run] = sum_splits(partial + (int64_t)(biB * (biB + 1) / 2 + bjB) * tile_floats + ((gjB & 127) * TILE + cjB), nsplit);
+      }
     }
   } else {
     ext0 = (P.perm_groups > 0 ? P.dcols : 0) + (grp - P.perm_groups) * FIN_W;
@@ -345,26 +361,22 @@ __global__ void __launch_bounds__(256) factor_batch_finish_kernel(const __grid_c
     for (int k = 0; k < 4; ++k) {
       const int rrA = warp + 8 * k, giA = gi0 + rrA, gjA = ext0 + lane;
       const int eB = warp + 8 * k, giB = gi0 + lane, gjB = ext0 + eB;
-      const bool doA = lane < n_ext && giA < d && gjA <= giA;
-      const bool doB = eB < n_ext && giB < d && gjB > giB;
-      float vA = 0.f, vB = 0.f;
-      if (doA) vA = batch_fetch(P.partial, nsplit, giA, gjA);
-      if (doB) vB = batch_fetch(P.partial, nsplit, gjB, giB);
-      if (doA) rs[rrA * pitch + lane] = vA;
-      if (doB) rs[lane * pitch + eB] = vB;
+      if (lane < n_ext && giA < d && gjA <= giA) rs[rrA * pitch + lane] = sum_splits(at(giA, gjA), nsplit);
+      if (eB < n_ext && giB < d && gjB > giB) rs[lane * pitch + eB] = sum_splits(at(gjB, giB), nsplit);
     }
   }
   __syncthreads();
   const bool bad = fp.status && *fp.status != 0;
+  const float alpha = P.alpha, beta = P.beta;
   for (int rr = warp; rr < FIN_ROWS; rr += 8) {
     const int gi = gi0 + rr;
     if (gi >= d) break;
     const int gr = (C > 0 && gi < P.dcols) ? (gi % C) * kk + gi / C : gi;
     float* orow = P.out + (int64_t)gr * P.ldo + ext0;
     for (int e = lane; e < n_ext; e += 32) {
-      float v = P.alpha * rs[rr * pitch + e];
+      float v = alpha * rs[rr * pitch + e];
       if (bad) v = __int_as_float(0x7fc00000);
-      orow[e] = (P.beta == 0.f) ? v : fmaf(P.beta, orow[e], v);
+      orow[e] = (beta == 0.f) ? v : fmaf(beta, orow[e], v);
     }
   }
 }
