@@ -385,6 +385,8 @@ def run_gpu_arm(args):
         # the kernels that build the curvature write the running average in their epilogue
         # (one closure call per step, which is how this loop drives the optimizer)
         opt.fuse_ema = True
+        # ... and the round of inverses starts inside the closure, beside the real backward pass
+        opt.early_inverse = args.early_inverse
     closure = fisher_closure(torchsso, opt, model, x_static, y_static)
     eager_closure = closure
     first = None
@@ -425,7 +427,7 @@ def run_gpu_arm(args):
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = nat.launch_count()
-        r0 = closure.replays if args.graph else 0
+        r0 = closure.library_launches if args.graph else 0
         ev0.record()
         last = None
         for i in range(nsteps):
@@ -442,7 +444,7 @@ def run_gpu_arm(args):
             ms = float(t.item())
         launches = nat.launch_count() - l0
         if args.graph:      # kernels inside the replayed graph are not seen by the host-side counter
-            launches += (closure.replays - r0) * closure.library_kernels_per_replay
+            launches += closure.library_launches - r0
         return ms, launches, float(last.detach()) if torch.is_tensor(last) else float(last)
 
     # warm-up (also builds plans and cuDNN algorithm choices); first step inverts
@@ -475,6 +477,7 @@ def run_gpu_arm(args):
     def step_with(inv):
         opt.update_inv = inv
         opt.step(closure=closure)
+    opt.update_inv = False
     closure_ms = avg_ms(closure_only, 5)
     step_noinv_ms = avg_ms(lambda: step_with(False), 5)
     step_inv_ms = avg_ms(lambda: step_with(True), 3)
@@ -532,6 +535,7 @@ def run_gpu_arm(args):
                    'closure': 'CUDA graph replay' if args.graph else 'eager',
                    'curvature_stream': bool(args.graph and args.side_stream),
                    'factor_launches': 'batched per pass' if args.batching else 'per layer',
+                   'inverses': 'started inside the closure, beside the real backward' if (args.early_inverse and args.fuse_ema and world == 1) else 'after the closure',
                    'ema': 'fused into the factor / BatchNorm epilogues' if (args.fuse_ema and world == 1) else 'separate pass',
                    'parallelism': 'dp%d, factors reduce-scattered to owners' % world if world > 1 else 'single',
                    'l2_policy': 'per-step inputs (%.0f MB activations + 615 MB factor pools) exceed the 126 MB L2'
@@ -615,6 +619,8 @@ def main():
                          'model kernels that run beside it')
     ap.add_argument('--no-fuse-ema', dest='fuse_ema', action='store_false',
                     help='keep curv.data and the separate data -> ema pass (single GPU only; N > 1 always does)')
+    ap.add_argument('--no-early-inverse', dest='early_inverse', action='store_false',
+                    help='run the round of inverses after the closure instead of beside its real backward pass')
     ap.add_argument('--no-graph', dest='graph', action='store_false',
                     help='issue the closure eagerly instead of replaying a captured CUDA graph')
     args = ap.parse_args()

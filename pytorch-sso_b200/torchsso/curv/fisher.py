@@ -94,6 +94,11 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
                 sampling_backward(F.cross_entropy(output, torch.full_like(target, i)), edges)
         set_sampling(False)
         del edges
+        # every G factor is complete now; the real backward below only produces gradients.  An optimizer
+        # with early_inverse set starts its round of inverses here, beside that backward pass.
+        after_sampling = getattr(optimizer, '_after_sampling_passes', None)
+        if after_sampling is not None:
+            after_sampling()
 
         loss = F.cross_entropy(output, target)
         loss.backward()

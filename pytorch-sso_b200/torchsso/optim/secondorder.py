@@ -197,6 +197,37 @@ class SecondOrderOptimizer(Optimizer):
                     c._have.discard('data')
         self.__dict__['_fuse_ema'] = bool(on)
 
+    @property
+    def early_inverse(self):
+        """Start the round of damped inverses inside the Fisher closure, as soon as its sampling passes
+        have finished: with ``fuse_ema`` the running averages of A and G are complete at that point and
+        the real backward pass that follows only produces gradients, so the inverses (issued on the
+        curvature stream when that is enabled) run beside it instead of after it.  Same matrices, same
+        step as ``torchsso/optim/secondorder.py:195-209`` inverts; only the place in the stream
+        changes.  Needs ``fuse_ema`` and ``l2_reg == 0`` (the damping must not depend on this step's
+        bookkeeping).  Closures not built by ``get_closure_for_fisher`` are unaffected."""
+        return self.__dict__.get('_early_inverse', False)
+
+    @early_inverse.setter
+    def early_inverse(self, on):
+        if on:
+            if not self.fuse_ema:
+                raise ValueError('early_inverse needs fuse_ema: the running averages must be complete inside the closure')
+            if any(g['l2_reg'] != 0 for g in self.param_groups):
+                raise ValueError('early_inverse needs l2_reg == 0')
+        self.__dict__['_early_inverse'] = bool(on)
+
+    def _after_sampling_passes(self):
+        if not (self.early_inverse and self.update_inv):
+            return
+        kc = [g['curv'] for g in self.local_param_groups
+              if isinstance(g['curv'], _KronFactors) and _is_pooled(g['curv'])]
+        if not kc:
+            return
+        nat.flush_factors()
+        nat.run_on_curvature_stream(lambda _: self.pool.update_inv(kc, with_std=False), self._grad_flat)
+        self.__dict__['_early_inverse_done'] = True
+
     #: what ``zero_grad()`` does when called without an argument (as the closures do).  True (torch's
     #: own default): set every ``p.grad`` to None, autograd assigns its own tensors and one
     #: multi-tensor copy after the closure brings them into the flat buffer (100 MB more memory for
@@ -380,11 +411,13 @@ class SecondOrderOptimizer(Optimizer):
         else:
             for c in curvs:
                 c.update_ema()
+        early = self.__dict__.pop('_early_inverse_done', False)     # consumed by this step whatever it does
         kc = [g['curv'] for g in kron]
         if kc:
             want_std = [bool(update_std(g)) if update_std else False for g in kron]
             if update_inv:
-                self.pool.update_inv(kc, with_std=any(want_std))
+                if not (early and not any(want_std)):      # else: issued inside the closure already
+                    self.pool.update_inv(kc, with_std=any(want_std))
                 for c in kc:
                     c._have.add('inv')
                     if any(want_std):

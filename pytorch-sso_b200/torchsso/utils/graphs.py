@@ -32,36 +32,63 @@ class GraphedClosure:
         side = torch.cuda.Stream(priority=-1)
         side.wait_stream(torch.cuda.current_stream())
         from torchsso import _native as nat
-        # with optimizer.fuse_ema the hooks advance the running averages: the executions below (warm-up
-        # and the capture itself) are not optimisation steps, so the averages are put back afterwards
+        # with optimizer.fuse_ema the hooks advance the running averages (and with early_inverse the
+        # closure rewrites the inverses): the executions below (warm-up and the captures themselves) are
+        # not optimisation steps, so those buffers are put back afterwards
         saved = []
         if getattr(optimizer, 'fuse_ema', False):
             pool = optimizer.pool
-            saved = [(pool.buf('ema', k), pool.buf('ema', k).clone()) for k in ('k', 'd') if pool.has('ema', k)]
+            roles = ('ema', 'inv') if getattr(optimizer, 'early_inverse', False) else ('ema',)
+            saved = [(pool.buf(r, k), pool.buf(r, k).clone()) for r in roles for k in ('k', 'd') if pool.has(r, k)]
+        # an optimizer that starts its inverses inside the closure needs one graph per kind of step
+        variants = [False, True] if getattr(optimizer, 'early_inverse', False) else [None]
+        keep_update_inv = optimizer.update_inv
         with torch.cuda.stream(side):
             for _ in range(max(1, warmup)):
+                if variants[0] is not None:
+                    optimizer.update_inv = False
                 closure()
                 nat.join_curvature_stream(None)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        before = nat.launch_count()
-        with torch.cuda.graph(self.graph, stream=side):
-            self.result = closure()
-            nat.join_curvature_stream(None)      # forked curvature kernels rejoin inside the capture
+        self._graphs, self._results, self._grads, self._launches = {}, {}, {}, {}
+        mem_pool = None
+        for v in variants:
+            if v is not None:
+                optimizer.update_inv = v
+            graph = torch.cuda.CUDAGraph()
+            before = nat.launch_count()
+            with torch.cuda.graph(graph, stream=side, pool=mem_pool):
+                result = closure()
+                nat.join_curvature_stream(None)      # forked curvature kernels rejoin inside the capture
+            optimizer.__dict__.pop('_early_inverse_done', None)
+            mem_pool = graph.pool()
+            self._graphs[v], self._results[v] = graph, result
+            self._grads[v] = [p.grad for p in params]
+            self._launches[v] = nat.launch_count() - before
+        optimizer.update_inv = keep_update_inv
         torch.cuda.synchronize()
         for buf, copy in saved:
             buf.copy_(copy)
-        #: kernels of libsso_b200 inside the graph, i.e. launched by every replay
-        self.library_kernels_per_replay = nat.launch_count() - before
+        self.graph = self._graphs[variants[0]]
+        self.result = self._results[variants[0]]
+        #: kernels of libsso_b200 inside the graph, i.e. launched by every replay (of a step without
+        #: inverses when there are two graphs)
+        self.library_kernels_per_replay = self._launches[variants[0]]
+        #: kernels of libsso_b200 launched by all replays so far
+        self.library_launches = 0
         self.replays = 0
         self._params = params
-        self._grads = [p.grad for p in params]
+        self._two = variants[0] is not None
 
     def __call__(self):
-        self.graph.replay()
+        v = bool(self.optimizer.update_inv) if self._two else None
+        self._graphs[v].replay()
         self.replays += 1
-        for p, g in zip(self._params, self._grads):
+        self.library_launches += self._launches[v]
+        if v:
+            self.optimizer.__dict__['_early_inverse_done'] = True
+        for p, g in zip(self._params, self._grads[v]):
             if p.grad is not g:
                 p.grad = g
-        return self.result
+        return self._results[v]

@@ -460,6 +460,50 @@ def test_fused_ema_equals_separate_pass(torchsso_mod, monkeypatch, graphed):
         assert rel(b, a.cpu().numpy()) < 3e-5        # one fused multiply-add instead of two rounded steps, over four updates
 
 
+@pytest.mark.parametrize('graphed', [False, True])
+def test_early_inverse_equals_inverse_after_closure(torchsso_mod, monkeypatch, graphed):
+    """optimizer.early_inverse: the round of inverses issued inside the closure (after the sampling
+    passes, on the curvature stream, beside the real backward pass) gives the same parameters as
+    the round issued after the closure; from a replayed graph there is one graph per kind of step."""
+    torchsso = torchsso_mod
+    state = {}
+
+    def run(early):
+        patch_targets(monkeypatch, torchsso, state)
+        model = cases.make_model('tiny_convnet', seed=1).cuda()
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, {'ema_decay': 0.9, 'damping': 1e-3}, lr=1e-2)
+        opt.fuse_ema = True
+        opt.early_inverse = early
+        xs = torch.empty((6, 3, 8, 8), device='cuda')
+        ys = torch.empty((6,), dtype=torch.int64, device='cuda')
+        closure = torchsso.get_closure_for_fisher(opt, model, xs, ys, approx_type='mc', num_mc=2)
+        step_closure = closure
+        torchsso.utils.set_curvature_stream(True)
+        try:
+            for t in range(5):
+                x, y = cases.make_batch((6, 3, 8, 8), 5, seed=100 + min(t, 1) if graphed else 100 + t)
+                xs.copy_(x); ys.copy_(y)
+                state['u'] = cases.make_uniform((2, 6), seed=200 + t)
+                if t == 1 and graphed:
+                    with torch.no_grad():
+                        fixed = inverse_cdf_targets(torch.softmax(model(xs), dim=1).float().cpu(), state['u']).cuda()
+                    monkeypatch.setattr(torchsso.curv.fisher, 'sample_targets', lambda prob, num_mc: fixed)
+                    bn = {k: v.clone() for k, v in model.state_dict().items()}
+                    step_closure = torchsso.utils.GraphedClosure(opt, closure)
+                    model.load_state_dict(bn)
+                opt.update_inv = t in (0, 2, 3)
+                opt.step(closure=step_closure)
+                opt.pool.check_info()
+        finally:
+            torchsso.utils.set_curvature_stream(False)
+        invs = [e.clone() for g in opt.param_groups for e in g['curv'].inv]
+        return invs + [p.detach().clone() for p in model.parameters()]
+
+    a, b = run(False), run(True)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
 def test_fisher_sampling_survives_nan_probabilities(torchsso_mod):
     """NaN / zero rows in the predictive distribution (a diverged model) must not reach the
     sampling kernel's device-side assertion."""
