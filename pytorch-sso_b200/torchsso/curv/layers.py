@@ -114,8 +114,8 @@ class _KronFactors(KronCurvature):
         key = (x.shape, x.stride(), x.dtype, out.data_ptr())
         op = ops.get(key)
         if op is None:
-            if len(ops) > 16:
-                ops.clear()
+            while len(ops) >= 16:          # oldest first: a second input shape must not evict the first
+                ops.pop(next(iter(ops)))
             op = nat.FactorOp(x, *geometry, append_ones, out)
             ops[key] = op
         return op
@@ -289,8 +289,8 @@ class _DiagBatchNorm(DiagCurvature):
         key = (t.shape, t.stride(), t.dtype, t.data_ptr() % 16)
         ent = cache.get(key)
         if ent is None:
-            if len(cache) > 16:
-                cache.clear()
+            while len(cache) >= 16:
+                cache.pop(next(iter(cache)))
             t2, st, splits = nat.bn_plane_layout(t)
             ent = (st, splits, t2 is t)
             cache[key] = ent

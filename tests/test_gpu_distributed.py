@@ -97,30 +97,89 @@ def test_data_parallel_equals_accumulation(world, balance):
     mp.spawn(_worker, args=(world, _free_port(), balance, ret), nprocs=world, join=True)
     sizes = [len(p) for p in ret['indices']]
     assert sum(sizes) == 16
+    # the ranks' shards are summed by the collective, the accumulation adds them one after the other:
+    # differences of one rounding, carried through three preconditioned updates
     for rank in range(world):
-        assert _worst(ret[rank], ref) < 2e-5, (rank, _worst(ret[rank], ref))
+        assert _worst(ret[rank], ref) < 1e-4, (rank, _worst(ret[rank], ref))
     for rank in range(1, world):
         for a, b in zip(ret[0], ret[rank]):
             assert torch.equal(a, b), 'ranks disagree after the all-gather'
 
 
-def test_two_gpu_half_precision_wire_with_scaling():
-    """fp16 on the wire: the gradients of this network (~1e-3) and its G factors (carrying n^2) span
-    orders of magnitude; with per-array scaling the update stays within fp16 rounding of the fp32
-    exchange, and it is closer than the plain cast."""
+def _wire_worker(rank, world, port, ret):
+    """Arrays from 1e-6 (a gradient vector) to 1e+5 (a factor) through the device packer and the
+    sso_wire_* kernels: owner `rank` must receive the world mean of its arrays to fp16 rounding with the
+    per-array scaling, and must NOT with the plain cast (underflow / overflow)."""
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    os.environ['NCCL_NVLS_ENABLE'] = '0'
+    torch.cuda.set_device(rank)
+    device = torch.device('cuda', rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    try:
+        from torchsso.utils.communicator import KFACCommunicator
+        dims = [37, 130]
+
+        def arrays_of(r):
+            out = []
+            for owner in range(world):
+                g = torch.Generator().manual_seed(1000 * r + owner)
+                n = dims[owner]
+                grad = torch.randn(n + 3, generator=g) * 1e-6
+                m = torch.randn(n, n, generator=g) * 1e5
+                out.append([grad, m + m.t()])
+            return out
+        mine = [[(t.to(device), t.dim() == 2) for t in local] for local in arrays_of(rank)]
+        expect = [sum(arrays_of(r)[rank][j] for r in range(world)) / world for j in range(2)]
+        result = {}
+        for scaling in (True, False):
+            arrays = [[(t.clone(), tri) for t, tri in local] for local in mine]
+            comm = KFACCommunicator(wire_dtype=torch.float16, wire_scaling=scaling)
+            comm.reduce_scatterv_arrays(arrays)
+            torch.cuda.synchronize()
+            errs = []
+            for (got, _), exp in zip(arrays[rank], expect):
+                e = ((got.cpu().double() - exp.double()).norm() / exp.double().norm()).item()
+                errs.append(e if e == e else float('inf'))
+            result[scaling] = errs
+            if scaling:
+                comm.allgatherv_arrays(arrays)       # the owners' values, again to fp16 rounding
+                torch.cuda.synchronize()
+                for owner in range(world):
+                    exp_o = [sum(arrays_of(r)[owner][j] for r in range(world)) / world for j in range(2)]
+                    for (got, _), exp in zip(arrays[owner], exp_o):
+                        e = ((got.cpu().double() - exp.double()).norm() / exp.double().norm()).item()
+                        assert e < 4e-3, ('all-gather', owner, e)
+        ret[rank] = result
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_half_precision_wire_needs_its_scaling():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_wire_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for rank in range(2):
+        scaled, plain = ret[rank][True], ret[rank][False]
+        assert max(scaled) < 2e-3, (rank, scaled)
+        assert max(plain) > 1e-2, (rank, plain)      # 1e-6 underflows fp16's 11 bits, 1e5 overflows its range
+
+
+def test_two_gpu_half_precision_wire_in_the_optimizer():
+    """The distributed optimizer with fp16 on the wire (per-array scaling on): three steps stay within
+    fp16 rounding, amplified by the preconditioner, of the fp32 exchange."""
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
     ref = _run_single(torch.device('cuda', 0), 2)
     mgr = mp.Manager()
-    errs = {}
-    for scaling in (True, False):
-        ret = mgr.dict()
-        mp.spawn(_worker, args=(2, _free_port(), 'inverse_cost', ret, torch.float16, scaling), nprocs=2, join=True)
-        errs[scaling] = _worst(ret[0], ref)
-        for a, b in zip(ret[0], ret[1]):
-            assert torch.equal(a, b)
-    assert errs[True] < 2e-2, errs
-    assert errs[True] <= errs[False] or not (errs[False] == errs[False]), errs
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(2, _free_port(), 'inverse_cost', ret, torch.float16, True), nprocs=2, join=True)
+    assert _worst(ret[0], ref) < 5e-2, _worst(ret[0], ref)
+    for a, b in zip(ret[0], ret[1]):
+        assert torch.equal(a, b)
 
 
 # ---------------------------------------------------------------------------------------------
