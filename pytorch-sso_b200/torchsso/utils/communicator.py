@@ -299,6 +299,12 @@ class KFACCommunicator:
         backend = dist.get_backend(self.group)
         if backend == 'nccl':
             dist.all_gather_into_tensor(recv, send, group=self.group)
+        elif send.is_cuda:
+            # gloo carries device tensors through the host and implements all_reduce for them: place the
+            # own segment into a zeroed buffer and sum (ranks that share one GPU in tests take this path)
+            recv.zero_()
+            recv[self.rank * seg:(self.rank + 1) * seg].copy_(send)
+            dist.all_reduce(recv, op=dist.ReduceOp.SUM, group=self.group)
         else:
             parts = [recv[r * seg:(r + 1) * seg] for r in range(self.size)]
             dist.all_gather(parts, send, group=self.group)
