@@ -2,9 +2,14 @@
 
 Grads and curvature data are averaged over ranks with equal weights, so N-rank data parallel
 training equals one process with ``acc_steps = N`` fed the N shards in rank order (batch-norm
-statistics are per shard in both).  Each case needs as many GPUs as ranks and is skipped
-otherwise.  The model has 13 Kronecker layers of very different sizes, so the two ownership
-rules give different, unbalanced partitions with padded segments."""
+statistics are per shard in both).  The model has 13 Kronecker layers of very different sizes, so the
+two ownership rules give different, unbalanced partitions with padded segments.
+
+Two ways of running the ranks: over NCCL with one GPU per rank (each case needs as many GPUs as ranks
+and is skipped otherwise), and over gloo with all ranks sharing GPU 0 (runs anywhere there is one GPU:
+same optimizer, ownership, device packer and exchange logic; only the collective's transport differs).
+Two steps: the preconditioned update multiplies a difference of one rounding by ~30 per step on this
+net (measured), so longer runs only test that amplification."""
 import os
 import socket
 
@@ -19,7 +24,8 @@ pytestmark = pytest.mark.gpu
 
 KRON = {'Linear': 'Kron', 'Conv2d': 'Kron', 'BatchNorm1d': 'Diag', 'BatchNorm2d': 'Diag'}
 KW = {'ema_decay': 0.95, 'damping': 1e-3}
-STEPS = 3
+STEPS = 2
+LR = 1e-3
 
 
 def _free_port():
@@ -39,7 +45,7 @@ def _shard(step, rank):
 def _run_single(device, world):
     import torchsso
     model = cases.make_model('uneven_net', seed=1).to(device)
-    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=1e-2, acc_steps=world)
+    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=LR, acc_steps=world)
     state = {}
     torchsso.curv.fisher.sample_targets = \
         lambda prob, num_mc: inverse_cdf_targets(prob.detach().float().cpu(), state['u']).to(prob.device)
@@ -52,19 +58,23 @@ def _run_single(device, world):
     return [p.detach().cpu().clone() for p in model.parameters()]
 
 
-def _worker(rank, world, port, balance, ret, wire=None, scaling=True):
+def _worker(rank, world, port, balance, ret, wire=None, scaling=True, backend='nccl'):
     import torch.distributed as dist
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     os.environ['NCCL_NVLS_ENABLE'] = '0'
-    torch.cuda.set_device(rank)
-    device = torch.device('cuda', rank)
-    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    index = rank if backend == 'nccl' else 0           # gloo ranks share GPU 0
+    torch.cuda.set_device(index)
+    device = torch.device('cuda', index)
+    if backend == 'nccl':
+        dist.init_process_group('nccl', rank=rank, world_size=world, device_id=device)
+    else:
+        dist.init_process_group('gloo', rank=rank, world_size=world)
     try:
         import torchsso
         model = cases.make_model('uneven_net', seed=1).to(device)
         comm = torchsso.utils.create_communicator(wire_dtype=wire, wire_scaling=scaling)
-        opt = torchsso.optim.DistributedSecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=1e-2,
+        opt = torchsso.optim.DistributedSecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=LR,
                                                              balance=balance, comm=comm)
         state = {}
         torchsso.curv.fisher.sample_targets = \
@@ -156,6 +166,22 @@ def _wire_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize('world', [2, 4])
+@pytest.mark.parametrize('balance', ['inverse_cost', 'contiguous'])
+def test_data_parallel_equals_accumulation_ranks_sharing_one_gpu(world, balance):
+    """The same equivalence with gloo ranks that all use GPU 0."""
+    ref = _run_single(torch.device('cuda', 0), world)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), balance, ret, None, True, 'gloo'), nprocs=world, join=True)
+    assert sum(len(p) for p in ret['indices']) == 16
+    for rank in range(world):
+        assert _worst(ret[rank], ref) < 2e-5, (rank, _worst(ret[rank], ref))
+    for rank in range(1, world):
+        for a, b in zip(ret[0], ret[rank]):
+            assert torch.equal(a, b), 'ranks disagree after the all-gather'
+
+
 def test_two_gpu_half_precision_wire_needs_its_scaling():
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
@@ -186,7 +212,8 @@ def test_two_gpu_half_precision_wire_in_the_optimizer():
 # MC-sample parallel VI: two ranks with one weight sample each on the SAME batch equal one process
 # with two samples, when rank r draws the noise the single process draws for its sample r.
 # ---------------------------------------------------------------------------------------------
-VI_STEPS = 3
+VI_STEPS = 2
+LR = 1e-3
 
 
 def _vi_setup(device, num_mc, distributed):
