@@ -47,14 +47,18 @@ def _run_single(device, world):
     model = cases.make_model('uneven_net', seed=1).to(device)
     opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', KRON, KW, lr=LR, acc_steps=world)
     state = {}
+    original = torchsso.curv.fisher.sample_targets
     torchsso.curv.fisher.sample_targets = \
         lambda prob, num_mc: inverse_cdf_targets(prob.detach().float().cpu(), state['u']).to(prob.device)
-    for step in range(STEPS):
-        for rank in range(world):
-            x, y, state['u'] = _shard(step, rank)
-            closure = torchsso.get_closure_for_fisher(opt, model, x.to(device), y.to(device),
-                                                      approx_type='mc', num_mc=1)
-            opt.step(closure=closure)
+    try:
+        for step in range(STEPS):
+            for rank in range(world):
+                x, y, state['u'] = _shard(step, rank)
+                closure = torchsso.get_closure_for_fisher(opt, model, x.to(device), y.to(device),
+                                                          approx_type='mc', num_mc=1)
+                opt.step(closure=closure)
+    finally:
+        torchsso.curv.fisher.sample_targets = original       # this runs in the test process itself
     return [p.detach().cpu().clone() for p in model.parameters()]
 
 
