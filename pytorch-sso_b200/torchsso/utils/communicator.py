@@ -209,8 +209,11 @@ class KFACCommunicator:
             self._all_gather(recv, send, seg, arrays)
         else:
             recv = send
+        # with a 16-bit wire the owner takes the rounded values back too: every rank must hold the same
+        # bits, or the replicas drift apart by one wire rounding per step
+        rounded = self.wire_dtype is not None and self.size > 1
         for r, local in enumerate(arrays):
-            if local and r != self.rank:
+            if local and (r != self.rank or rounded):
                 self.packer.unpack(local, recv, r * seg, symmetric)
         self.last_bytes['agv'] = (4 if self.wire_dtype is None else 2) * seg * self.size
 

@@ -108,6 +108,12 @@ def _worker(rank, world, port, dims, ret, wire_dtype=None, rtol=1e-6, spread=Fal
                                            for r in range(world)])
             for (got, _), e in zip(arrays[owner], exp):
                 assert _close(got, e, 2 * rtol)
+        # the replicas hold the same bits (with a 16-bit wire the owner takes the rounded values too)
+        flat = torch.cat([t.reshape(-1) for local in arrays for t, _ in local]).clone()
+        lo, hi = flat.clone(), flat.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert torch.equal(lo, hi), 'ranks disagree after the all-gather'
         sizes, seg = comm.segment_sizes(arrays)
         assert seg % 64 == 0 and seg >= max(sizes)
         ret[rank] = 'ok'
