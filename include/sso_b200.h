@@ -274,7 +274,8 @@ typedef struct {
   float alpha, beta;
 } sso_tile_task;
 
-/* diagonal-block record: factor block (<= 64 x 64) in place, also write the inverse of its factor */
+/* diagonal-block record: factor block (<= 64 x 64 in a phase of kind 2, <= 128 x 128 in one of kind 5) in
+   place, also write the inverse of its factor */
 typedef struct {
   float* L;           /* block (j,j) of the working matrix; lower triangle valid on entry */
   float* Linv;        /* receives the inverse of the block's Cholesky factor */
@@ -301,7 +302,8 @@ typedef struct {
 } sso_copy_rec;
 
 typedef struct {
-  int32_t kind;       /* 0 gemm64, 1 gemm128, 2 diag-block factor, 3 copy, 4 gemm128 whose operands are both read along k */
+  int32_t kind;       /* 0 gemm64, 1 gemm128, 2 diag-block factor (<= 64), 3 copy, 4 gemm128 whose operands are both read along k,
+                         5 diag-block factor of a 128-column panel (same records as 2, size <= 128) */
   int32_t first;      /* first record of this phase in its table */
   int32_t count;      /* number of records (= CTAs) */
   int32_t reserved;

@@ -67,7 +67,7 @@ static int g_tma_auto = 1;   // whether SSO_IMPL_AUTO may pick the TMA-fed tcgen
 
 using namespace sso;
 
-namespace sso { extern int g_engine_tma; extern int g_chol_ksplit; extern int g_phase_lpt; }
+namespace sso { extern int g_engine_tma; extern int g_chol_ksplit; extern int g_phase_lpt; extern int g_chol_panel; }
 
 extern "C" {
 
@@ -88,6 +88,7 @@ int sso_configure(const char* key, int value) {
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }
   if (k == "phase_lpt") { g_phase_lpt = value != 0; return 0; }
   if (k == "chol_ksplit") { g_chol_ksplit = (int)value; return 0; }
+  if (k == "chol_panel") { g_chol_panel = value != 0; return 0; }
   // failure-path controls, current device only: the limit of every bounded device-side wait in units of
   // 1024 clocks (0 = the default of ~2 s), and a switch that makes the TMA producers of the factor and
   // tile-task kernels issue no loads, so that the waits of their consumers run out

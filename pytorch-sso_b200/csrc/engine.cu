@@ -4,11 +4,12 @@
 // (one kernel launch per phase, covering every matrix of every layer) plus a dense 64x64
 // diagonal-block factorisation done by one CTA in shared memory.
 //
-// Blocked algorithm per SPD matrix M (block size 64, nb = ceil(d/64)):
-//   Cholesky (right looking), step j:
-//       diag   : L_jj = chol(M_jj), also Linv_jj = L_jj^-1          (diag-block kernel)
-//       panel  : L_ij = M_ij * Linv_jj^T                 for i > j  (tile tasks)
-//       update : M_ik -= L_ij * L_kj^T                   for i >= k > j
+// Blocked algorithm per SPD matrix M (panels of 128 columns, left looking):
+//   Cholesky, panel p:
+//       update : M_ip -= sum_{k<p} L_ik * L_pk^T         for i >= p (128-wide tile tasks, long K)
+//       diag   : L_pp = chol(M_pp), also Linv_pp = L_pp^-1          (diag-panel kernel, one CTA)
+//       panel  : L_ip = M_ip * Linv_pp^T                 for i > p  (128-wide tile tasks)
+//     (with "chol_panel" off: the same with two 64-wide halves per panel and the 64x64 diag-block kernel)
 //   Triangular inverse by recursive doubling over block ranges [first | second]:
 //       Y   = L_21 * Inv_11          (into scratch)      Inv_21 = - Inv_22 * Y
 //   Inverse:  M^-1 = Linv^T * Linv   (lower tiles computed, mirrored into the upper triangle)
@@ -18,6 +19,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "diag_panel.cuh"
 
 namespace sso {
 
@@ -29,6 +31,7 @@ int g_phase_lpt = 1;    // tasks of a 128-wide phase sorted by decreasing K
 int g_chol_ksplit = 6;  // Cholesky panel updates from this panel index on are cut along K (0: never)
 int g_engine_tma = 1;   // k-contiguous 128-wide tasks fetch their operands with TMA (tensor maps per task)
 int g_engine_tc = 1;    // run 128-wide tile phases on the tensor cores (3xTF32) instead of FFMA
+int g_chol_panel = 1;   // factorise a 128-column panel's diagonal block in one launch (else two 64-wide halves)
 
 constexpr int NB = 64;  // algorithmic block size of the factorisations
 
@@ -527,6 +530,30 @@ static void emit_cholesky(Builder& b, const std::vector<Mat>& ms, int info_slot)
       }
     b.end_phase(1, first, b.task_begin() - first);
     b.end_phase(3, first_sum, (int)b.p.copies.size() - first_sum);
+    if (g_chol_panel) {
+      // the panel's 128x128 diagonal block in one launch (factor, inverse and its transpose), then the
+      // rows below as 128-wide tasks with K = 128:  L_ip = M_ip * Linv_pp^T, in place
+      first = (int)b.p.diags.size();
+      for (auto& m : ms)
+        if (p * PB < m.d) {
+          DiagRec r;
+          r.L = blk2(m.W, m.ld, p, p); r.Linv = blk2(m.Li, m.ld, p, p);
+          r.ld_l = m.ld; r.ld_inv = m.ld; r.size = std::min(PB, m.d - p * PB); r.mat = m.mat_index; r.row0 = p * PB;
+          r.info_slot = info_slot;
+          r.LinvT = m.X ? blk2(m.X, m.ldx, p, p) : nullptr; r.ld_invt = m.ldx; r.pad = 0;
+          b.p.diags.push_back(r);
+        }
+      b.end_phase(5, first, (int)b.p.diags.size() - first);
+      first = b.task_begin();
+      for (auto& m : ms) {
+        const int np = (m.d + PB - 1) / PB;
+        for (int i = p + 1; i < np; ++i)
+          b.gemm(blk2(m.W, m.ld, i, p), m.ld, false, blk2(m.Li, m.ld, p, p), m.ld, true,
+                 blk2(m.W, m.ld, i, p), m.ld, std::min(PB, m.d - i * PB), PB, PB, 1.f, 0.f);
+      }
+      b.end_phase(1, first, b.task_begin() - first);
+      continue;
+    }
     for (int half = 0; half < 2; ++half) {
       const int j = 2 * p + half;
       if (half == 1) {   // second block column of the panel: update by the first
@@ -682,6 +709,10 @@ static int run_phases(const Plan& p, const std::vector<sso_phase>& phases, int* 
         tile_task_kernel<8><<<ph.count, 256, 0, st>>>(p.d_tasks + ph.first);
         break;
       case 2: diag_block_kernel<<<ph.count, 256, 0, st>>>(p.d_diags + ph.first, info); break;
+      case 5:
+        SSO_ENSURE_SMEM((dpanel::diag_panel_kernel), dpanel::SMEM_BYTES);
+        dpanel::diag_panel_kernel<<<ph.count, dpanel::THREADS, dpanel::SMEM_BYTES, st>>>(p.d_diags + ph.first, info);
+        break;
       case 3: copy_kernel<<<ph.count, 256, 0, st>>>(p.d_copies + ph.first, p.d_shift); break;
       default: return fail(-1, "bad phase kind %d", ph.kind);
     }
@@ -729,7 +760,8 @@ static Plan* build_kron(int n, const int64_t* dims, float* const* src, float* co
     // triangular inverse by recursive doubling over block ranges [lo,mid) | [mid,hi)
     int max_nb = 0;
     for (auto& m : ms) max_nb = std::max(max_nb, m.nb);
-    for (int s = 1; s < max_nb; s *= 2) {
+    // (the panel kernel has already inverted whole 128x128 diagonal blocks: the first level is done)
+    for (int s = g_chol_panel ? 2 : 1; s < max_nb; s *= 2) {
       // from s = 2 on every range boundary is a multiple of two blocks: 128x128 tasks (the
       // zero blocks just above the diagonal of Li make the wider K ranges harmless)
       const int w = s == 1 ? 1 : 2;

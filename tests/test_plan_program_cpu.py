@@ -62,7 +62,8 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
                 mem.view(t.C, t.m, t.n, t.ldc)[...] = val
                 if t.C2:
                     mem.view(t.C2, t.n, t.m, t.ldc2)[...] = val.T
-        elif kind == 2:
+        elif kind in (2, 5):    # diagonal block: 64-wide, or a whole 128-column panel's
+            assert all(diags[i].size <= (64 if kind == 2 else 128) for i in range(first, first + count))
             for r in [diags[i] for i in range(first, first + count)]:
                 Lv = mem.view(r.L, r.size, r.size, r.ld_l)
                 blk = np.tril(Lv).astype(np.float64)
@@ -70,7 +71,9 @@ def run_program(plan, mem, shift=None, scale_alpha=None):
                 try:
                     L = np.linalg.cholesky(blk)
                 except np.linalg.LinAlgError:
-                    info[(r.mat, r.info_slot)] = r.row0 + 1
+                    # LAPACK numbering, as the kernels report it: the first pivot that is not positive
+                    bad = next(j for j in range(r.size) if np.linalg.eigvalsh(blk[:j + 1, :j + 1]).min() <= 0)
+                    info[(r.mat, r.info_slot)] = r.row0 + bad + 1
                     L = np.eye(r.size)
                 Lv[...] = L.astype(np.float32)
                 Linv = np.linalg.inv(L).astype(np.float32)
@@ -207,7 +210,7 @@ def test_kron_program_reports_bad_pivot():
                          [-1], [0], device=None, host_only=True)
     mem.bufs.append(plan.host_mem)
     info = run_program(plan, mem, shift=[0.0])
-    assert info == {(0, 0): 65}          # first row of the failing block, 1-based
+    assert info == {(0, 0): 67}          # the failing pivot (row 66), 1-based
 
 
 @pytest.mark.parametrize('dA,dG,bias', [(21, 16, True), (130, 70, True), (300, 129, False), (64, 1, True)])
