@@ -7,16 +7,20 @@
 // the 16 threads of a row of the grid touch 16 consecutive shared-memory rows, which at a pitch of 132
 // floats are 4 banks apart: 16-byte loads without conflicts).  Right-looking over panels of 16 columns:
 //   publish : the owners write panel k (rows >= 16 k) into shared memory
-//   factor  : one warp, lane = row, factorises the 16x16 diagonal block with shuffles (16 pivots, each a
-//             broadcast of the pivot, an rsqrt, a column scale and a rank-1 update of the lane's row)
+//   factor  : one warp, lane = row, factorises the 16x16 diagonal block: per pivot one round of shuffles
+//             (the raw column, and the next diagonal element so that the next pivot's rsqrt starts early)
 //   solve   : one thread per row below solves its 16 unknowns against that block (forward substitution)
 //   update  : every thread subtracts the panel's outer product from its registers
 // i.e. three block barriers per 16 columns instead of one per column.  The finished factor sits in shared
 // memory; its inverse follows by the inverses of the eight 16x16 diagonal blocks (one warp each, lane =
 // column) and three levels of doubling, Inv21 = -Inv22 * (L21 * Inv11), with the product L21 * Inv11
 // parked in the (otherwise unused) upper triangle.  Rows and columns past the block's size behave as an
-// identity block.  A non-positive or NaN pivot is recorded once per matrix (LAPACK numbering) and
-// replaced by 1, like the 64-wide kernel does.
+// identity block.  A pivot that is not a positive normal number (non-positive, denormal or NaN) is recorded
+// once per matrix (LAPACK numbering) and replaced by 1, like the 64-wide kernel does for non-positive ones.
+// Measured (d = 4608, 36 panels): 24 us per launch against 2 x 44 us for the two 64-wide factorisations plus
+// 2 x 14 us of 64-wide panel tasks it replaces; what is left is bound by shared-memory bandwidth (trailing
+// update and doubling products: 16-byte loads cost four cycles each for the whole SM) and by the chain of
+// 128 pivots (86 cycles each).
 #pragma once
 #include "common.cuh"
 
@@ -29,6 +33,12 @@ constexpr int PK = 16;         // panel width inside the block
 constexpr int THREADS = 256;
 constexpr size_t SMEM_BYTES = (size_t)(2 * PN * PP + PN) * sizeof(float);
 
+// MUFU.RSQ alone (2 ulp); the argument is a positive normal number wherever this is called
+__device__ __forceinline__ float rsqrt_approx(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float x, float y, float z, float w) {
   *reinterpret_cast<float4*>(p) = make_float4(x, y, z, w);
@@ -54,7 +64,7 @@ __device__ __forceinline__ void doubling_product(float* __restrict__ S, float* _
     // Y[r][c] = sum_q L[mid + r][lo + q] * Inv[lo + q][lo + c], Inv11[q][c] = 0 for q < c
     const float* Lr = S + (mid + ty) * PP + lo;
     const float* Vc = V + lo * PP + lo + tx;
-#pragma unroll 4
+#pragma unroll 8
     for (int q = 0; q < SZ / 2; ++q) {      // meets the columns of the first half only (all of them if NT == 1)
       float l[NT];
 #pragma unroll
@@ -66,7 +76,7 @@ __device__ __forceinline__ void doubling_product(float* __restrict__ S, float* _
         for (int a = 0; a < NT; ++a) acc[a][b] = fmaf(l[a], v, acc[a][b]);
       }
     }
-#pragma unroll 4
+#pragma unroll 8
     for (int q = SZ / 2; q < SZ; ++q) {
       float l[NT];
 #pragma unroll
@@ -87,7 +97,7 @@ __device__ __forceinline__ void doubling_product(float* __restrict__ S, float* _
     // Inv21[r][c] = -sum_q Inv[mid + r][mid + q] * Y[q][c], Inv22[r][q] = 0 for q > r
     const float* Vr = V + (mid + ty) * PP + mid;
     const float* Yc = S + lo * PP + mid + tx;
-#pragma unroll 4
+#pragma unroll 8
     for (int q = 0; q < SZ / 2; ++q) {
       float y[NT];
 #pragma unroll
@@ -99,7 +109,7 @@ __device__ __forceinline__ void doubling_product(float* __restrict__ S, float* _
         for (int b = 0; b < NT; ++b) acc[a][b] = fmaf(v, y[b], acc[a][b]);
       }
     }
-#pragma unroll 4
+#pragma unroll 8
     for (int q = SZ / 2; q < SZ; ++q) {     // meets the rows of the second half only (all of them if NT == 1)
       float y[NT];
 #pragma unroll
@@ -126,6 +136,49 @@ __device__ __forceinline__ void doubling_level(float* S, float* V, int cols, int
   __syncthreads();
   for (int lo = 0; lo + SZ < cols; lo += 2 * SZ) doubling_product<SZ>(S, V, lo, 1, ty, tx);
   __syncthreads();
+}
+
+// Panel K of the thread's elements goes to shared memory (rows >= 16 K).
+template <int K>
+__device__ __forceinline__ void publish_panel(const float (&a)[8][8], float* __restrict__ S, int ty, int tx) {
+#pragma unroll
+  for (int i = K; i < 8; ++i) S[(ty + 16 * i) * PP + PK * K + tx] = a[i][K];
+}
+
+// a[i][j] -= sum_q L[row_i][16 K + q] * L[col_j][16 K + q] for K < j <= i, four q at a time.  K is a template
+// parameter so that the loop body is straight-line code: a branch per block column costs a single warp
+// more than the multiply-adds it guards.  Rows past the matrix hold zeros in the published panel.
+template <int K>
+__device__ __forceinline__ void update_trailing(float (&a)[8][8], const float* __restrict__ S, int ty, int tx) {
+  if (K >= 7) return;
+  const float* rbase = S + ty * PP + PK * K;
+  const float* cbase = S + tx * PP + PK * K;
+#pragma unroll 1
+  for (int qc = 0; qc < PK / 4; ++qc) {
+    float4 rv[8], cv[8];
+#pragma unroll
+    for (int i = K + 1; i < 8; ++i) {
+      rv[i] = ld4(rbase + 16 * i * PP + 4 * qc);
+      cv[i] = ld4(cbase + 16 * i * PP + 4 * qc);
+    }
+    // one component of the four at a time over all pairs: consecutive multiply-adds are independent
+#pragma unroll
+    for (int j = K + 1; j < 8; ++j)
+#pragma unroll
+      for (int i = j; i < 8; ++i) a[i][j] = fmaf(-rv[i].x, cv[j].x, a[i][j]);
+#pragma unroll
+    for (int j = K + 1; j < 8; ++j)
+#pragma unroll
+      for (int i = j; i < 8; ++i) a[i][j] = fmaf(-rv[i].y, cv[j].y, a[i][j]);
+#pragma unroll
+    for (int j = K + 1; j < 8; ++j)
+#pragma unroll
+      for (int i = j; i < 8; ++i) a[i][j] = fmaf(-rv[i].z, cv[j].z, a[i][j]);
+#pragma unroll
+    for (int j = K + 1; j < 8; ++j)
+#pragma unroll
+      for (int i = j; i < 8; ++i) a[i][j] = fmaf(-rv[i].w, cv[j].w, a[i][j]);
+  }
 }
 
 __global__ void __launch_bounds__(THREADS, 1) diag_panel_kernel(const sso_diag_rec* __restrict__ recs,
@@ -157,14 +210,20 @@ __global__ void __launch_bounds__(THREADS, 1) diag_panel_kernel(const sso_diag_r
   for (int k = 0; k < np; ++k) {
     const int c0 = PK * k;
     // ---- publish panel k
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (j == k) {
-#pragma unroll
-        for (int i = j; i < 8; ++i) S[(ty + 16 * i) * PP + c0 + tx] = a[i][j];
-      }
+    switch (k) {
+      case 0: publish_panel<0>(a, S, ty, tx); break;
+      case 1: publish_panel<1>(a, S, ty, tx); break;
+      case 2: publish_panel<2>(a, S, ty, tx); break;
+      case 3: publish_panel<3>(a, S, ty, tx); break;
+      case 4: publish_panel<4>(a, S, ty, tx); break;
+      case 5: publish_panel<5>(a, S, ty, tx); break;
+      case 6: publish_panel<6>(a, S, ty, tx); break;
+      default: publish_panel<7>(a, S, ty, tx); break;
+    }
     __syncthreads();
-    // ---- 16x16 diagonal block: lane l (and its twin l + 16) holds row l
+    // ---- 16x16 diagonal block by warp 0: lane l (and its twin l + 16) holds row l.  One exchange per pivot:
+    // every lane fetches the raw column j (pivot included) from the lanes that own it, takes the rsqrt of
+    // the pivot itself and applies the rank-1 update to its own row.
     if (warp == 0) {
       const int l = lane & 15;
       float* row = S + (c0 + l) * PP + c0;
@@ -177,24 +236,36 @@ __global__ void __launch_bounds__(THREADS, 1) diag_panel_kernel(const sso_diag_r
 #pragma unroll
       for (int c = 0; c < PK; ++c)
         if (c > l) r[c] = 0.f;
+      // The pivot of step j + 1 is formed inside step j from the next raw diagonal element (fetched with
+      // the column) by the same multiply-add its owner applies to it: the rsqrt of the next pivot then runs
+      // while the shuffles of the next column are in flight, instead of after them.
+      float pv = __shfl_sync(0xffffffffu, r[0], 0);
+      int first_bad = -1;
 #pragma unroll
       for (int j = 0; j < PK; ++j) {
-        float pv = __shfl_sync(0xffffffffu, r[j], j);
-        if (!(pv > 0.f)) {      // non-positive or NaN pivot: record once, continue with 1
-          if (lane == 0 && info && c0 + j < n)
-            atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + c0 + j + 1);
-          pv = 1.f;
-        }
-        const float rs = rsqrtf(pv);
-        const float lj = (l == j) ? sqrtf(pv) : r[j] * rs;      // rows above the pivot hold 0
+        float t[PK];
+#pragma unroll
+        for (int c = j + 1; c < PK; ++c) t[c] = __shfl_sync(0xffffffffu, r[j], c);     // a[c][j], c > j
+        float d1 = 0.f;
+        if (j + 1 < PK) d1 = __shfl_sync(0xffffffffu, r[j + 1], j + 1);                // a[j+1][j+1] before this step
+        // a pivot that is not a positive normal number (or is NaN) is remembered and replaced by 1; no branch
+        // here: the chain from one pivot to the next is what bounds this kernel
+        const bool bad = !(pv >= 1.17549435e-38f);
+        if (bad && first_bad < 0) first_bad = j;
+        pv = bad ? 1.f : pv;
+        const float rs = rsqrt_approx(pv);
+        const float lj = (l == j) ? pv * rs : r[j] * rs;      // L[l][j]; rows above the pivot hold 0
+#pragma unroll
+        for (int c = j + 1; c < PK; ++c) r[c] = fmaf(-lj, t[c] * rs, r[c]);            // kept for c <= l only
         r[j] = lj;
         if (lane == j) dinv[c0 + j] = rs;
-#pragma unroll
-        for (int c = j + 1; c < PK; ++c) {
-          const float t = __shfl_sync(0xffffffffu, lj, c);       // L[c][j]
-          r[c] = fmaf(-lj, t, r[c]);                             // only columns c <= l are kept below
+        if (j + 1 < PK) {
+          const float x = t[j + 1] * rs;
+          pv = fmaf(-x, x, d1);
         }
       }
+      if (first_bad >= 0 && lane == 0 && info && c0 + first_bad < n)
+        atomicCAS(info + 2 * rec.mat + rec.info_slot, 0, rec.row0 + c0 + first_bad + 1);
       if (lane < PK) {
 #pragma unroll
         for (int q = 0; q < PK; q += 4)
@@ -203,11 +274,13 @@ __global__ void __launch_bounds__(THREADS, 1) diag_panel_kernel(const sso_diag_r
       }
     }
     __syncthreads();
-    // ---- rows below the diagonal block: x * L16^T = a, one thread per row
+    // ---- rows below the diagonal block: x * L16^T = a, one thread per row, right looking (each finished
+    // unknown is subtracted from all later ones at once, so the dependent chain is two operations per step)
     {
       const int rowi = c0 + PK + tid;
       if (rowi < cols) {
         float* xr = S + rowi * PP + c0;
+        const float* lblk = S + c0 * PP + c0;            // same addresses in every lane: broadcast
         float x[PK];
 #pragma unroll
         for (int q = 0; q < PK; q += 4) {
@@ -216,47 +289,25 @@ __global__ void __launch_bounds__(THREADS, 1) diag_panel_kernel(const sso_diag_r
         }
 #pragma unroll
         for (int c = 0; c < PK; ++c) {
-          const float* lrow = S + (c0 + c) * PP + c0;    // same address in every lane: broadcast
-          float lr[PK];
+          x[c] *= dinv[c0 + c];
 #pragma unroll
-          for (int q = 0; q < c; q += 4) {
-            const float4 v = ld4(lrow + q);
-            lr[q] = v.x; lr[q + 1] = v.y; lr[q + 2] = v.z; lr[q + 3] = v.w;
-          }
-          float s = x[c];
-#pragma unroll
-          for (int q = 0; q < c; ++q) s = fmaf(-x[q], lr[q], s);
-          x[c] = s * dinv[c0 + c];
+          for (int c2 = c + 1; c2 < PK; ++c2) x[c2] = fmaf(-x[c], lblk[c2 * PP + c], x[c2]);
         }
 #pragma unroll
         for (int q = 0; q < PK; q += 4) st4(xr + q, x[q], x[q + 1], x[q + 2], x[q + 3]);
       }
     }
     __syncthreads();
-    // ---- trailing update: a[i][j] -= sum_q L[row_i][c0 + q] * L[col_j][c0 + q] for k < j <= i
+    // ---- trailing update
     if (k + 1 < np) {
-#pragma unroll
-      for (int qc = 0; qc < PK / 4; ++qc) {
-        float4 rv[8];
-#pragma unroll
-        for (int i = 1; i < 8; ++i) {
-          rv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (i > k && i < np) rv[i] = ld4(S + (ty + 16 * i) * PP + c0 + 4 * qc);
-        }
-#pragma unroll
-        for (int j = 1; j < 8; ++j)
-          if (j > k && j < np) {
-            const float4 cv = ld4(S + (tx + 16 * j) * PP + c0 + 4 * qc);
-#pragma unroll
-            for (int i = j; i < 8; ++i) {
-              float t = a[i][j];
-              t = fmaf(-rv[i].x, cv.x, t);
-              t = fmaf(-rv[i].y, cv.y, t);
-              t = fmaf(-rv[i].z, cv.z, t);
-              t = fmaf(-rv[i].w, cv.w, t);
-              a[i][j] = t;
-            }
-          }
+      switch (k) {
+        case 0: update_trailing<0>(a, S, ty, tx); break;
+        case 1: update_trailing<1>(a, S, ty, tx); break;
+        case 2: update_trailing<2>(a, S, ty, tx); break;
+        case 3: update_trailing<3>(a, S, ty, tx); break;
+        case 4: update_trailing<4>(a, S, ty, tx); break;
+        case 5: update_trailing<5>(a, S, ty, tx); break;
+        default: update_trailing<6>(a, S, ty, tx); break;
       }
     }
   }
@@ -292,14 +343,29 @@ __global__ void __launch_bounds__(THREADS, 1) diag_panel_kernel(const sso_diag_r
   doubling_level<16>(S, V, cols, ty, tx);
   doubling_level<32>(S, V, cols, ty, tx);
   doubling_level<64>(S, V, cols, ty, tx);
-  // ---- results: L (lower, zeros above), L^-1 (same) and optionally its transpose
-  for (int e = tid; e < n * PN; e += THREADS) {
-    const int r = e >> 7, c = e & (PN - 1);
-    if (c < n) {
-      const bool low = c <= r;
-      rec.L[(int64_t)r * rec.ld_l + c] = low ? S[r * PP + c] : 0.f;
-      rec.Linv[(int64_t)r * rec.ld_inv + c] = low ? V[r * PP + c] : 0.f;
-      if (rec.LinvT) rec.LinvT[(int64_t)r * rec.ld_invt + c] = (c >= r) ? V[c * PP + r] : 0.f;
+  // ---- results: the lower triangle of L, L^-1 with zeros above its diagonal, and optionally the upper
+  // triangle of the transpose of L^-1.  Nothing reads L above the diagonal, and the buffer of the transpose
+  // is zeroed before the factorisation starts.
+  for (int r = warp; r < n; r += THREADS / 32) {
+    float* lrow = rec.L + (int64_t)r * rec.ld_l;
+    float* vrow = rec.Linv + (int64_t)r * rec.ld_inv;
+    float* trow = rec.LinvT ? rec.LinvT + (int64_t)r * rec.ld_invt : nullptr;
+    float lv[4], vv[4], tv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {           // all loads of the row first, then all stores
+      const int c = lane + 32 * u;
+      lv[u] = S[r * PP + c];
+      vv[u] = V[r * PP + c];
+      tv[u] = V[c * PP + r];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = lane + 32 * u;
+      if (c < n) {
+        if (c <= r) lrow[c] = lv[u];
+        vrow[c] = (c <= r) ? vv[u] : 0.f;     // read in full (K = 128) by the tasks of the rows below
+        if (trow && c >= r) trow[c] = tv[u];
+      }
     }
   }
 }
