@@ -211,7 +211,8 @@ def suite_peaks(args):
 def suite_steps(args):
     """Whole optimizer steps of the smaller reference configurations (fp32, eager launches, a fresh
     seeded batch every step): the 784-1000-1000-10 MLP at batch 128 with inverses every step, the
-    5x5/5x5/3x3 ConvNet at batch 256 with inverses every 5 steps, and the VGG-16-style network under
+    5x5/5x5/3x3 ConvNet at batch 256 with inverses every 5 steps (also with four Monte Carlo targets per
+    step, as one batched sampling pass and as one pass per target), and the VGG-16-style network under
     VIOptimizer with 4 weight samples per step at batch 128."""
     import torch.nn as nn
     import torch.nn.functional as F
@@ -309,6 +310,21 @@ def suite_steps(args):
         opt2.update_inv = (i % 5 == 0)
         return opt2.step(closure=closure2)[0]
     run('convnet 5x5-5x5-3x3 + 4096-512-10, Fisher MC, inverse every 5', step_conv, 256, args.iters * 2)
+
+    # the same ConvNet with four Monte Carlo targets per step: one walk of the graph for all of them
+    # against one walk per target (the reference's loop, torchsso/curv/fisher/__init__.py:65-72)
+    for batched in (True, False):
+        model4 = ConvNet().to(dev)
+        opt4 = torchsso.optim.SecondOrderOptimizer(model4, 'Fisher', kron, kw, lr=1e-3)
+        closure4 = torchsso.get_closure_for_fisher(opt4, model4, x2, y2, approx_type='mc', num_mc=4,
+                                                   batch_mc_passes=batched)
+
+        def step_mc(i):
+            x2.copy_(xs2[i % 8]); y2.copy_(ys2[i % 8])
+            opt4.update_inv = (i % 5 == 0)
+            return opt4.step(closure=closure4)[0]
+        run('convnet, Fisher MC with 4 targets, %s' % ('one batched sampling pass' if batched else 'one pass per target'),
+            step_mc, 256, args.iters * 2)
 
     # VGG-16-style under VIOptimizer, 4 weight samples per step
     model3 = VGG().to(dev)

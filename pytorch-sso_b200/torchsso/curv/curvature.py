@@ -146,6 +146,8 @@ class Curvature(object):
                 d['output_edge'] = torch.autograd.graph.get_gradient_edge(output)
 
     def _backward_hook(self, grad_output):
+        if self.__dict__.get('_mute_hook'):
+            return      # a batched walk of the graph: its caller feeds the kernels slice by slice afterwards
         self.backward_postprocess(self._module, None, (grad_output,))
 
     def backward_postprocess(self, module, grad_input, grad_output):

@@ -7,7 +7,20 @@ The reference freezes the parameters for the sampling passes (requires_grad = Fa
 forward), which still computes every weight gradient and drops it at the accumulation node.
 Here a sampling pass asks autograd for the output gradients of the hooked modules only
 (``prune_sampling_pass=True``, the default): the hooks see the same values, the weight-gradient
-kernels of those passes never run.  ``prune_sampling_pass=False`` is the reference's protocol."""
+kernels of those passes never run.  ``prune_sampling_pass=False`` is the reference's protocol.
+
+With several Monte Carlo targets the reference walks the graph once per target
+(torchsso/curv/fisher/__init__.py:65-72).  A backward pass is linear in the gradient it starts
+from, so the ``num_mc`` walks can be one (``batch_mc_passes=True``, needs the pruned pass): autograd
+is asked for the output gradients of all targets at once
+(``torch.autograd.grad(..., is_grads_batched=True)``: every backward op runs once on tensors with a
+leading target dimension), the hooks stay silent during that walk (they would be handed batched
+tensors that have no address), and the curvature kernels are then fed target by target with the
+slices of the returned gradients, exactly as the hooks would have been.  Off by default, by
+measurement (ResNet-50, batch 32, bf16, 4 targets, B200): issued eagerly the single walk saves host
+time (47.4 against 52.1 ms per step), but replayed from a CUDA graph, where launches are free, the
+batched backward kernels that vmap selects are slower than four plain walks (40.5 against 30.7 ms);
+the 5x5 ConvNet at batch 256: 9.7 against 9.2 ms."""
 from __future__ import annotations
 
 import torch
@@ -34,7 +47,11 @@ def sample_targets(prob: torch.Tensor, num_mc: int) -> torch.Tensor:
 
 
 def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num_mc=1,
-                           prune_sampling_pass=True):
+                           prune_sampling_pass=True, batch_mc_passes=False):
+
+    if batch_mc_passes and not prune_sampling_pass:
+        raise ValueError('batch_mc_passes needs prune_sampling_pass: the batched walk returns the output '
+                         'gradients of the hooked modules instead of running their hooks')
 
     def set_sampling(on: bool):
         for group in optimizer.param_groups:
@@ -56,6 +73,24 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
         # beside whatever the closure does next (the next pass accumulates onto them)
         nat.flush_factors()
 
+    def batched_sampling_backward(output, mc_targets, curvs, edges):
+        """All Monte Carlo targets in one walk of the graph, then the hooks' work target by target."""
+        losses = torch.stack([F.cross_entropy(output, mc_targets[i]) for i in range(num_mc)])
+        seeds = torch.eye(num_mc, device=losses.device, dtype=losses.dtype)
+        for curv in curvs:
+            curv.__dict__['_mute_hook'] = True
+        try:
+            grads = torch.autograd.grad(losses, edges, grad_outputs=seeds, is_grads_batched=True,
+                                        retain_graph=True, allow_unused=True)
+        finally:
+            for curv in curvs:
+                curv.__dict__['_mute_hook'] = False
+        for i in range(num_mc):
+            for curv, g in zip(curvs, grads):
+                if g is not None:
+                    curv.backward_postprocess(curv.module, None, (g[i],))
+            nat.flush_factors()
+
     def closure():
         for group in optimizer.param_groups:
             assert isinstance(group['curv'], Fisher), f"Invalid Curvature type: {type(group['curv'])}."
@@ -67,12 +102,13 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
         nat.flush_factors()          # batched factor construction: all A factors of the forward pass
         prob = F.softmax(output, dim=1)
 
-        edges = []
+        edges, edge_curvs = [], []
         if prune_sampling_pass:
             for group in optimizer.param_groups:
                 edge = group['curv'].module.__dict__.pop('output_edge', None)
                 if edge is not None:
                     edges.append(edge)
+                    edge_curvs.append(group['curv'])
             if not edges:
                 raise RuntimeError('no hooked module produced an output that requires grad')
 
@@ -83,8 +119,11 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
             for group in optimizer.param_groups:
                 group['curv'].prob = weight
                 group['curv'].prob_scale = 1.0 / num_mc
-            for i in range(num_mc):
-                sampling_backward(F.cross_entropy(output, mc_targets[i]), edges)
+            if batch_mc_passes and prune_sampling_pass and num_mc > 1:
+                batched_sampling_backward(output, mc_targets, edge_curvs, edges)
+            else:
+                for i in range(num_mc):
+                    sampling_backward(F.cross_entropy(output, mc_targets[i]), edges)
         else:
             for i in range(model.num_classes):
                 weight = prob[:, i].detach().float().contiguous()
@@ -93,7 +132,7 @@ def get_closure_for_fisher(optimizer, model, data, target, approx_type=None, num
                     group['curv'].prob_scale = None
                 sampling_backward(F.cross_entropy(output, torch.full_like(target, i)), edges)
         set_sampling(False)
-        del edges
+        del edges, edge_curvs
         # every G factor is complete now; the real backward below only produces gradients.  An optimizer
         # with early_inverse set starts its round of inverses here, beside that backward pass.
         after_sampling = getattr(optimizer, '_after_sampling_passes', None)

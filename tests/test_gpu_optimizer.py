@@ -59,10 +59,12 @@ def check(gold, tag, opt, f_tol, i_tol, with_std=False, grad_floor=1e-30):
             assert rel(p.grad, gold['%s/g%d/grad%d' % (tag, gi, j)], grad_floor) < i_tol * 3, (tag, gi, 'grad', j)
 
 
-@pytest.mark.parametrize('prune', [True, False])
-def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch, prune):
+@pytest.mark.parametrize('prune,batched', [(True, True), (True, False), (False, False)])
+def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch, prune, batched):
     """prune: the sampling passes ask autograd for the hooked output gradients only (default) or
-    run the reference's full backward with frozen parameters; same vectors either way."""
+    run the reference's full backward with frozen parameters; batched: the two Monte Carlo targets
+    share one walk of the graph or take one each (default), as in the reference
+    (torchsso/curv/fisher/__init__.py:65-72); same vectors every way."""
     torchsso = torchsso_mod
     gold = load('tiny_convnet_fisher')
     state = {}
@@ -75,7 +77,7 @@ def test_tiny_convnet_fisher_mc(torchsso_mod, monkeypatch, prune):
         state['u'] = cases.make_uniform((2, 6), seed=200 + t)
         opt.update_inv = (t != 2)
         closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2,
-                                                  prune_sampling_pass=prune)
+                                                  prune_sampling_pass=prune, batch_mc_passes=batched)
         loss, _ = opt.step(closure=closure)
         for group in opt.param_groups:
             assert 'output_edge' not in group['curv'].module.__dict__ or not prune
@@ -101,7 +103,10 @@ def test_tiny_convnet_diag_fisher_and_cov(torchsso_mod, monkeypatch):
     for t in range(2):
         x, y = cases.make_batch((6, 3, 8, 8), 5, seed=500 + t)
         state['u'] = cases.make_uniform((2, 6), seed=600 + t)
-        closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2)
+        # (second step: both targets in one batched walk of the graph, whose slices then feed the
+        # BatchNorm and squared-gradient kernels)
+        closure = torchsso.get_closure_for_fisher(opt, model, x.cuda(), y.cuda(), approx_type='mc', num_mc=2,
+                                                  batch_mc_passes=(t == 1))
         loss, _ = opt.step(closure=closure)
         assert abs(loss.item() - float(gold['fisher%d/loss' % t])) < 1e-4
         # the bias of a convolution that feeds a BatchNorm has a gradient of pure rounding noise
