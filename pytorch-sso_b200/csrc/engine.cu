@@ -306,17 +306,28 @@ __global__ void __launch_bounds__(256) copy_kernel(const CopyRec* __restrict__ r
   if (r.mode == 3) {
     // dst (a tile of nrows x d) += its r.mat partial products, which sit side by side 128 columns
     // apart starting at src; summed in that order
+    // Four elements per thread at a time, all their loads (up to 32) issued before the first store: one
+    // element at a time, the loads of the next would wait behind the store of the previous to the same array.
     const int total = r.nrows * d;
-    for (int e = threadIdx.x; e < total; e += 256) {
-      const int row = e / d, col = e - row * d;
-      const int64_t o = (int64_t)row * ld + col;
-      float x = r.dst[o];
-      float pv[7];      // at most 7 partial products (8 slices); the loads are independent of each other
+    for (int e0 = threadIdx.x; e0 < total; e0 += 4 * 256) {
+      float x[4], pv[4][7];     // at most 7 partial products (8 slices)
+      int64_t o[4];
 #pragma unroll
-      for (int q = 0; q < 7; ++q) pv[q] = q < r.mat ? r.src[o + q * 128] : 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + 256 * j;
+        const int row = e / d, col = e - row * d;
+        o[j] = (int64_t)row * ld + col;
+        const bool in = e < total;
+        x[j] = in ? r.dst[o[j]] : 0.f;
 #pragma unroll
-      for (int q = 0; q < 7; ++q) x += pv[q];
-      r.dst[o] = x;
+        for (int q = 0; q < 7; ++q) pv[j][q] = (in && q < r.mat) ? r.src[o[j] + q * 128] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int q = 0; q < 7; ++q) x[j] += pv[j][q];
+        if (e0 + 256 * j < total) r.dst[o[j]] = x[j];
+      }
     }
     return;
   }

@@ -157,13 +157,41 @@ __device__ __forceinline__ void accumulate_and_store(const sso_tile_task& t, uin
   asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
   {
     const bool sym = (t.flags & 4u) != 0;
-    for (int rr = warp; rr < t.m; rr += EPI_WARPS) {
-      float* crow = t.C + (int64_t)rr * t.ldc;
-      for (int c = lane; c < t.n; c += 32) {
-        // symmetric tile: only the lower half was computed to be used; mirror it
-        float v = (sym && c > rr) ? ct[c * CT_LD + rr] : ct[rr * CT_LD + c];
-        if (t.beta != 0.f) v = fmaf(t.beta, crow[c], v);
-        crow[c] = v;
+    if (t.beta != 0.f) {
+      // an updated tile: the old values of four rows (16 loads per lane) are fetched before anything is
+      // stored; one row at a time, every load would wait behind the previous row's stores to the same
+      // array, i.e. 64 round trips to L2 in a row per warp (measured: 29 us against 13 us for the same
+      // task with beta = 0)
+      for (int r0 = warp; r0 < t.m; r0 += 4 * EPI_WARPS) {
+        float old[4][TILE / 32];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = r0 + j * EPI_WARPS;
+#pragma unroll
+          for (int u = 0; u < TILE / 32; ++u) {
+            const int c = lane + 32 * u;
+            old[j][u] = (rr < t.m && c < t.n) ? t.C[(int64_t)rr * t.ldc + c] : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = r0 + j * EPI_WARPS;
+#pragma unroll
+          for (int u = 0; u < TILE / 32; ++u) {
+            const int c = lane + 32 * u;
+            if (rr < t.m && c < t.n) {
+              const float v = (sym && c > rr) ? ct[c * CT_LD + rr] : ct[rr * CT_LD + c];
+              t.C[(int64_t)rr * t.ldc + c] = fmaf(t.beta, old[j][u], v);
+            }
+          }
+        }
+      }
+    } else {
+      for (int rr = warp; rr < t.m; rr += EPI_WARPS) {
+        float* crow = t.C + (int64_t)rr * t.ldc;
+        for (int c = lane; c < t.n; c += 32)
+          // symmetric tile: only the lower half was computed to be used; mirror it
+          crow[c] = (sym && c > rr) ? ct[c * CT_LD + rr] : ct[rr * CT_LD + c];
       }
     }
   }
