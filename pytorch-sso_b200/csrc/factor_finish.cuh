@@ -70,22 +70,37 @@ __device__ __forceinline__ void write_tile(const FactorParams& p, int bi, int bj
   const bool bad = p.status && *reinterpret_cast<volatile int*>(p.status) != 0;
   const float nanv = __int_as_float(0x7fc00000);
   const bool diag = (bi == bj);
-  for (int r = warp; r < vr; r += nw) {
-    float* orow = p.out + (int64_t)(bi * T + r) * p.ldo + bj * T;
-    for (int c = lane; c < vc; c += 32) {
-      // diagonal tile: the value above the diagonal is the mirrored one, so that out == out^T bit for bit
-      float v = p.alpha * ((diag && c > r) ? ct[c * CT_LD + r] : ct[r * CT_LD + c]);
-      if (bad) v = nanv;
-      orow[c] = (p.beta == 0.f) ? v : fmaf(p.beta, orow[c], v);
-    }
-  }
-  if (diag) return;
-  for (int c = warp; c < vc; c += nw) {
-    float* orow = p.out + (int64_t)(bj * T + c) * p.ldo + bi * T;
-    for (int r = lane; r < vr; r += 32) {
-      float v = p.alpha * ct[r * CT_LD + c];
-      if (bad) v = nanv;
-      orow[r] = (p.beta == 0.f) ? v : fmaf(p.beta, orow[r], v);
+  // Rows go four at a time: with beta != 0 the old values of all four (16 loads per lane) are fetched
+  // before the first store; row by row, each load would wait behind the previous row's stores to the
+  // same array, a chain of round trips to L2 as long as the tile is high.
+  // pass 0: the tile itself (row r of the tile, lanes along its columns); pass 1: its mirror
+  for (int pass = 0; pass < (diag ? 1 : 2); ++pass) {
+    const int rows = pass == 0 ? vr : vc, cols = pass == 0 ? vc : vr;
+    float* obase = pass == 0 ? p.out + (int64_t)(bi * T) * p.ldo + bj * T : p.out + (int64_t)(bj * T) * p.ldo + bi * T;
+    for (int r0 = warp; r0 < rows; r0 += 4 * nw) {
+      float old[4][T / 32];
+      if (p.beta != 0.f) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int u = 0; u < T / 32; ++u) {
+            const int r = r0 + j * nw, c = lane + 32 * u;
+            old[j][u] = (r < rows && c < cols) ? obase[(int64_t)r * p.ldo + c] : 0.f;
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int u = 0; u < T / 32; ++u) {
+          const int r = r0 + j * nw, c = lane + 32 * u;
+          if (r < rows && c < cols) {
+            // diagonal tile: the value above the diagonal is the mirrored one, so that out == out^T bit for bit
+            float v = pass == 0 ? p.alpha * ((diag && c > r) ? ct[c * CT_LD + r] : ct[r * CT_LD + c])
+                                : p.alpha * ct[c * CT_LD + r];
+            if (bad) v = nanv;
+            obase[(int64_t)r * p.ldo + c] = (p.beta == 0.f) ? v : fmaf(p.beta, old[j][u], v);
+          }
+        }
     }
   }
 }
