@@ -285,67 +285,73 @@ def suite_steps(args):
              images_per_sec=round(batch / ms * 1e3, 1), last_loss=round(float(loss), 4))
 
     torch.manual_seed(0)
-    # MLP, inverse every step
-    model = MLP().to(dev)
-    opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', kron, kw, lr=1e-2)
-    xs, ys = batches((128, 1, 28, 28), 10)
-    x, y = xs[0].clone(), ys[0].clone()
-    closure = torchsso.get_closure_for_fisher(opt, model, x, y, approx_type='mc', num_mc=1)
+    want = lambda k: args.case is None or args.case == k      # --case: 0 MLP, 1 ConvNet, 2 ConvNet with 4 targets, 3 VGG / VI
+    if want(0):
+        # MLP, inverse every step
+        model = MLP().to(dev)
+        opt = torchsso.optim.SecondOrderOptimizer(model, 'Fisher', kron, kw, lr=1e-2)
+        xs, ys = batches((128, 1, 28, 28), 10)
+        x, y = xs[0].clone(), ys[0].clone()
+        closure = torchsso.get_closure_for_fisher(opt, model, x, y, approx_type='mc', num_mc=1)
 
-    def step_mlp(i):
-        x.copy_(xs[i % 8]); y.copy_(ys[i % 8])
-        opt.update_inv = True
-        return opt.step(closure=closure)[0]
-    run('mlp 784-1000-1000-10, Fisher MC, inverse every step', step_mlp, 128, args.iters * 3)
+        def step_mlp(i):
+            x.copy_(xs[i % 8]); y.copy_(ys[i % 8])
+            opt.update_inv = True
+            return opt.step(closure=closure)[0]
+        run('mlp 784-1000-1000-10, Fisher MC, inverse every step', step_mlp, 128, args.iters * 3)
 
-    # ConvNet (NCHW, as a reference user would run it), inverse every 5 steps
-    model2 = ConvNet().to(dev)
-    opt2 = torchsso.optim.SecondOrderOptimizer(model2, 'Fisher', kron, kw, lr=1e-3)
-    xs2, ys2 = batches((256, 3, 32, 32), 10)
-    x2, y2 = xs2[0].clone(), ys2[0].clone()
-    closure2 = torchsso.get_closure_for_fisher(opt2, model2, x2, y2, approx_type='mc', num_mc=1)
+    if want(1) or want(2):
+        # ConvNet (NCHW, as a reference user would run it), inverse every 5 steps
+        model2 = ConvNet().to(dev)
+        opt2 = torchsso.optim.SecondOrderOptimizer(model2, 'Fisher', kron, kw, lr=1e-3)
+        xs2, ys2 = batches((256, 3, 32, 32), 10)
+        x2, y2 = xs2[0].clone(), ys2[0].clone()
+    if want(1):
+        closure2 = torchsso.get_closure_for_fisher(opt2, model2, x2, y2, approx_type='mc', num_mc=1)
 
-    def step_conv(i):
-        x2.copy_(xs2[i % 8]); y2.copy_(ys2[i % 8])
-        opt2.update_inv = (i % 5 == 0)
-        return opt2.step(closure=closure2)[0]
-    run('convnet 5x5-5x5-3x3 + 4096-512-10, Fisher MC, inverse every 5', step_conv, 256, args.iters * 2)
-
-    # the same ConvNet with four Monte Carlo targets per step: one walk of the graph for all of them
-    # against one walk per target (the reference's loop, torchsso/curv/fisher/__init__.py:65-72)
-    for batched in (True, False):
-        model4 = ConvNet().to(dev)
-        opt4 = torchsso.optim.SecondOrderOptimizer(model4, 'Fisher', kron, kw, lr=1e-3)
-        closure4 = torchsso.get_closure_for_fisher(opt4, model4, x2, y2, approx_type='mc', num_mc=4,
-                                                   batch_mc_passes=batched)
-
-        def step_mc(i):
+        def step_conv(i):
             x2.copy_(xs2[i % 8]); y2.copy_(ys2[i % 8])
-            opt4.update_inv = (i % 5 == 0)
-            return opt4.step(closure=closure4)[0]
-        run('convnet, Fisher MC with 4 targets, %s' % ('one batched sampling pass' if batched else 'one pass per target'),
-            step_mc, 256, args.iters * 2)
+            opt2.update_inv = (i % 5 == 0)
+            return opt2.step(closure=closure2)[0]
+        run('convnet 5x5-5x5-3x3 + 4096-512-10, Fisher MC, inverse every 5', step_conv, 256, args.iters * 2)
 
-    # VGG-16-style under VIOptimizer, 4 weight samples per step
-    model3 = VGG().to(dev)
-    # kl_weighting 0.01 (the start value of the reference's warm-up, vi.py:302-319): with 1.0 the weight
-    # noise of the untrained network overflows the activations on N(0,1) inputs within two steps
-    opt3 = torchsso.optim.VIOptimizer(model3, 50000, 'Cov', kron, kw, lr=1e-3, num_mc_samples=4,
-                                      kl_weighting=0.01, prior_variance=1)
-    xs3, ys3 = batches((128, 3, 32, 32), 100, count=4)
-    x3, y3 = xs3[0].clone(), ys3[0].clone()
+    if want(2):
+        # the same ConvNet with four Monte Carlo targets per step: one walk of the graph for all of them
+        # against one walk per target (the reference's loop, torchsso/curv/fisher/__init__.py:65-72)
+        for batched in (True, False):
+            model4 = ConvNet().to(dev)
+            opt4 = torchsso.optim.SecondOrderOptimizer(model4, 'Fisher', kron, kw, lr=1e-3)
+            closure4 = torchsso.get_closure_for_fisher(opt4, model4, x2, y2, approx_type='mc', num_mc=4,
+                                                       batch_mc_passes=batched)
 
-    def closure3():
-        opt3.zero_grad()
-        o = model3(x3)
-        loss = F.cross_entropy(o, y3)
-        loss.backward()
-        return loss, o
+            def step_mc(i):
+                x2.copy_(xs2[i % 8]); y2.copy_(ys2[i % 8])
+                opt4.update_inv = (i % 5 == 0)
+                return opt4.step(closure=closure4)[0]
+            run('convnet, Fisher MC with 4 targets, %s' % ('one batched sampling pass' if batched else 'one pass per target'),
+                step_mc, 256, args.iters * 2)
 
-    def step_vi(i):
-        x3.copy_(xs3[i % 4]); y3.copy_(ys3[i % 4])
-        return opt3.step(closure=closure3)[0]
-    run('vgg16-style, VIOptimizer, 4 MC samples, inverse + std every step', step_vi, 128, max(3, args.iters // 2))
+    if want(3):
+        # VGG-16-style under VIOptimizer, 4 weight samples per step
+        model3 = VGG().to(dev)
+        # kl_weighting 0.01 (the start value of the reference's warm-up, vi.py:302-319): with 1.0 the weight
+        # noise of the untrained network overflows the activations on N(0,1) inputs within two steps
+        opt3 = torchsso.optim.VIOptimizer(model3, 50000, 'Cov', kron, kw, lr=1e-3, num_mc_samples=4,
+                                          kl_weighting=0.01, prior_variance=1)
+        xs3, ys3 = batches((128, 3, 32, 32), 100, count=4)
+        x3, y3 = xs3[0].clone(), ys3[0].clone()
+
+        def closure3():
+            opt3.zero_grad()
+            o = model3(x3)
+            loss = F.cross_entropy(o, y3)
+            loss.backward()
+            return loss, o
+
+        def step_vi(i):
+            x3.copy_(xs3[i % 4]); y3.copy_(ys3[i % 4])
+            return opt3.step(closure=closure3)[0]
+        run('vgg16-style, VIOptimizer, 4 MC samples, inverse + std every step', step_vi, 128, max(3, args.iters // 2))
 
 
 def suite_collective(args):
