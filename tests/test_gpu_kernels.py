@@ -483,6 +483,41 @@ def test_kron_inverse_reports_non_spd(nat):
     assert int(info[1]) == 0
 
 
+@pytest.mark.parametrize('panel', [1, 0])
+def test_kron_inverse_block_sizes_and_pivot_positions(nat, panel):
+    """One launch factorises a whole 128-column panel's diagonal block in panels of 16 columns (or, with
+    "chol_panel" 0, two 64-wide halves): sizes on both sides of every internal boundary, all in one plan,
+    against the fp64 oracle; then a non-positive pivot at several positions, reported LAPACK style."""
+    nat.configure('chol_panel', panel)
+    try:
+        dims = [1, 2, 15, 16, 17, 31, 33, 63, 64, 65, 100, 127, 128, 129, 143, 144, 145, 255, 257, 300]
+        mats = [spd_pair(d, 8, 700 + d)[0] + 1e-2 * torch.eye(d) for d in dims]
+        src = [dev(m) for m in mats]
+        dst = [torch.full_like(m, float('nan')) for m in src]
+        work = [torch.full_like(m, float('nan')) for m in src]
+        std = [torch.full_like(m, float('nan')) for m in src]
+        plan = nat.kron_plan(dims, src, dst, work, std, [-1] * len(dims), [0] * len(dims), torch.device('cuda'))
+        info = torch.zeros(2 * len(dims), dtype=torch.int32, device='cuda')
+        nat.kron_plan_run(plan, torch.zeros(len(dims), device='cuda'), info, True, True)
+        assert int(info.abs().sum()) == 0
+        for d, m, got, u in zip(dims, mats, dst, std):
+            ref = ko.spd_inverse(m.double())
+            assert rel(got, ref) < INV_TOL, d
+            assert torch.equal(got, got.t()), d
+            assert rel(u, ko.cholesky_upper(ref)) < INV_TOL, d
+        for d, bad in ((40, 0), (40, 15), (40, 16), (130, 70), (130, 127), (130, 128), (300, 299)):
+            A = spd_pair(d, 8, 900 + d)[0] + 1e-2 * torch.eye(d)
+            A[bad, bad] = -1.0
+            s1 = dev(A)
+            d1, w1 = torch.empty_like(s1), torch.empty_like(s1)
+            plan = nat.kron_plan([d], [s1], [d1], [w1], None, [-1], [0], torch.device('cuda'))
+            info = torch.zeros(2, dtype=torch.int32, device='cuda')
+            nat.kron_plan_run(plan, torch.zeros(1, device='cuda'), info, True, False)
+            assert int(info[0]) == bad + 1, (d, bad, int(info[0]))
+    finally:
+        nat.configure('chol_panel', 1)
+
+
 def test_utils_inv_and_cholesky(nat):
     import torchsso
     A, _ = spd_pair(200, 8, 9)
