@@ -542,3 +542,24 @@ def test_zero_grad_to_none_same_step(torchsso_mod, monkeypatch):
         outs.append([p.detach().clone() for p in model.parameters()])
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+def test_batch_prefetcher_delivers_every_batch_in_order(torchsso_mod):
+    """The double-buffered input pipeline: the fixed device tensors hold batch i during iteration i, for
+    more batches than staging buffers, while a kernel on the compute stream keeps the consumer busy."""
+    torchsso = torchsso_mod
+    batches = [(torch.full((64, 3, 8, 8), float(i)).pin_memory(), torch.full((64,), i, dtype=torch.int64).pin_memory())
+               for i in range(7)]
+    x = torch.empty((64, 3, 8, 8), device='cuda')
+    y = torch.empty((64,), dtype=torch.int64, device='cuda')
+    seen = []
+    sink = torch.zeros((), device='cuda')
+    for i in torchsso.utils.BatchPrefetcher(iter(batches), (x, y)):
+        torch.cuda._sleep(2_000_000)            # ~1 ms of "step" between the copy in and the read below
+        sink += x.sum() * 0 + y.float().mean()
+        seen.append((i, x.clone(), y.clone()))
+    torch.cuda.synchronize()
+    assert [i for i, _, _ in seen] == list(range(7))
+    for i, xv, yv in seen:
+        assert torch.equal(xv.cpu(), batches[i][0]) and torch.equal(yv.cpu(), batches[i][1])
+    assert float(sink) == sum(range(7))
