@@ -436,10 +436,20 @@ def run_gpu_arm(args):
         if e2e:
             # every batch comes from pinned host memory inside the timed region, through the package's
             # double-buffered input pipeline (the copy of batch i + 1 runs beside step i), and every
-            # step's loss is read back
+            # step's loss is copied to the host and read there (checked for NaN) one step later
             feed = torchsso.utils.BatchPrefetcher((next_batch(pinned) for _ in range(nsteps)), (x_static, y_static))
-            for _ in feed:
-                last = run_step().item()
+            host_loss = torch.empty(nsteps, dtype=torch.float32).pin_memory()
+            copied = [torch.cuda.Event() for _ in range(nsteps)]
+            for i in feed:
+                host_loss[i:i + 1].copy_(run_step().detach().reshape(1), non_blocking=True)
+                copied[i].record()
+                if i > 0:               # read one step behind, so the host keeps the device fed
+                    copied[i - 1].synchronize()
+                    last = float(host_loss[i - 1])
+                    if last != last:
+                        raise RuntimeError('loss is NaN at e2e step %d' % (i - 1))
+            copied[nsteps - 1].synchronize()
+            last = float(host_loss[nsteps - 1])
         else:
             for i in range(nsteps):
                 last = one_step(*next_batch(resident))
