@@ -311,23 +311,78 @@ __global__ void diag_inv_precond_kernel(const float* __restrict__ ema, float* __
 // ------------------------------------------------------------------------------------------
 // triangular pack / unpack over a table of row runs
 // ------------------------------------------------------------------------------------------
+// Both kernels read through the read-only path in batches of four loads per thread: the source and the
+// destination come out of one record, so with plain loads every load would wait for the previous store.
 __global__ void __launch_bounds__(256) tri_pack_kernel(const sso_tri_rec* __restrict__ recs, float scale) {
   const sso_tri_rec r = recs[blockIdx.x];
   for (int row = r.row0; row < r.row0 + r.nrows; ++row) {
     const int64_t base = (int64_t)r.n * row - (int64_t)row * (row + 1) / 2;
     const float* src = r.m + (int64_t)row * r.ld;
-    for (int x = row + threadIdx.x; x < r.n; x += 256) r.packed[base + x] = scale * src[x];
+    float* dst = r.packed + base;
+    for (int x0 = row + threadIdx.x; x0 < r.n; x0 += 4 * 256) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = (x0 + 256 * u < r.n) ? __ldg(src + x0 + 256 * u) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (x0 + 256 * u < r.n) dst[x0 + 256 * u] = scale * v[u];
+    }
   }
 }
+// A record of at most 32 rows: the part on and above the diagonal is copied row by row (contiguous in the
+// packed form); the part below it is the transpose of packed rows, moved in 32 x 32 tiles through shared
+// memory so that the packed rows are read and the matrix rows written in whole 128-byte lines.  Longer
+// records take the element-wise path (strided reads below the diagonal).
 __global__ void __launch_bounds__(256) tri_unpack_kernel(const sso_tri_rec* __restrict__ recs, float scale,
                                                          int symmetric) {
+  __shared__ float tile[2][32][33];
   const sso_tri_rec r = recs[blockIdx.x];
-  for (int row = r.row0; row < r.row0 + r.nrows; ++row) {
+  const int n = r.n, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* pk = r.packed;
+  auto base = [n](int row) { return (int64_t)n * row - (int64_t)row * (row + 1) / 2; };
+  if (r.nrows > 32) {
+    if (blockIdx.y != 0) return;
+    for (int row = r.row0; row < r.row0 + r.nrows; ++row) {
+      float* dst = r.m + (int64_t)row * r.ld;
+      for (int x = tid; x < n; x += 256) {
+        const int lo = min(row, x), hi = max(row, x);
+        const float v = scale * __ldg(pk + base(lo) + hi);
+        dst[x] = (symmetric || x >= row) ? v : 0.f;
+      }
+    }
+    return;
+  }
+  // gridDim.y CTAs share a record: rows of the upper part and tiles of the lower part are dealt round robin
+  const int part = blockIdx.y, parts = gridDim.y;
+  for (int rr = part; rr < r.nrows; rr += parts) {
+    const int row = r.row0 + rr;
+    const float* src = pk + base(row);
     float* dst = r.m + (int64_t)row * r.ld;
-    for (int x = threadIdx.x; x < r.n; x += 256) {
-      const int lo = min(row, x), hi = max(row, x);
-      const float v = scale * r.packed[(int64_t)r.n * lo - (int64_t)lo * (lo + 1) / 2 + hi];
-      dst[x] = (symmetric || x >= row) ? v : 0.f;
+    for (int x0 = row + tid; x0 < n; x0 += 4 * 256) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = (x0 + 256 * u < n) ? __ldg(src + x0 + 256 * u) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (x0 + 256 * u < n) dst[x0 + 256 * u] = scale * v[u];
+    }
+  }
+  const int xend = r.row0 + r.nrows - 1;        // columns x < xend have elements below the diagonal in this band
+  int buf = 0;
+  for (int x0 = 32 * part; x0 < xend; x0 += 32 * parts, buf ^= 1) {
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int x = x0 + warp + 8 * k, row = r.row0 + lane;
+      v[k] = (symmetric && lane < r.nrows && x < row) ? __ldg(pk + base(x) + row) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tile[buf][warp + 8 * k][lane] = v[k];
+    __syncthreads();          // (two buffers: the next tile's stores cannot overtake this tile's reads)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int rr = warp + 8 * k, row = r.row0 + rr, x = x0 + lane;
+      if (rr < r.nrows && x < row) r.m[(int64_t)row * r.ld + x] = scale * tile[buf][lane][rr];
     }
   }
 }
@@ -338,9 +393,16 @@ __global__ void __launch_bounds__(256) copy_segments_kernel(const sso_seg_rec* _
   const bool vec = ((reinterpret_cast<uintptr_t>(r.src) | reinterpret_cast<uintptr_t>(r.dst)) & 15) == 0;
   if (vec) {
     const int64_t n4 = r.count >> 2;
-    for (int64_t i = threadIdx.x; i < n4; i += 256) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(r.src) + i);
-      reinterpret_cast<float4*>(r.dst)[i] = make_float4(scale * v.x, scale * v.y, scale * v.z, scale * v.w);
+    // four 16-byte loads in flight per thread: one at a time leaves an SM with ~10 KB on its way to it
+    for (int64_t i0 = threadIdx.x; i0 < n4; i0 += 4 * 256) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + 256 * u < n4) v[u] = __ldg(reinterpret_cast<const float4*>(r.src) + i0 + 256 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + 256 * u < n4)
+          reinterpret_cast<float4*>(r.dst)[i0 + 256 * u] = make_float4(scale * v[u].x, scale * v[u].y, scale * v[u].z, scale * v[u].w);
     }
     for (int64_t i = (n4 << 2) + threadIdx.x; i < r.count; i += 256) r.dst[i] = scale * r.src[i];
   } else {
@@ -505,7 +567,7 @@ int sso_tri_pack(const sso_tri_rec* recs_dev, int n_recs, float scale, void* str
 int sso_tri_unpack(const sso_tri_rec* recs_dev, int n_recs, float scale, int symmetric, void* stream) {
   SSO_CHECK_ARG(recs_dev && n_recs >= 0, "tri_unpack: bad argument");
   if (n_recs == 0) return 0;
-  tri_unpack_kernel<<<n_recs, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale, symmetric);
+  tri_unpack_kernel<<<dim3((unsigned)n_recs, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(recs_dev, scale, symmetric);
   SSO_LAUNCH_OK("tri_unpack_kernel");
   return 0;
 }

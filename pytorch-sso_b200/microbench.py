@@ -176,6 +176,21 @@ def suite_stream(args):
     ms = timeit(lambda: nat.ema_update(a, b, 0.95, False), args.iters)
     emit(suite='stream', kernel='ema_update', bytes=12 * n, ms=round(ms, 4), gbs=round(12.0 * n / ms / 1e6, 1),
          frac_of_measured_hbm=round(12.0 * n / ms / 1e6 / hbm, 3))
+    # triangular pack / unpack of the exchange (two 4608^2 and eight 1152^2 factors, as the communicator does it)
+    mats = [torch.randn((4608, 4608), device='cuda') for _ in range(2)] + [torch.randn((1152, 1152), device='cuda') for _ in range(8)]
+    offs, off = [], 0
+    for m in mats:
+        offs.append(off)
+        off += m.shape[0] * (m.shape[0] + 1) // 2
+    buf = torch.empty(off, device='cuda')
+    t_pack, t_unpack = nat.tri_records(mats, buf, offs), nat.tri_records(mats, buf, offs, 32)
+    full = sum(m.numel() for m in mats) * 4
+    ms = timeit(lambda: nat.tri_pack(t_pack, 0.5), args.iters)
+    emit(suite='stream', kernel='tri_pack', bytes=2 * off * 4, ms=round(ms, 4), gbs=round(2 * off * 4 / ms / 1e6, 1),
+         frac_of_measured_hbm=round(2 * off * 4 / ms / 1e6 / hbm, 3))
+    ms = timeit(lambda: nat.tri_unpack(t_unpack, 1.0, True), args.iters)
+    emit(suite='stream', kernel='tri_unpack (symmetric)', bytes=off * 4 + full, ms=round(ms, 4),
+         gbs=round((off * 4 + full) / ms / 1e6, 1), frac_of_measured_hbm=round((off * 4 + full) / ms / 1e6 / hbm, 3))
     ms = timeit(lambda: nat.axpby(a, b, 0.5, 0.5), args.iters)
     emit(suite='stream', kernel='axpby', bytes=12 * n, ms=round(ms, 4), gbs=round(12.0 * n / ms / 1e6, 1),
          frac_of_measured_hbm=round(12.0 * n / ms / 1e6 / hbm, 3))

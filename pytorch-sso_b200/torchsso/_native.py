@@ -564,7 +564,7 @@ def tri_unpack(table: torch.Tensor, scale: float = 1.0, symmetric: bool = True):
 SEG_REC_DTYPE = np.dtype([('src', np.uint64), ('dst', np.uint64), ('count', np.int64)])
 
 
-def seg_records(pairs, device, chunk: int = 1 << 16) -> torch.Tensor:
+def seg_records(pairs, device, chunk: int = 1 << 14) -> torch.Tensor:
     """Device table for sso_copy_segments from (src, dst) pairs of equal-sized flat fp32 tensors."""
     recs = []
     for src, dst in pairs:

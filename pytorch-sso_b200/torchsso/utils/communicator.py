@@ -60,9 +60,18 @@ class DevicePacker:
 
     def __init__(self):
         self._tables = {}
+        self._by_list = {}
 
     def _table(self, arrays, buf, offset, direction):
         from torchsso import _native as nat
+        # A list that comes back unchanged (the communicator caches the lists it extracts) is recognised by
+        # identity, length and its first and last tensor: asking every tensor of a ResNet-50 for its
+        # address on every call costs more host time than the kernels take on the device.
+        quick = (direction, buf.data_ptr(), offset, id(arrays))
+        hit = self._by_list.get(quick)
+        if (hit is not None and hit[0] is arrays and hit[1] == len(arrays) and arrays and
+                hit[2] == (arrays[0][0].data_ptr(), arrays[-1][0].data_ptr())):
+            return hit[3]
         key = (direction, buf.data_ptr(), offset, tuple((t.data_ptr(), tri) for t, tri in arrays))
         ent = self._tables.get(key)
         if ent is None:
@@ -81,11 +90,17 @@ class DevicePacker:
                     strided[1].append(buf[off: off + k].view(t.shape))
                 off += k
             seg_tab = nat.seg_records(flat_pairs, buf.device) if flat_pairs else None
-            tri_tab = nat.tri_records(tri_mats, buf, tri_offs) if tri_mats else None
+            # unpacking goes in bands of 32 rows (the kernel transposes 32 x 32 tiles below the diagonal)
+            tri_tab = nat.tri_records(tri_mats, buf, tri_offs, 32 if direction == 'unpack' else 0) if tri_mats else None
             while len(self._tables) >= 256:      # oldest first; one model needs 2 x world entries
                 self._tables.pop(next(iter(self._tables)))
             ent = (seg_tab, tri_tab, strided)
             self._tables[key] = ent
+        if arrays:
+            while len(self._by_list) >= 256:
+                self._by_list.pop(next(iter(self._by_list)))
+            # (the entry keeps the list alive, so its id cannot be handed to another list meanwhile)
+            self._by_list[quick] = (arrays, len(arrays), (arrays[0][0].data_ptr(), arrays[-1][0].data_ptr()), ent)
         return ent
 
     # ---- 16-bit wire format (per-array scaling fused into the casts) ---------------------------
@@ -152,6 +167,7 @@ class KFACCommunicator:
         self.wire_scaling = bool(wire_scaling)
         self._wire_layouts = {}
         self._extract_cache = {}
+        self._layouts = {}
         self.indices = None
         self._optimizer = None
         self._bufs = {}
@@ -175,13 +191,26 @@ class KFACCommunicator:
         seg = (seg + 63) // 64 * 64       # equal, 256-byte aligned segments
         return sizes, seg
 
+    def _layout(self, arrays: Arrays):
+        """(sizes, segment length, device) of a list of arrays; remembered for lists that come back
+        unchanged (same object, same lengths), like the ones ``extract`` caches."""
+        lens = tuple(len(local) for local in arrays)
+        hit = self._layouts.get(id(arrays))
+        if hit is not None and hit[0] is arrays and hit[1] == lens:
+            return hit[2]
+        sizes, seg = self.segment_sizes(arrays)
+        device = next((t.device for local in arrays for t, _ in local), None)
+        while len(self._layouts) >= 16:
+            self._layouts.pop(next(iter(self._layouts)))
+        self._layouts[id(arrays)] = (arrays, lens, (sizes, seg, device))
+        return sizes, seg, device
+
     # ---- the two collectives -----------------------------------------------------------------
     def reduce_scatterv_arrays(self, arrays: Arrays):
         """Owner r ends up with the world mean of every array in arrays[r]."""
-        sizes, seg = self.segment_sizes(arrays)
+        sizes, seg, device = self._layout(arrays)
         if seg == 0:
             return
-        device = next(t for local in arrays for t, _ in local).device
         send = self._buffer('rsv_send', seg * self.size, device)
         recv = self._buffer('rsv_recv', seg, device)
         for r, local in enumerate(arrays):
@@ -197,10 +226,9 @@ class KFACCommunicator:
 
     def allgatherv_arrays(self, arrays: Arrays, symmetric=True):
         """Every rank ends up with rank r's values of every array in arrays[r]."""
-        sizes, seg = self.segment_sizes(arrays)
+        sizes, seg, device = self._layout(arrays)
         if seg == 0:
             return
-        device = next(t for local in arrays for t, _ in local).device
         send = self._buffer('agv_send', seg, device)
         recv = self._buffer('agv_recv', seg * self.size, device)
         if arrays[self.rank]:

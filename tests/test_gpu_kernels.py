@@ -403,9 +403,12 @@ def test_ema_axpby_diag(nat):
     assert rel(grad, g0.cpu().double() * ref_inv) < 1e-6
 
 
-def test_tri_pack_unpack_roundtrip(nat):
+@pytest.mark.parametrize('rows', [0, 32, 7])
+def test_tri_pack_unpack_roundtrip(nat, rows):
+    """rows: rows per record of the unpack table (0: long records, element-wise path; <= 32: bands whose
+    part below the diagonal is transposed through shared memory, as the communicator unpacks)."""
     mats, packed_ref, offs, off = [], [], [], 0
-    for i, n in enumerate([1, 7, 64, 129, 300]):
+    for i, n in enumerate([1, 7, 64, 129, 300, 1000]):
         m = cases.make_normal((n, n), 40 + i)
         m = m + m.t()
         mats.append(dev(m))
@@ -417,11 +420,11 @@ def test_tri_pack_unpack_roundtrip(nat):
     nat.tri_pack(table, 0.5)
     assert torch.equal(buf.cpu(), 0.5 * torch.cat(packed_ref))
     outs = [torch.full_like(m, float('nan')) for m in mats]
-    nat.tri_unpack(nat.tri_records(outs, buf, offs), 2.0, True)
+    nat.tri_unpack(nat.tri_records(outs, buf, offs, rows), 2.0, True)
     for o, m in zip(outs, mats):
         assert torch.equal(o, m)
     up = [torch.full_like(m, float('nan')) for m in mats]
-    nat.tri_unpack(nat.tri_records(up, buf, offs), 2.0, False)
+    nat.tri_unpack(nat.tri_records(up, buf, offs, rows), 2.0, False)
     for o, m in zip(up, mats):
         assert torch.equal(o, torch.triu(m))
 
