@@ -116,6 +116,11 @@ def _worker(rank, world, port, dims, ret, wire_dtype=None, rtol=1e-6, spread=Fal
         assert torch.equal(lo, hi), 'ranks disagree after the all-gather'
         sizes, seg = comm.segment_sizes(arrays)
         assert seg % 64 == 0 and seg >= max(sizes)
+        # the layout of a list is remembered while the list comes back unchanged, recomputed when it grew
+        assert comm._layout(arrays)[:2] == (sizes, seg)
+        arrays[rank].append((torch.zeros(3 * seg), False))
+        grown, seg2, _ = comm._layout(arrays)
+        assert grown[rank] == sizes[rank] + 3 * seg and seg2 > seg
         ret[rank] = 'ok'
     finally:
         dist.destroy_process_group()
