@@ -45,7 +45,8 @@ uint64_t sso_launch_count(void);
  * the TMA-fed one), "engine_tc" (0/1: 128-wide tile phases of the engine on tcgen05 3xTF32 or fp32 FFMA),
  * "tc_flush" (stages of tensor-core accumulation between drains into fp32 registers),
  * "chol_ksplit" (first 128-column panel of the blocked Cholesky whose update tasks are cut along K;
- * 0 = never; read when a plan is built), "chol_panel" (0/1: a panel's 128x128 diagonal block is factorised
+ * 0 = never; read when a plan is built), "rowwise_max_splits" (column-permuted factors of >= 1024 columns with
+ * at most this many row splits are finished by the kernel that writes whole output rows), "chol_panel" (0/1: a panel's 128x128 diagonal block is factorised
  * and inverted by one launch, or as two 64-wide halves; read when a plan is built), "phase_lpt" (0/1: tasks
  * of a 128-wide phase ordered by decreasing K, so that the longest tasks of a launch start first; read when
  * a plan is built) */

@@ -56,6 +56,7 @@ void factor_tma_set_pair_min_d(int d);
 void factor_tma_set_f32(int on);
 void factor_tma_set_fused_finish(int on);
 void factor_batch_set_pairs(int pairs);
+void factor_tc_set_rowwise_max_splits(int s);
 int factor_tma_launch(FactorParams p, int dtype, void* workspace, size_t workspace_bytes, int flush, cudaStream_t st);
 size_t factor_batch_scratch_bytes(const FactorParams* ps, const int* dtypes, int n);
 int factor_batch_launch(const FactorParams* ps, const int* dtypes, int n, unsigned char* done, void* workspace,
@@ -83,6 +84,7 @@ int sso_configure(const char* key, int value) {
   if (k == "engine_tc") { g_engine_tc = value != 0; return 0; }
   if (k == "tma_f32") { factor_tma_set_f32(value); return 0; }
   if (k == "batch_pairs") { factor_batch_set_pairs(value); return 0; }
+  if (k == "rowwise_max_splits") { factor_tc_set_rowwise_max_splits(value); return 0; }
   if (k == "fused_finish") { factor_tma_set_fused_finish(value); return 0; }
   if (k == "tma_pair_min_d") { factor_tma_set_pair_min_d(value); return 0; }
   if (k == "engine_tma") { g_engine_tma = value != 0; return 0; }

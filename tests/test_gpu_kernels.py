@@ -133,6 +133,7 @@ TC_CONVS = [
     (4, 256, 14, 14, (1, 1), (1, 1), (0, 0), (1, 1), False),
     (16, 32, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1), True),      # 16384 rows: several splits
     (2, 136, 6, 6, (3, 3), (1, 1), (1, 1), (1, 1), False),       # d = 1224: 10 x 10 tiles, ragged edge
+    (32, 128, 16, 16, (3, 3), (1, 1), (1, 1), (1, 1), False),    # d = 1152 from 8192 rows: several splits, row-wise finish
 ]
 
 
