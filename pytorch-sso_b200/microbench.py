@@ -5,8 +5,8 @@
     python pytorch-sso_b200/microbench.py rows     [--case I]      fp32 X^T X, d in 64..4608
     python pytorch-sso_b200/microbench.py inverse  [--case I]      damped SPD inverse, d in 64..4608
     python pytorch-sso_b200/microbench.py precond  [--case I]      G^-1 dW A^-1
-    python pytorch-sso_b200/microbench.py stream                   EMA / axpby / BN plane sums
-    python pytorch-sso_b200/microbench.py steps                    whole steps of the smaller reference configurations
+    python pytorch-sso_b200/microbench.py stream                   EMA / axpby / BN plane sums / triangular pack and unpack
+    python pytorch-sso_b200/microbench.py steps    [--case 0..3]   whole steps of the smaller reference configurations
     python pytorch-sso_b200/microbench.py peaks                    cuBLAS bf16 / TF32 GEMM and copy, for reference
     torchrun ... pytorch-sso_b200/microbench.py collective         factor exchange sweep (N > 1)
 
