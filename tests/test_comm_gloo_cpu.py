@@ -183,3 +183,15 @@ def test_owner_assignment_rules():
     assert max(sum([98, 10, 10, 10, 10][i] for i in p) for p in parts) == 98
     with pytest.raises(ValueError):
         assign_owners([1], 1, 'nope')
+
+
+def test_host_side_argument_checks():
+    """Switches that are refused before anything touches a device."""
+    import torchsso
+    with pytest.raises(ValueError, match='prune_sampling_pass'):
+        torchsso.get_closure_for_fisher(None, None, None, None, approx_type='mc', num_mc=2,
+                                        prune_sampling_pass=False, batch_mc_passes=True)
+    from torchsso.utils.communicator import KFACCommunicator
+    assert not dist.is_initialized()
+    with pytest.raises(RuntimeError, match='not initialised'):
+        KFACCommunicator()
